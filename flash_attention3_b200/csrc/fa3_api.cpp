@@ -1,0 +1,224 @@
+// Host-only half of the C ABI: parameter initialisation, capability report,
+// validation, workspace sizing and status strings.  This translation unit has
+// no CUDA dependency, so the contract tests can exercise it on a machine
+// without a GPU.  Behaviour follows reference src/shaobo_fa3_bwd_api.cpp
+// (validation order and status codes, lines 70-120; workspace carving, lines
+// 122-156), widened to BF16 and head_dim 64.
+#include <cmath>
+#include <cstring>
+#include <limits>
+
+#include "fa3_host.h"
+#include "shaobo_fa3_components.h"
+
+namespace fa3b200 {
+
+bool mul_ok(size_t a, size_t b, size_t* out) {
+    if (a != 0 && b > std::numeric_limits<size_t>::max() / a) return false;
+    *out = a * b;
+    return true;
+}
+
+bool add_ok(size_t a, size_t b, size_t* out) {
+    if (b > std::numeric_limits<size_t>::max() - a) return false;
+    *out = a + b;
+    return true;
+}
+
+bool round_up_256(size_t bytes, size_t* out) {
+    size_t padded = 0;
+    if (!add_ok(bytes, kWorkspaceAlignment - 1, &padded)) return false;
+    *out = padded & ~(kWorkspaceAlignment - 1);
+    return true;
+}
+
+namespace {
+
+bool is_flag(int32_t v) { return v == 0 || v == 1; }
+
+bool finite_nonneg(float v) { return std::isfinite(v) && v >= 0.0f; }
+
+// A window that covers every key a causal / full mask would cover counts as
+// "no window" (reference src/shaobo_fa3_bwd_api.cpp:53-68).
+bool window_is_plain(const ShaoboFa3Params* p) {
+    int left = p->window_left >= p->seqlen_k - 1 ? -1 : p->window_left;
+    int right = p->window_right >= p->seqlen_q - 1 ? -1 : p->window_right;
+    if (p->causal != 0) right = 0;
+    if (left >= 0) return false;
+    return p->causal != 0 ? right == 0 : right < 0;
+}
+
+bool lengths_are_fixed(const ShaoboFa3Params* p) {
+    if (p->cu_seqlens_q || p->cu_seqlens_k || p->seqused_q || p->seqused_k) return false;
+    if (p->max_seqlen_q != 0 && p->max_seqlen_q != p->seqlen_q) return false;
+    if (p->max_seqlen_k != 0 && p->max_seqlen_k != p->seqlen_k) return false;
+    const int64_t tq = int64_t(p->batch) * p->seqlen_q;
+    const int64_t tk = int64_t(p->batch) * p->seqlen_k;
+    if (p->total_q != 0 && p->total_q != tq) return false;
+    if (p->total_k != 0 && p->total_k != tk) return false;
+    return true;
+}
+
+size_t row_count(const ShaoboFa3Params* p, bool* ok) {
+    size_t rows = size_t(p->batch);
+    *ok = mul_ok(rows, size_t(p->num_heads_q), &rows) && mul_ok(rows, size_t(p->seqlen_q), &rows);
+    return rows;
+}
+
+}  // namespace
+
+int validate_v2(const ShaoboFa3Params* p) {
+    // ---- malformed input: INVALID_VALUE -------------------------------------
+    if (p == nullptr || p->struct_size < sizeof(ShaoboFa3Params)) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    const bool dims_ok = p->batch > 0 && p->seqlen_q > 0 && p->seqlen_k > 0 &&
+                         p->num_heads_q > 0 && p->num_heads_kv > 0 &&
+                         p->num_heads_q % p->num_heads_kv == 0;
+    const bool flags_ok = is_flag(p->causal) && is_flag(p->deterministic) &&
+                          is_flag(p->sync_after_launch) && is_flag(p->softmax_scale_is_set);
+    const bool scale_ok = p->softmax_scale_is_set == 0 || finite_nonneg(p->softmax_scale);
+    const bool reals_ok = finite_nonneg(p->softcap) && finite_nonneg(p->dropout_p) &&
+                          p->dropout_p < 1.0f;
+    if (!(dims_ok && flags_ok && scale_ok && reals_ok)) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    // ---- well-formed but outside the capability set: UNSUPPORTED ------------
+    if (!lengths_are_fixed(p) || !dtype_supported(p->dtype) ||
+        p->layout != SHAOBO_FA3_LAYOUT_BHSD || !head_dim_supported(p->head_dim_qk) ||
+        p->head_dim_v != p->head_dim_qk || p->seqlen_q != p->seqlen_k ||
+        p->seqlen_q % kSequenceAlignment != 0 || p->dropout_p != 0.0f ||
+        p->softcap != 0.0f || p->sm_margin != 0 || !window_is_plain(p)) {
+        return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    }
+    return SHAOBO_FA3_STATUS_SUCCESS;
+}
+
+bool fused_shape_ok(const ShaoboFa3Params* p) {
+    return p != nullptr && p->batch > 0 && p->num_heads_q > 0 && p->num_heads_kv > 0 &&
+           p->num_heads_q % p->num_heads_kv == 0 && p->seqlen_q > 0 &&
+           p->seqlen_q == p->seqlen_k && p->seqlen_k % kSequenceAlignment == 0 &&
+           head_dim_supported(p->head_dim_qk) && p->head_dim_v == p->head_dim_qk;
+}
+
+size_t dq_accum_bytes(const ShaoboFa3Params* p) {
+    if (!fused_shape_ok(p)) return 0;
+    bool ok = false;
+    size_t n = row_count(p, &ok);
+    size_t out = 0;
+    if (!ok || !mul_ok(n, size_t(p->head_dim_qk), &n) || !mul_ok(n, sizeof(float), &n) ||
+        !round_up_256(n, &out)) {
+        return 0;
+    }
+    return out;
+}
+
+V2Workspace v2_workspace(const ShaoboFa3Params* p) {
+    V2Workspace w;
+    if (validate_v2(p) != SHAOBO_FA3_STATUS_SUCCESS) return w;
+    w.dq_accum_bytes = dq_accum_bytes(p);
+    if (w.dq_accum_bytes == 0) return w;
+    w.delta_offset = w.dq_accum_bytes;  // already a multiple of 256
+    bool ok = false;
+    const size_t rows = row_count(p, &ok);
+    size_t delta_bytes = 0, sidecar_bytes = 0, end_of_delta = 0;
+    if (!ok || !mul_ok(rows, sizeof(float), &delta_bytes) ||
+        !mul_ok(delta_bytes, size_t(kSidecarFields), &sidecar_bytes) ||
+        !add_ok(w.delta_offset, delta_bytes, &end_of_delta) ||
+        !round_up_256(end_of_delta, &w.sidecar_offset) ||
+        !add_ok(w.sidecar_offset, sidecar_bytes, &w.total_bytes)) {
+        return V2Workspace{};
+    }
+    w.valid = true;
+    return w;
+}
+
+size_t naive_reference_bytes(const ShaoboFa3Params* p) {
+    if (p == nullptr || p->batch <= 0 || p->seqlen_q <= 0 || p->seqlen_k != p->seqlen_q ||
+        p->num_heads_q <= 0 || p->num_heads_kv != p->num_heads_q ||
+        !head_dim_supported(p->head_dim_qk) || p->head_dim_v != p->head_dim_qk ||
+        !dtype_supported(p->dtype) || p->layout != SHAOBO_FA3_LAYOUT_BHSD ||
+        p->dropout_p != 0.0f) {
+        return 0;
+    }
+    bool ok = false;
+    const size_t rows = row_count(p, &ok);
+    size_t pairs = 0, total = 0, tail = 0;
+    if (!ok || !mul_ok(rows, size_t(p->seqlen_k), &pairs) || !mul_ok(pairs, 2, &total) ||
+        !mul_ok(rows, 3, &tail) || !add_ok(total, tail, &total) ||
+        !mul_ok(total, sizeof(float), &total)) {
+        return 0;
+    }
+    return total;
+}
+
+}  // namespace fa3b200
+
+using namespace fa3b200;
+
+extern "C" void shaobo_fa3_params_init(ShaoboFa3Params* params) {
+    if (params == nullptr) return;
+    std::memset(params, 0, sizeof(ShaoboFa3Params));
+    params->struct_size = uint32_t(sizeof(ShaoboFa3Params));
+    params->window_left = -1;
+    params->window_right = -1;
+    params->dtype = SHAOBO_FA3_DTYPE_FP16;
+    params->layout = SHAOBO_FA3_LAYOUT_BHSD;
+    params->softmax_aux_mode = SHAOBO_FA3_SOFTMAX_AUX_LSE;
+}
+
+extern "C" int shaobo_fa3_bwd_get_capabilities(ShaoboFa3BwdCapabilities* caps) {
+    if (caps == nullptr || caps->struct_size < sizeof(ShaoboFa3BwdCapabilities)) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    caps->api_version = SHAOBO_FA3_API_VERSION;
+    // The reference's set (src/shaobo_fa3_bwd_api.cpp:180-187) plus BF16.
+    caps->feature_mask = SHAOBO_FA3_BWD_FEATURE_FIXED_LENGTH | SHAOBO_FA3_BWD_FEATURE_FP16 |
+                         SHAOBO_FA3_BWD_FEATURE_BF16 | SHAOBO_FA3_BWD_FEATURE_CAUSAL |
+                         SHAOBO_FA3_BWD_FEATURE_GQA | SHAOBO_FA3_BWD_FEATURE_DETERMINISTIC |
+                         SHAOBO_FA3_BWD_FEATURE_SOFTMAX_LSE | SHAOBO_FA3_BWD_FEATURE_BHSD |
+                         SHAOBO_FA3_BWD_FEATURE_FULL_ATTENTION;
+    caps->min_head_dim = kMinHeadDim;
+    caps->max_head_dim = kMaxHeadDim;
+    caps->head_dim_alignment = kMinHeadDim;
+    caps->sequence_alignment = kSequenceAlignment;
+    return SHAOBO_FA3_STATUS_SUCCESS;
+}
+
+extern "C" int shaobo_fa3_bwd_v2_validate(const ShaoboFa3Params* params) {
+    return validate_v2(params);
+}
+
+extern "C" size_t shaobo_fa3_bwd_v2_workspace_bytes(const ShaoboFa3Params* params) {
+    const V2Workspace w = v2_workspace(params);
+    return w.valid ? w.total_bytes : 0;
+}
+
+extern "C" size_t shaobo_fa3_bwd_fused5_workspace_bytes(const ShaoboFa3Params* params) {
+    if (params == nullptr || !dtype_supported(params->dtype) ||
+        params->layout != SHAOBO_FA3_LAYOUT_BHSD) {
+        return 0;
+    }
+    return dq_accum_bytes(params);
+}
+
+extern "C" size_t shaobo_fa3_bwd_dkv_workspace_bytes(const ShaoboFa3Params* params) {
+    if (params == nullptr || params->dkv_path != SHAOBO_FA3_DKV_PATH_REFERENCE) return 0;
+    return naive_reference_bytes(params);
+}
+
+extern "C" size_t shaobo_fa3_bwd_dq_workspace_bytes(const ShaoboFa3Params* params) {
+    if (params == nullptr || params->dq_path != SHAOBO_FA3_DQ_PATH_REFERENCE) return 0;
+    return naive_reference_bytes(params);
+}
+
+extern "C" size_t shaobo_fa3_bwd_workspace_bytes(const ShaoboFa3Params* params) {
+    return shaobo_fa3_bwd_dkv_workspace_bytes(params);
+}
+
+extern "C" const char* shaobo_fa3_status_string(int status) {
+    static const char* const names[] = {"success", "invalid_value", "unsupported",
+                                        "not_implemented", "hip_error"};
+    if (status < 0 || status > SHAOBO_FA3_STATUS_HIP_ERROR) return "unknown";
+    return names[status];
+}

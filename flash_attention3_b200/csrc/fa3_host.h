@@ -1,0 +1,59 @@
+// Host-side helpers shared by the validation layer (fa3_api.cpp, plain C++)
+// and the launch layer (fa3_launch.cu).  Nothing here touches CUDA.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include "shaobo_fa3_api.h"
+
+namespace fa3b200 {
+
+constexpr size_t kWorkspaceAlignment = 256;  // same as reference src/shaobo_fa3_bwd_api.cpp:16
+constexpr int kSequenceAlignment = 128;      // K/Q tile edge; reference :18
+constexpr int kMinHeadDim = 64;
+constexpr int kMaxHeadDim = 128;
+constexpr int kSidecarFields = 3;            // {m, r, delta}; reference src/dot_do_o_kernel.cpp:11
+
+// Overflow-checked size arithmetic (role of reference
+// src/shaobo_fa3_bwd_api.cpp:28-51).
+bool mul_ok(size_t a, size_t b, size_t* out);
+bool add_ok(size_t a, size_t b, size_t* out);
+bool round_up_256(size_t bytes, size_t* out);
+
+inline bool head_dim_supported(int d) { return d == 64 || d == 128; }
+inline bool dtype_supported(int t) {
+    return t == SHAOBO_FA3_DTYPE_FP16 || t == SHAOBO_FA3_DTYPE_BF16;
+}
+
+// Public validation used by every v2 entry.
+int validate_v2(const ShaoboFa3Params* p);
+
+// Shape test shared by the fused stage and its workspace formula: positive
+// dims, Hq % Hkv == 0, Sq == Sk, S % 128 == 0, D in {64,128}, Dqk == Dv.
+bool fused_shape_ok(const ShaoboFa3Params* p);
+
+// Bytes of the fp32 dQ accumulator [B,Hq,S,D] rounded up to 256; 0 on
+// overflow or unsupported shape.
+size_t dq_accum_bytes(const ShaoboFa3Params* p);
+
+// Carving of the caller's workspace by shaobo_fa3_bwd_v2:
+//   [0, dq_accum)                fp32 dQ accumulator
+//   [delta_offset, +rows*4)      delta, used when softmax_d is NULL
+//   [sidecar_offset, +rows*12)   packed sidecar
+// Each region starts on a 256-byte boundary.
+struct V2Workspace {
+    size_t dq_accum_bytes = 0;
+    size_t delta_offset = 0;
+    size_t sidecar_offset = 0;
+    size_t total_bytes = 0;
+    bool valid = false;
+};
+V2Workspace v2_workspace(const ShaoboFa3Params* p);
+
+// Workspace of the naive fp32 device reference used by dkv_path/dq_path == 1:
+// prob[rows,Sk] + dp[rows,Sk] + row_max + row_sum + delta
+// (reference src/dkv_kernel.cpp:88-97).
+size_t naive_reference_bytes(const ShaoboFa3Params* p);
+
+}  // namespace fa3b200
