@@ -1,0 +1,301 @@
+// Three-GEMM dQ kernel for sm_100a: the dQ half of the atomic-free split path.
+//
+// One CTA owns one (batch, query head, 128-row query tile): Q and dO stay in
+// shared memory, K and V tiles stream through a two-stage ring, and dQ is
+// accumulated in tensor memory over all key tiles in a fixed order, so the
+// result is bitwise reproducible and needs no workspace.  Per key tile:
+//
+//     S  = Q K^T      [query i on TMEM lanes, key j on columns]        SS MMA
+//     dP = dO V^T                                                       SS MMA
+//     dS = exp2(S*scale*log2e - m_i) * r_i * (dP - delta_i)  -> TMEM b16
+//          (row statistics live in registers: thread i owns query row i)
+//     dQ += dS K      A = dS from TMEM, B = K (MN-major)                TS MMA
+//
+// Tensor-memory ledger: S [0,128)  dP, then dS in place [128,256)  dQ [256,256+D).
+// Shared-memory ledger: Q, dO resident (2 x D*256), K and V two stages each
+// (4 x D*256), mbarriers 128: 196,736 bytes at D=128, 98,432 at D=64.
+//
+// Same math as reference src/dq_kernel.cpp:546-596 (S, dP, dS, dQ per K/V
+// page with a resident Q/dO tile), restated for tcgen05.
+#pragma once
+
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "fused_bwd_kernel.cuh"
+#include "ptx.cuh"
+
+namespace fa3b200 {
+
+struct DqArgs {
+    const float* sidecar;  // [B,Hq,S,3]
+    void* dq;              // [B,Hq,S,D]
+    int batch;
+    int heads_q;
+    int heads_kv;
+    int seqlen;
+    float scale;
+    float scale_log2;
+};
+
+template <int D>
+struct DqCfg {
+    static constexpr int kTile = 128;
+    static constexpr int kThreads = 256;
+    static constexpr int kBoxBytes = 128 * 128;
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kOperandBytes = kBoxes * kBoxBytes;
+    static constexpr int kStages = 2;
+    static constexpr int kOffQ = 0;
+    static constexpr int kOffDO = kOperandBytes;
+    static constexpr int kOffK = 2 * kOperandBytes;
+    static constexpr int kOffV = kOffK + kStages * kOperandBytes;
+    static constexpr int kOffBar = kOffV + kStages * kOperandBytes;
+    static constexpr int kSmemBytes = kOffBar + 128;
+    static constexpr int kTmemCols = 512;
+    static constexpr int kColS = 0;
+    static constexpr int kColDP = 128;
+    static constexpr int kColDQ = 256;
+};
+
+enum DqBar : int {
+    kDqbQFull = 0,
+    kDqbKvFull = 1,   // 2 stages
+    kDqbKvEmpty = 3,  // 2 stages
+    kDqbSFull = 5,
+    kDqbDpFull = 6,
+    kDqbSFree = 7,
+    kDqbDsReady = 8,
+    kDqbDone = 9,
+    kDqbNum = 10,
+};
+
+template <typename T, int D, bool kCausal, typename TOut>
+__global__ void __launch_bounds__(256, 1)
+dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+              const DqArgs a) {
+    using C = DqCfg<D>;
+    constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = ptx::smem_u32(smem);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    auto bar = [&](int i) -> uint32_t { return sbase + C::kOffBar + 8 * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kDqbNum);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int n_tiles = a.seqlen / C::kTile;
+    const int bh_count = a.batch * a.heads_q;
+    // heaviest query tiles (most visible keys) are launched first
+    const int qt = kCausal ? n_tiles - 1 - int(blockIdx.x) / bh_count : int(blockIdx.x) / bh_count;
+    const int bhi = int(blockIdx.x) % bh_count;
+    const int b = bhi / a.heads_q;
+    const int hq = bhi % a.heads_q;
+    const int kvh = hq / (a.heads_q / a.heads_kv);
+    const int n_steps = kCausal ? qt + 1 : n_tiles;  // key tiles 0 .. n_steps-1, diagonal last
+    const bool misaligned = (sbase & 1023u) != 0;
+
+    if (threadIdx.x == 0) {
+        if (misaligned) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
+        ptx::mbar_init(bar(kDqbQFull), 1);
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(bar(kDqbKvFull + s), 1);
+            ptx::mbar_init(bar(kDqbKvEmpty + s), 1);
+        }
+        ptx::mbar_init(bar(kDqbSFull), 1);
+        ptx::mbar_init(bar(kDqbDpFull), 1);
+        ptx::mbar_init(bar(kDqbSFree), 128);
+        ptx::mbar_init(bar(kDqbDsReady), 128);
+        ptx::mbar_init(bar(kDqbDone), 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile;
+
+    if (!misaligned) {
+        if (warp == 0) {
+            if (lane == 0) {
+                ptx::prefetch_tensormap(&tm_q);
+                ptx::prefetch_tensormap(&tm_k);
+                ptx::prefetch_tensormap(&tm_v);
+                ptx::prefetch_tensormap(&tm_do);
+                ptx::mbar_arrive_expect_tx(bar(kDqbQFull), 2 * C::kOperandBytes);
+#pragma unroll
+                for (int bx = 0; bx < C::kBoxes; ++bx) {
+                    ptx::tma_load_2d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kDqbQFull), bx * 64, q_row);
+                    ptx::tma_load_2d(sbase + C::kOffDO + bx * C::kBoxBytes, &tm_do, bar(kDqbQFull), bx * 64, q_row);
+                }
+#pragma unroll 1
+                for (int t = 0; t < n_steps; ++t) {
+                    const int s = t & 1;
+                    const int kv_row = (b * a.heads_kv + kvh) * a.seqlen + t * C::kTile;
+                    if (!bounded_wait(bar(kDqbKvEmpty + s), ((t >> 1) & 1) ^ 1, abort_flag)) break;
+                    ptx::mbar_arrive_expect_tx(bar(kDqbKvFull + s), 2 * C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
+                        ptx::tma_load_2d(sbase + C::kOffK + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_k,
+                                         bar(kDqbKvFull + s), bx * 64, kv_row);
+                        ptx::tma_load_2d(sbase + C::kOffV + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_v,
+                                         bar(kDqbKvFull + s), bx * 64, kv_row);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                constexpr uint32_t kIdSdP = ptx::instr_desc_f16(kBf16, 128, 128, false, false);
+                constexpr uint32_t kIdDq = ptx::instr_desc_f16(kBf16, 128, D, false, true);
+                auto k_major = [&](uint32_t base, int kk) -> uint64_t {
+                    return ptx::smem_desc_sw128(base + (kk >> 2) * C::kBoxBytes + (kk & 3) * 32, 16, 1024);
+                };
+                auto mn_major = [&](uint32_t base, int kk) -> uint64_t {
+                    return ptx::smem_desc_sw128(base + kk * 2048, C::kBoxBytes, 1024);
+                };
+                const uint32_t sQ = sbase + C::kOffQ, sDO = sbase + C::kOffDO;
+                auto sK = [&](int t) { return sbase + C::kOffK + (t & 1) * C::kOperandBytes; };
+                auto sV = [&](int t) { return sbase + C::kOffV + (t & 1) * C::kOperandBytes; };
+                auto issue_s = [&](int t) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        ptx::mma_ss(tmem + C::kColS, k_major(sQ, kk), k_major(sK(t), kk), kIdSdP, kk > 0);
+                    ptx::tc_commit(bar(kDqbSFull));
+                };
+                auto issue_dp = [&](int t) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        ptx::mma_ss(tmem + C::kColDP, k_major(sDO, kk), k_major(sV(t), kk), kIdSdP, kk > 0);
+                    ptx::tc_commit(bar(kDqbDpFull));
+                };
+                bool ok = bounded_wait(bar(kDqbQFull), 0, abort_flag) &&
+                          bounded_wait(bar(kDqbKvFull + 0), 0, abort_flag);
+                if (ok) {
+                    ptx::tc_fence_after();
+                    issue_s(0);
+                    issue_dp(0);
+                }
+#pragma unroll 1
+                for (int t = 0; ok && t < n_steps; ++t) {
+                    const bool more = t + 1 < n_steps;
+                    if (more) {
+                        // S(t) is in registers: S(t+1) may overwrite it
+                        if (!(ok = bounded_wait(bar(kDqbSFree), t & 1, abort_flag))) break;
+                        if (!(ok = bounded_wait(bar(kDqbKvFull + ((t + 1) & 1)), ((t + 1) >> 1) & 1, abort_flag))) break;
+                        ptx::tc_fence_after();
+                        issue_s(t + 1);
+                    }
+                    if (!(ok = bounded_wait(bar(kDqbDsReady), t & 1, abort_flag))) break;
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)
+                        ptx::mma_ts(tmem + C::kColDQ, tmem + C::kColDP + kk * 8, mn_major(sK(t), kk), kIdDq,
+                                    (t > 0 || kk > 0) ? 1u : 0u);
+                    if (more) issue_dp(t + 1);  // after dQ(t) in issue order: dS(t) is consumed first
+                    ptx::tc_commit(bar(kDqbKvEmpty + (t & 1)));
+                }
+                if (ok) ptx::tc_commit(bar(kDqbDone));
+            }
+        } else if (warp >= 4) {
+            const int i = threadIdx.x - 128;  // query row inside the tile == TMEM lane
+            const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
+            const float* side = a.sidecar + (int64_t(q_row) + i) * 3;
+            const float neg = __log2f(side[1]) - side[0];
+            const float delta = side[2];
+            uint32_t ppk[64];
+            bool ok = true;
+#pragma unroll 1
+            for (int t = 0; t < n_steps; ++t) {
+                if (!(ok = warp_wait(bar(kDqbSFull), t & 1, abort_flag))) break;
+                ptx::tc_fence_after();
+                const bool diagonal = kCausal && t == qt;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tl + C::kColS + c * 32, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, neg));
+                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, neg));
+                        if (diagonal) {
+                            const int j = c * 32 + e;
+                            p0 = (j + 0 <= i) ? p0 : 0.0f;
+                            p1 = (j + 1 <= i) ? p1 : 0.0f;
+                        }
+                        ppk[c * 16 + e / 2] = ptx::Pack2<T>::pack(p0, p1);
+                    }
+                }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(bar(kDqbSFree));
+                if (!(ok = warp_wait(bar(kDqbDpFull), t & 1, abort_flag))) break;
+                ptx::tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tl + C::kColDP + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    uint32_t o[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float2 p = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2]);
+                        o[e / 2] = ptx::Pack2<T>::pack(p.x * (__uint_as_float(r[e + 0]) - delta),
+                                                       p.y * (__uint_as_float(r[e + 1]) - delta));
+                    }
+                    // dS chunk c lands on columns [16c, 16c+16) of the dP region,
+                    // all of which were read by chunk loads <= c
+                    ptx::tmem_st16(tl + C::kColDP + c * 16, o);
+                }
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(bar(kDqbDsReady));
+            }
+            if (ok) ok = warp_wait(bar(kDqbDone), 0, abort_flag);
+            if (ok) {
+                ptx::tc_fence_after();
+                TOut* dst = reinterpret_cast<TOut*>(a.dq) + (int64_t(q_row) + i) * D;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tl + C::kColDQ + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    if (sizeof(TOut) == 4) {
+                        float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            d4[e] = make_float4(__uint_as_float(r[4 * e]) * a.scale, __uint_as_float(r[4 * e + 1]) * a.scale,
+                                                __uint_as_float(r[4 * e + 2]) * a.scale, __uint_as_float(r[4 * e + 3]) * a.scale);
+                    } else {
+                        uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            uint4 o;
+                            o.x = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 0]) * a.scale, __uint_as_float(r[8 * e + 1]) * a.scale);
+                            o.y = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 2]) * a.scale, __uint_as_float(r[8 * e + 3]) * a.scale);
+                            o.z = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 4]) * a.scale, __uint_as_float(r[8 * e + 5]) * a.scale);
+                            o.w = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 6]) * a.scale, __uint_as_float(r[8 * e + 7]) * a.scale);
+                            d4[e] = o;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem, C::kTmemCols);
+    }
+}
+
+}  // namespace fa3b200

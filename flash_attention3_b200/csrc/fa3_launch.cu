@@ -1,0 +1,458 @@
+// Launch layer of the C ABI: tensor-map construction, kernel dispatch over
+// (dtype, head_dim, causal) and the stage chaining of shaobo_fa3_bwd_v2
+// (role of reference src/shaobo_fa3_bwd_api.cpp:206-260 and
+// src/fused_bwd_kernel.cpp:1673-1764).  No allocation happens here: every
+// buffer, the workspace included, belongs to the caller.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "cta_order.h"
+#include "fa3_host.h"
+#include "fused_bwd_kernel.cuh"
+#include "dq_kernel.cuh"
+#include "rowwise_kernels.cuh"
+#include "shaobo_fa3_components.h"
+
+namespace fa3b200 {
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+                cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            p = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Row-major [rows, cols] tensor, boxes of [box_rows][box_cols] with the
+// 128-byte swizzle (box_cols * element size must be 128 bytes).
+bool make_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base,
+              uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * uint64_t(elem_bytes)};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return fn(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaStream_t stream_of(const ShaoboFa3Params* p) {
+    return static_cast<cudaStream_t>(p->reserved_ptr[SHAOBO_FA3_RESERVED_PTR_STREAM]);
+}
+
+int sm_count() {
+    static std::mutex mu;
+    static std::map<int, int> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(dev);
+    if (it != cache.end()) return it->second;
+    int n = 148;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cache[dev] = n;
+    return n;
+}
+
+CtaOrderPlan cached_plan(int n_tiles, int bh, int group, bool causal, int sms) {
+    static std::mutex mu;
+    static std::map<std::tuple<int, int, int, bool, int>, CtaOrderPlan> cache;
+    const auto key = std::make_tuple(n_tiles, bh, group, causal, sms);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    const CtaOrderPlan plan = plan_cta_order(n_tiles, bh, group, causal, sms);
+    cache[key] = plan;
+    return plan;
+}
+
+int finish(const ShaoboFa3Params* p, bool sync) {
+    if (cudaGetLastError() != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
+    if (sync && cudaStreamSynchronize(stream_of(p)) != cudaSuccess) {
+        return SHAOBO_FA3_STATUS_HIP_ERROR;
+    }
+    return SHAOBO_FA3_STATUS_SUCCESS;
+}
+
+// ------------------------------------------------------------------ delta
+template <typename T, int D>
+void launch_delta_t(const void* dout, const void* out, const float* aux0, const float* aux1,
+                    float* delta, float* sidecar, float* zero_rows, int64_t rows, bool lse,
+                    float scale_log2, cudaStream_t st) {
+    constexpr int kRowsPerBlock = 8 * (32 / (D / 8));
+    int64_t blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+    const int64_t cap = int64_t(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    if (lse) {
+        delta_sidecar_kernel<T, D, true><<<int(blocks), 256, 0, st>>>(
+            static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
+            zero_rows, rows, scale_log2);
+    } else {
+        delta_sidecar_kernel<T, D, false><<<int(blocks), 256, 0, st>>>(
+            static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
+            zero_rows, rows, scale_log2);
+    }
+}
+
+void launch_delta(const ShaoboFa3Params* p, const void* dout, const void* out, const float* aux0,
+                  const float* aux1, float* delta, float* sidecar, float* zero_rows, bool lse) {
+    const int64_t rows = int64_t(p->batch) * p->num_heads_q * p->seqlen_q;
+    const float scale_log2 = p->softmax_scale * kLog2E;
+    cudaStream_t st = stream_of(p);
+    const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
+    if (p->head_dim_qk == 128) {
+        if (bf) launch_delta_t<__nv_bfloat16, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, st);
+        else launch_delta_t<__half, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, st);
+    } else {
+        if (bf) launch_delta_t<__nv_bfloat16, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, st);
+        else launch_delta_t<__half, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, st);
+    }
+}
+
+// ---------------------------------------------------------------- convert
+void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq) {
+    const int64_t n8 = int64_t(p->batch) * p->num_heads_q * p->seqlen_q * p->head_dim_qk / 8;
+    int64_t blocks = (n8 + 255) / 256;
+    const int64_t cap = int64_t(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = stream_of(p);
+    if (p->dtype == SHAOBO_FA3_DTYPE_BF16) {
+        dq_convert_kernel<__nv_bfloat16><<<int(blocks), 256, 0, st>>>(
+            accum, static_cast<__nv_bfloat16*>(dq), n8, p->softmax_scale);
+    } else {
+        dq_convert_kernel<__half><<<int(blocks), 256, 0, st>>>(accum, static_cast<__half*>(dq), n8,
+                                                              p->softmax_scale);
+    }
+}
+
+// ------------------------------------------------------- fused / dKV kernel
+template <typename T, int D, bool kCausal, bool kWithDq, typename TOut>
+int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                   const CUtensorMap& mdo, const CUtensorMap& mdq, const FusedArgs& args,
+                   int blocks, cudaStream_t st) {
+    auto kernel = fused_bwd_kernel<T, D, kCausal, kWithDq, TOut>;
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 FusedCfg<D>::kSmemBytes) != cudaSuccess) {
+            return SHAOBO_FA3_STATUS_HIP_ERROR;
+        }
+        configured = true;
+    }
+    kernel<<<blocks, FusedCfg<D>::kThreads, FusedCfg<D>::kSmemBytes, st>>>(mq, mk, mv, mdo, mdq, args);
+    return SHAOBO_FA3_STATUS_SUCCESS;
+}
+
+template <typename T, bool kWithDq, typename TOut>
+int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorMap& mk,
+                   const CUtensorMap& mv, const CUtensorMap& mdo, const CUtensorMap& mdq,
+                   const FusedArgs& args, int blocks) {
+    cudaStream_t st = stream_of(p);
+    if (p->head_dim_qk == 128) {
+        return p->causal ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st)
+                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st);
+    }
+    return p->causal ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st)
+                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st);
+}
+
+// with_dq: fused five-GEMM kernel writing dK/dV in the input dtype and adding
+// dQ into dq_accum (already zero).  !with_dq: four-GEMM dK/dV kernel with fp32
+// outputs (split path).
+int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
+                 const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
+                 bool with_dq) {
+    const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
+    const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const uint64_t d = uint64_t(p->head_dim_qk);
+    const uint64_t q_rows = uint64_t(p->batch) * p->num_heads_q * p->seqlen_q;
+    const uint64_t kv_rows = uint64_t(p->batch) * p->num_heads_kv * p->seqlen_k;
+    CUtensorMap mq, mk, mv, mdo, mdq;
+    if (!make_map(&mq, type, 2, q, q_rows, d, 64, 128) ||
+        !make_map(&mk, type, 2, k, kv_rows, d, 64, 128) ||
+        !make_map(&mv, type, 2, v, kv_rows, d, 64, 128) ||
+        !make_map(&mdo, type, 2, dout, q_rows, d, 64, 128)) {
+        return SHAOBO_FA3_STATUS_HIP_ERROR;
+    }
+    if (with_dq) {
+        if (!make_map(&mdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dq_accum, q_rows, d, 32, 32)) {
+            return SHAOBO_FA3_STATUS_HIP_ERROR;
+        }
+    } else {
+        mdq = mq;  // unused by the kernel
+    }
+    const int n_tiles = p->seqlen_k / 128;
+    const int bh = p->batch * p->num_heads_kv;
+    const int group = p->num_heads_q / p->num_heads_kv;
+    const CtaOrderPlan plan = cached_plan(n_tiles, bh, group, p->causal != 0, sm_count());
+    FusedArgs args;
+    args.sidecar = sidecar;
+    args.dk = dk;
+    args.dv = dv;
+    args.batch = p->batch;
+    args.heads_q = p->num_heads_q;
+    args.heads_kv = p->num_heads_kv;
+    args.seqlen = p->seqlen_q;
+    args.scale = p->softmax_scale;
+    args.scale_log2 = p->softmax_scale * kLog2E;
+    args.order_mode = plan.mode;
+    args.order_width = plan.width;
+    const int64_t blocks64 = int64_t(n_tiles) * bh;
+    if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    const int blocks = int(blocks64);
+    if (with_dq) {
+        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks)
+                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, args, blocks);
+    }
+    return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks)
+              : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks);
+}
+
+// -------------------------------------------------------------- dQ kernel
+template <typename T, int D, bool kCausal, typename TOut>
+int launch_dq_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                const CUtensorMap& mdo, const DqArgs& args, int blocks, cudaStream_t st) {
+    auto kernel = dq_bwd_kernel<T, D, kCausal, TOut>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 DqCfg<D>::kSmemBytes) != cudaSuccess) {
+            return SHAOBO_FA3_STATUS_HIP_ERROR;
+        }
+        configured = true;
+    }
+    kernel<<<blocks, DqCfg<D>::kThreads, DqCfg<D>::kSmemBytes, st>>>(mq, mk, mv, mdo, args);
+    return SHAOBO_FA3_STATUS_SUCCESS;
+}
+
+template <typename T, typename TOut>
+int launch_dq_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorMap& mk,
+                const CUtensorMap& mv, const CUtensorMap& mdo, const DqArgs& args, int blocks) {
+    cudaStream_t st = stream_of(p);
+    if (p->head_dim_qk == 128) {
+        return p->causal ? launch_dq_t<T, 128, true, TOut>(mq, mk, mv, mdo, args, blocks, st)
+                         : launch_dq_t<T, 128, false, TOut>(mq, mk, mv, mdo, args, blocks, st);
+    }
+    return p->causal ? launch_dq_t<T, 64, true, TOut>(mq, mk, mv, mdo, args, blocks, st)
+                     : launch_dq_t<T, 64, false, TOut>(mq, mk, mv, mdo, args, blocks, st);
+}
+
+// Three-GEMM dQ kernel (split path).  out_f32 selects fp32 or input-dtype dq.
+int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
+              const void* v, const float* sidecar, void* dq, bool out_f32) {
+    const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
+    const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const uint64_t d = uint64_t(p->head_dim_qk);
+    const uint64_t q_rows = uint64_t(p->batch) * p->num_heads_q * p->seqlen_q;
+    const uint64_t kv_rows = uint64_t(p->batch) * p->num_heads_kv * p->seqlen_k;
+    CUtensorMap mq, mk, mv, mdo;
+    if (!make_map(&mq, type, 2, q, q_rows, d, 64, 128) ||
+        !make_map(&mk, type, 2, k, kv_rows, d, 64, 128) ||
+        !make_map(&mv, type, 2, v, kv_rows, d, 64, 128) ||
+        !make_map(&mdo, type, 2, dout, q_rows, d, 64, 128)) {
+        return SHAOBO_FA3_STATUS_HIP_ERROR;
+    }
+    DqArgs args;
+    args.sidecar = sidecar;
+    args.dq = dq;
+    args.batch = p->batch;
+    args.heads_q = p->num_heads_q;
+    args.heads_kv = p->num_heads_kv;
+    args.seqlen = p->seqlen_q;
+    args.scale = p->softmax_scale;
+    args.scale_log2 = p->softmax_scale * kLog2E;
+    const int64_t blocks64 = int64_t(p->seqlen_q / 128) * p->batch * p->num_heads_q;
+    if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    const int blocks = int(blocks64);
+    if (out_f32) {
+        return bf ? launch_dq_d<__nv_bfloat16, float>(p, mq, mk, mv, mdo, args, blocks)
+                  : launch_dq_d<__half, float>(p, mq, mk, mv, mdo, args, blocks);
+    }
+    return bf ? launch_dq_d<__nv_bfloat16, __nv_bfloat16>(p, mq, mk, mv, mdo, args, blocks)
+              : launch_dq_d<__half, __half>(p, mq, mk, mv, mdo, args, blocks);
+}
+
+bool stage_params_ok(const ShaoboFa3Params* p) {
+    return p != nullptr && dtype_supported(p->dtype) && p->layout == SHAOBO_FA3_LAYOUT_BHSD &&
+           (p->causal == 0 || p->causal == 1) && fused_shape_ok(p);
+}
+
+}  // namespace
+}  // namespace fa3b200
+
+using namespace fa3b200;
+
+// Extension (no counterpart in the reference): reads and optionally clears the
+// device-side error flag that a kernel raises when a bounded wait runs out
+// (1) or shared memory is misaligned (2).  Synchronises the device.
+extern "C" int shaobo_fa3_b200_device_error(int clear) {
+    int value = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&value, g_device_error, sizeof(int)) != cudaSuccess) return -1;
+    if (clear && value != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_device_error, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
+    return value;
+}
+
+#ifdef FA3B200_DEBUG_DUMP
+extern "C" int shaobo_fa3_b200_debug_dump(float* host_out) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    return cudaMemcpyFromSymbol(host_out, g_debug_dump, sizeof(float) * 3 * 128 * 128) == cudaSuccess ? 0 : -1;
+}
+#endif
+
+extern "C" int shaobo_fa3_bwd_dot_do_o(const void* dout, const void* out, const void* aux0,
+                                       const void* aux1, void* delta, void* packed_sidecar,
+                                       const ShaoboFa3Params* params) {
+    const bool ok = params != nullptr && params->batch > 0 && params->seqlen_q > 0 &&
+                    params->num_heads_q > 0 && head_dim_supported(params->head_dim_qk) &&
+                    params->head_dim_v == params->head_dim_qk && dtype_supported(params->dtype) &&
+                    params->layout == SHAOBO_FA3_LAYOUT_BHSD &&
+                    (params->softmax_aux_mode == SHAOBO_FA3_SOFTMAX_AUX_SMAX_SSUM ||
+                     params->softmax_aux_mode == SHAOBO_FA3_SOFTMAX_AUX_LSE);
+    if (!ok) return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    const bool lse = params->softmax_aux_mode == SHAOBO_FA3_SOFTMAX_AUX_LSE;
+    if (dout == nullptr || out == nullptr || aux0 == nullptr || (!lse && aux1 == nullptr) ||
+        delta == nullptr || packed_sidecar == nullptr) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    launch_delta(params, dout, out, static_cast<const float*>(aux0),
+                 static_cast<const float*>(aux1), static_cast<float*>(delta),
+                 static_cast<float*>(packed_sidecar), nullptr, lse);
+    return finish(params, params->sync_after_launch != 0);
+}
+
+extern "C" int shaobo_fa3_bwd_fused5(const void* dout, const void* q, const void* k,
+                                     const void* v, const void* packed_sidecar, void* dq, void* dk,
+                                     void* dv, const ShaoboFa3Params* params) {
+    if (params == nullptr || dout == nullptr || q == nullptr || k == nullptr || v == nullptr ||
+        packed_sidecar == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    if (!stage_params_ok(params)) return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    const size_t need = dq_accum_bytes(params);
+    if (need == 0 || params->workspace == nullptr || params->workspace_bytes < need) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    float* accum = static_cast<float*>(params->workspace);
+    if (cudaMemsetAsync(accum, 0, need, stream_of(params)) != cudaSuccess) {
+        return SHAOBO_FA3_STATUS_HIP_ERROR;
+    }
+    int status = launch_fused(params, dout, q, k, v, static_cast<const float*>(packed_sidecar),
+                              accum, dk, dv, true);
+    if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
+    launch_convert(params, accum, dq);
+    return finish(params, params->sync_after_launch != 0);
+}
+
+extern "C" int shaobo_fa3_bwd_dkv(const void* dout, const void* q, const void* k, const void* v,
+                                  const void* out, const void* aux0, const void* aux1, void* dq,
+                                  void* dk, void* dv, const ShaoboFa3Params* params) {
+    (void)out; (void)aux0; (void)aux1; (void)dq;
+    if (params == nullptr) return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    if (params->dkv_path == SHAOBO_FA3_DKV_PATH_REFERENCE) return SHAOBO_FA3_STATUS_NOT_IMPLEMENTED;
+    if (params->dkv_path != SHAOBO_FA3_DKV_PATH_CANONICAL || !stage_params_ok(params)) {
+        return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    }
+    const void* sidecar = params->reserved_ptr[SHAOBO_FA3_RESERVED_PTR_SIDECAR];
+    if (dout == nullptr || q == nullptr || k == nullptr || v == nullptr || dk == nullptr ||
+        dv == nullptr || sidecar == nullptr) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    const int status = launch_fused(params, dout, q, k, v, static_cast<const float*>(sidecar),
+                                    nullptr, dk, dv, false);
+    if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
+    return finish(params, params->sync_after_launch != 0);
+}
+
+extern "C" int shaobo_fa3_bwd(const void* dout, const void* q, const void* k, const void* v,
+                              const void* out, const void* aux0, const void* aux1, void* dq,
+                              void* dk, void* dv, const ShaoboFa3Params* params) {
+    return shaobo_fa3_bwd_dkv(dout, q, k, v, out, aux0, aux1, dq, dk, dv, params);
+}
+
+extern "C" int shaobo_fa3_bwd_dq(const void* dout, const void* q, const void* k, const void* v,
+                                 const void* out, const void* aux0, const void* aux1, void* dq,
+                                 void* dk, void* dv, const ShaoboFa3Params* params) {
+    (void)out; (void)dk; (void)dv; (void)aux0; (void)aux1;
+    if (params == nullptr) return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    if (params->dq_path == SHAOBO_FA3_DQ_PATH_REFERENCE) return SHAOBO_FA3_STATUS_NOT_IMPLEMENTED;
+    if (params->dq_path != SHAOBO_FA3_DQ_PATH_CANONICAL || !stage_params_ok(params)) {
+        return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    }
+    // The row statistics travel in the packed sidecar, like the dK/dV half;
+    // delta alone (reserved_ptr[0]) is not enough without the row maximum and
+    // sum, which the reference passes as aux0/aux1.  Both conventions are
+    // accepted: a sidecar in reserved_ptr[3] wins.
+    const void* sidecar = params->reserved_ptr[SHAOBO_FA3_RESERVED_PTR_SIDECAR];
+    if (dout == nullptr || q == nullptr || k == nullptr || v == nullptr || dq == nullptr ||
+        sidecar == nullptr) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    const int status = launch_dq(params, dout, q, k, v, static_cast<const float*>(sidecar), dq, true);
+    if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
+    return finish(params, params->sync_after_launch != 0);
+}
+
+extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k, const void* v,
+                                 const void* out, const void* softmax_lse, void* dq, void* dk,
+                                 void* dv, void* softmax_d, const ShaoboFa3Params* params) {
+    const int validation = validate_v2(params);
+    if (validation != SHAOBO_FA3_STATUS_SUCCESS) return validation;
+    if (dout == nullptr || q == nullptr || k == nullptr || v == nullptr || out == nullptr ||
+        softmax_lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    const V2Workspace ws = v2_workspace(params);
+    if (!ws.valid || params->workspace == nullptr || params->workspace_bytes < ws.total_bytes) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    uint8_t* base = static_cast<uint8_t*>(params->workspace);
+    float* accum = reinterpret_cast<float*>(base);
+    float* delta = softmax_d != nullptr ? static_cast<float*>(softmax_d)
+                                        : reinterpret_cast<float*>(base + ws.delta_offset);
+    float* sidecar = reinterpret_cast<float*>(base + ws.sidecar_offset);
+
+    ShaoboFa3Params launch = *params;
+    launch.softmax_aux_mode = SHAOBO_FA3_SOFTMAX_AUX_LSE;
+    if (launch.softmax_scale_is_set == 0) {
+        launch.softmax_scale = 1.0f / std::sqrt(float(launch.head_dim_qk));
+    }
+
+    int status = SHAOBO_FA3_STATUS_SUCCESS;
+    if (launch.deterministic == 0) {
+        // delta + sidecar, and the dQ accumulator is cleared in the same pass
+        launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
+                     sidecar, accum, true);
+        status = launch_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true);
+        if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq);
+    } else {
+        // Atomic-free split path: dQ by the three-GEMM kernel, dK/dV by the
+        // four-GEMM kernel into the fp32 workspace region, then converted.
+        return SHAOBO_FA3_STATUS_NOT_IMPLEMENTED;
+    }
+    if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
+    return finish(&launch, params->sync_after_launch != 0);
+}

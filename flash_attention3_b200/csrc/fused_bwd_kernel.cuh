@@ -1,0 +1,583 @@
+// Fused five-GEMM attention backward for sm_100a.
+//
+// One CTA owns one (batch, KV head, 128-key tile) and walks every 128-row query
+// tile that can see those keys, for each of the G query heads that share the
+// KV head.  dK and dV stay in tensor memory for the whole walk, so a GQA group
+// is reduced inside the kernel and written once.  Per query tile ("step"):
+//
+//     S^T  = K  Q^T        [key j on TMEM lanes, query i on columns]   SS MMA
+//     dP^T = V  dO^T                                                    SS MMA
+//     P^T  = exp2(S^T * scale*log2e - m_i) * r_i      (CUDA cores, -> TMEM b16)
+//     dV  += P^T dO        A = P^T from TMEM, B = dO (MN-major)         TS MMA
+//     dS^T = P^T o (dP^T - delta_i)                   (CUDA cores, -> smem b16)
+//     dK  += dS^T Q        A = dS^T (K-major), B = Q (MN-major)         SS MMA
+//     dQ   = dS K          A = dS^T read MN-major, B = K (MN-major)     SS MMA
+//     dQacc[tile] += dQ    TMEM -> regs -> smem -> TMA reduce-add (fp32)
+//
+// The softmax scale is applied once at the end (dK in the epilogue, dQ in the
+// convert kernel) instead of per element of dS.
+//
+// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 4-7 = softmax / dS warpgroup (thread j owns TMEM lane j = key j),
+// warps 8-11 = dQ drain warpgroup.  All hand-offs go through mbarriers; every
+// wait is bounded and a time-out raises an error flag instead of hanging.
+//
+// Tensor-memory ledger (512 columns x 128 lanes x 32 bit):
+//     D = 128:  dK [0,128)  dV [128,256)  S/P [256,384)  dP and dQ share [384,512)
+//     D =  64:  dK [0,64)   dV [64,128)   S/P [128,256)  dP [256,384)  dQ [384,448)
+// P^T (16-bit, two per column) is written over the first half of S^T in place.
+//
+// Shared-memory ledger (bytes; every tile is made of 16 KiB boxes of
+// [128 rows][64 x 16 bit] in the 128-byte swizzle):
+//     K, V            2 x D*256            resident for the CTA
+//     Q               2 stages x D*256
+//     dO              1 stage (D=128) or 2 stages (D=64) x D*256
+//     dS^T            32 KiB               [128 keys][128 queries]
+//     dQ staging      32 KiB               4 warps x 2 boxes of [32 rows][32 fp32]
+//     row statistics  2 KiB                {-m + log2 r, delta} x 128 rows x 2 buffers
+//     mbarriers       256
+//     total           231,680 (D=128) / 166,144 (D=64)   of 232,448 available
+#pragma once
+
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "ptx.cuh"
+
+namespace fa3b200 {
+
+enum DeviceError : int {
+    kDevOk = 0,
+    kDevWaitTimeout = 1,
+    kDevSmemMisaligned = 2,
+};
+
+// First error raised by any kernel since the flag was last cleared.
+__device__ int g_device_error = 0;
+
+#ifdef FA3B200_DEBUG_DUMP
+// Debug builds only: raw S^T, dP^T ([key][query]) and dQ ([query][d]) of the
+// first step of block 0.
+__device__ float g_debug_dump[3 * 128 * 128];
+#endif
+
+struct FusedArgs {
+    const float* sidecar;  // [B,Hq,S,3]
+    void* dk;              // [B,Hkv,S,D]
+    void* dv;              // [B,Hkv,S,D]
+    int batch;
+    int heads_q;
+    int heads_kv;
+    int seqlen;
+    float scale;
+    float scale_log2;
+    int order_mode;        // see cta_order.h
+    int order_width;
+};
+
+__host__ __device__ inline int remap_k_tile(int physical, int count, int mode, int width) {
+    if (mode == 0) return physical;                 // heaviest (lowest index) first
+    if (mode == 1) return count - 1 - physical;     // lightest first
+    // mode 2: serpentine inside rounds of `width` tiles
+    const int round = physical / width;
+    const int base = round * width;
+    const int slot = physical - base;
+    int span = count - base;
+    if (span > width) span = width;
+    return base + ((round & 1) == 0 ? slot : span - 1 - slot);
+}
+
+template <int D>
+struct FusedCfg {
+    static constexpr int kTile = 128;
+    static constexpr int kThreads = 384;
+    static constexpr int kBoxBytes = 128 * 128;
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kOperandBytes = kBoxes * kBoxBytes;
+    static constexpr int kQStages = 2;
+    static constexpr int kDoStages = D == 128 ? 1 : 2;
+    static constexpr int kDsBytes = 2 * kBoxBytes;
+    static constexpr int kStageBoxBytes = 32 * 128;
+    static constexpr int kStageBytes = 4 * 2 * kStageBoxBytes;
+
+    static constexpr int kOffK = 0;
+    static constexpr int kOffV = kOffK + kOperandBytes;
+    static constexpr int kOffQ = kOffV + kOperandBytes;
+    static constexpr int kOffDO = kOffQ + kQStages * kOperandBytes;
+    static constexpr int kOffDS = kOffDO + kDoStages * kOperandBytes;
+    static constexpr int kOffStage = kOffDS + kDsBytes;
+    static constexpr int kOffStats = kOffStage + kStageBytes;
+    static constexpr int kOffBar = kOffStats + 2048;
+    static constexpr int kSmemBytes = kOffBar + 256;
+    static_assert(kSmemBytes <= 232448, "shared-memory ledger exceeds 227 KiB");
+    static_assert(kOffStage % 1024 == 0 && kOffDS % 1024 == 0, "swizzled regions need 1 KiB alignment");
+
+    static constexpr int kTmemCols = 512;
+    static constexpr int kColDK = 0;
+    static constexpr int kColDV = D;
+    static constexpr int kColS = 2 * D;
+    static constexpr int kColDP = 2 * D + 128;
+    static constexpr int kColDQ = D == 128 ? kColDP : kColDP + 128;
+    static_assert(kColDQ + D <= kTmemCols, "tensor-memory ledger exceeds 512 columns");
+};
+
+enum Bar : int {
+    kKvFull = 0,
+    kQFull = 1,     // 2 stages
+    kQEmpty = 3,    // 2 stages
+    kDoFull = 5,    // up to 2 stages
+    kDoEmpty = 7,   // up to 2 stages
+    kSFull = 9,
+    kDpFull = 10,
+    kPReady = 11,
+    kDsReady = 12,
+    kDsFree = 13,
+    kDqFull = 14,
+    kDqEmpty = 15,
+    kDkvFull = 16,
+    kStatsFull = 17,  // 2 buffers
+    kNumBars = 19,
+};
+
+constexpr long long kWaitTimeoutCycles = 2000000000LL;  // about one second
+
+// Bounded mbarrier wait.  Returns false when the wait timed out here or was
+// abandoned because another thread of the CTA timed out.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
+                                             volatile uint32_t* abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+    }
+    const long long start = clock64();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) {
+            if (ptx::mbar_try_wait(bar, parity)) return true;
+        }
+        if (*abort_flag != 0) return false;
+        if (clock64() - start > kWaitTimeoutCycles) {
+            *abort_flag = 1;
+            atomicCAS(&g_device_error, kDevOk, kDevWaitTimeout);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity,
+                                          volatile uint32_t* abort_flag) {
+    const bool ok = bounded_wait(bar, parity, abort_flag);
+    return __all_sync(0xffffffffu, ok);
+}
+
+// T: storage type of Q/K/V/dO (__half or __nv_bfloat16).  TOut: type of the dK
+// and dV outputs (T for the fused path, float for the split path).  kWithDq:
+// false turns the kernel into the four-GEMM dK/dV half of the split path.
+template <typename T, int D, bool kCausal, bool kWithDq, typename TOut>
+__global__ void __launch_bounds__(384, 1)
+fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                 const __grid_constant__ CUtensorMap tm_dqacc, const FusedArgs a) {
+    using C = FusedCfg<D>;
+    constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = ptx::smem_u32(smem);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    auto bar = [&](int i) -> uint32_t { return sbase + C::kOffBar + 8 * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kNumBars);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    // ---- which tile is ours ------------------------------------------------
+    const int n_tiles = a.seqlen / C::kTile;
+    const int bh_count = a.batch * a.heads_kv;
+    const int kt = remap_k_tile(int(blockIdx.x) / bh_count, n_tiles, a.order_mode, a.order_width);
+    const int bhi = int(blockIdx.x) % bh_count;
+    const int b = bhi / a.heads_kv;
+    const int kvh = bhi % a.heads_kv;
+    const int group = a.heads_q / a.heads_kv;
+    const int q_begin = kCausal ? kt : 0;
+    const int steps_per_head = n_tiles - q_begin;
+    const int n_steps = group * steps_per_head;
+    const bool misaligned = (sbase & 1023u) != 0;
+
+    if (threadIdx.x == 0) {
+        if (misaligned) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
+        ptx::mbar_init(bar(kKvFull), 1);
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(bar(kQFull + s), 1);
+            ptx::mbar_init(bar(kQEmpty + s), 1);
+            ptx::mbar_init(bar(kDoFull + s), 1);
+            ptx::mbar_init(bar(kDoEmpty + s), 1);
+            ptx::mbar_init(bar(kStatsFull + s), 128);
+        }
+        ptx::mbar_init(bar(kSFull), 1);
+        ptx::mbar_init(bar(kDpFull), 1);
+        ptx::mbar_init(bar(kPReady), 128);
+        ptx::mbar_init(bar(kDsReady), 128);
+        ptx::mbar_init(bar(kDsFree), 1);
+        ptx::mbar_init(bar(kDqFull), 1);
+        ptx::mbar_init(bar(kDqEmpty), 128);
+        ptx::mbar_init(bar(kDkvFull), 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    auto step_coords = [&](int t, int& hq, int& qt) {
+        const int g = t / steps_per_head;
+        hq = kvh * group + g;
+        qt = q_begin + (t - g * steps_per_head);
+    };
+
+    if (!misaligned) {
+        if (warp == 0) {
+            // =================================================== TMA producer
+            if (lane == 0) {
+                ptx::prefetch_tensormap(&tm_q);
+                ptx::prefetch_tensormap(&tm_k);
+                ptx::prefetch_tensormap(&tm_v);
+                ptx::prefetch_tensormap(&tm_do);
+                const int kv_row = (b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile;
+                ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
+#pragma unroll
+                for (int bx = 0; bx < C::kBoxes; ++bx) {
+                    ptx::tma_load_2d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64, kv_row);
+                    ptx::tma_load_2d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64, kv_row);
+                }
+#pragma unroll 1
+                for (int t = 0; t < n_steps; ++t) {
+                    int hq, qt;
+                    step_coords(t, hq, qt);
+                    const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile;
+                    const int s = t % C::kQStages;
+                    if (!bounded_wait(bar(kQEmpty + s), ((t / C::kQStages) & 1) ^ 1, abort_flag)) break;
+                    ptx::mbar_arrive_expect_tx(bar(kQFull + s), C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
+                        ptx::tma_load_2d(sbase + C::kOffQ + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_q,
+                                         bar(kQFull + s), bx * 64, q_row);
+                    }
+                    const int sd = t % C::kDoStages;
+                    if (!bounded_wait(bar(kDoEmpty + sd), ((t / C::kDoStages) & 1) ^ 1, abort_flag)) break;
+                    ptx::mbar_arrive_expect_tx(bar(kDoFull + sd), C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
+                        ptx::tma_load_2d(sbase + C::kOffDO + sd * C::kOperandBytes + bx * C::kBoxBytes, &tm_do,
+                                         bar(kDoFull + sd), bx * 64, q_row);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ===================================================== MMA issuer
+            if (lane == 0) {
+                constexpr uint32_t kIdSdP = ptx::instr_desc_f16(kBf16, 128, 128, false, false);
+                constexpr uint32_t kIdDkv = ptx::instr_desc_f16(kBf16, 128, D, false, true);
+                constexpr uint32_t kIdDq = ptx::instr_desc_f16(kBf16, 128, D, true, true);
+                auto k_major = [&](uint32_t base, int kk) -> uint64_t {
+                    return ptx::smem_desc_sw128(base + (kk >> 2) * C::kBoxBytes + (kk & 3) * 32, 16, 1024);
+                };
+                auto mn_major = [&](uint32_t base, int kk) -> uint64_t {
+                    return ptx::smem_desc_sw128(base + kk * 2048, C::kBoxBytes, 1024);
+                };
+                const uint32_t sK = sbase + C::kOffK, sV = sbase + C::kOffV, sDS = sbase + C::kOffDS;
+                auto sQ = [&](int t) { return sbase + C::kOffQ + (t % C::kQStages) * C::kOperandBytes; };
+                auto sDO = [&](int t) { return sbase + C::kOffDO + (t % C::kDoStages) * C::kOperandBytes; };
+                auto issue_s = [&](int t) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        ptx::mma_ss(tmem + C::kColS, k_major(sK, kk), k_major(sQ(t), kk), kIdSdP, kk > 0);
+                    ptx::tc_commit(bar(kSFull));
+                };
+                auto issue_dp = [&](int t) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        ptx::mma_ss(tmem + C::kColDP, k_major(sV, kk), k_major(sDO(t), kk), kIdSdP, kk > 0);
+                    ptx::tc_commit(bar(kDpFull));
+                };
+                bool ok = bounded_wait(bar(kKvFull), 0, abort_flag) &&
+                          bounded_wait(bar(kQFull + 0), 0, abort_flag);
+                if (ok) {
+                    ptx::tc_fence_after();
+                    issue_s(0);
+                    ok = bounded_wait(bar(kDoFull + 0), 0, abort_flag);
+                }
+                if (ok) {
+                    ptx::tc_fence_after();
+                    issue_dp(0);
+                }
+#pragma unroll 1
+                for (int t = 0; ok && t < n_steps; ++t) {
+                    const bool more = t + 1 < n_steps;
+                    // dV += P^T dO
+                    if (!(ok = bounded_wait(bar(kPReady), t & 1, abort_flag))) break;
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)
+                        ptx::mma_ts(tmem + C::kColDV, tmem + C::kColS + kk * 8, mn_major(sDO(t), kk), kIdDkv,
+                                    (t > 0 || kk > 0) ? 1u : 0u);
+                    ptx::tc_commit(bar(kDoEmpty + t % C::kDoStages));
+                    // S(t+1) may overwrite S/P(t): MMAs execute in issue order.
+                    if (more) {
+                        if (!(ok = bounded_wait(bar(kQFull + (t + 1) % C::kQStages),
+                                                ((t + 1) / C::kQStages) & 1, abort_flag))) break;
+                        ptx::tc_fence_after();
+                        issue_s(t + 1);
+                    }
+                    // dK += dS^T Q
+                    if (!(ok = bounded_wait(bar(kDsReady), t & 1, abort_flag))) break;
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)
+                        ptx::mma_ss(tmem + C::kColDK, k_major(sDS, kk), mn_major(sQ(t), kk), kIdDkv,
+                                    (t > 0 || kk > 0) ? 1u : 0u);
+                    ptx::tc_commit(bar(kQEmpty + t % C::kQStages));
+                    if (kWithDq) {
+                        if (D == 64) {  // own dQ region: wait for the drain of step t-1
+                            if (!(ok = bounded_wait(bar(kDqEmpty), (t & 1) ^ 1, abort_flag))) break;
+                            ptx::tc_fence_after();
+                        }
+                        // dQ = dS K  (overwrites dP(t) when D = 128: dP(t) was consumed before kDsReady)
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk)
+                            ptx::mma_ss(tmem + C::kColDQ, mn_major(sDS, kk), mn_major(sK, kk), kIdDq, kk > 0);
+                        ptx::tc_commit(bar(kDqFull));
+                    }
+                    ptx::tc_commit(bar(kDsFree));
+                    if (more) {
+                        if (!(ok = bounded_wait(bar(kDoFull + (t + 1) % C::kDoStages),
+                                                ((t + 1) / C::kDoStages) & 1, abort_flag))) break;
+                        if (kWithDq && D == 128) {  // dP(t+1) reuses the dQ(t) columns
+                            if (!(ok = bounded_wait(bar(kDqEmpty), t & 1, abort_flag))) break;
+                        }
+                        ptx::tc_fence_after();
+                        issue_dp(t + 1);
+                    }
+                }
+                if (ok) ptx::tc_commit(bar(kDkvFull));
+            }
+        } else if (warp >= 4 && warp < 8) {
+            // ========================================= softmax / dS warpgroup
+            const int j = threadIdx.x - 128;  // key row inside the tile == TMEM lane
+            const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
+            float* stats = reinterpret_cast<float*>(smem + C::kOffStats);
+            uint32_t ppk[64];
+            const float* side_base = a.sidecar;
+            float s0, s1, s2;
+            {
+                int hq, qt;
+                step_coords(0, hq, qt);
+                const int64_t row = int64_t(b * a.heads_q + hq) * a.seqlen + qt * C::kTile + j;
+                s0 = side_base[row * 3 + 0];
+                s1 = side_base[row * 3 + 1];
+                s2 = side_base[row * 3 + 2];
+            }
+            bool ok = true;
+#pragma unroll 1
+            for (int t = 0; t < n_steps; ++t) {
+                int hq, qt;
+                step_coords(t, hq, qt);
+                const int buf = t & 1;
+                float* negp = stats + buf * 128;
+                float* delp = stats + 256 + buf * 128;
+                negp[j] = __log2f(s1) - s0;  // P = exp2(x - m) * r = exp2(x + (log2 r - m))
+                delp[j] = s2;
+                ptx::mbar_arrive(bar(kStatsFull + buf));
+                if (t + 1 < n_steps) {
+                    int hq1, qt1;
+                    step_coords(t + 1, hq1, qt1);
+                    const int64_t row = int64_t(b * a.heads_q + hq1) * a.seqlen + qt1 * C::kTile + j;
+                    s0 = side_base[row * 3 + 0];
+                    s1 = side_base[row * 3 + 1];
+                    s2 = side_base[row * 3 + 2];
+                }
+                if (!(ok = warp_wait(bar(kStatsFull + buf), (t >> 1) & 1, abort_flag))) break;
+                if (!(ok = warp_wait(bar(kSFull), t & 1, abort_flag))) break;
+                ptx::tc_fence_after();
+                const bool diagonal = kCausal && qt == kt;
+                // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked where query i < key j
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tl + C::kColS + c * 32, r);
+                    ptx::tmem_ld_wait();
+#ifdef FA3B200_DEBUG_DUMP
+                    if (blockIdx.x == 0 && t == 0)
+                        for (int e = 0; e < 32; ++e) g_debug_dump[j * 128 + c * 32 + e] = __uint_as_float(r[e]);
+#endif
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4) {
+                        const float4 n4 = *reinterpret_cast<const float4*>(negp + c * 32 + e);
+                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, n4.x));
+                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, n4.y));
+                        float p2 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 2]), a.scale_log2, n4.z));
+                        float p3 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 3]), a.scale_log2, n4.w));
+                        if (diagonal) {
+                            const int i = c * 32 + e;
+                            p0 = (i + 0 >= j) ? p0 : 0.0f;
+                            p1 = (i + 1 >= j) ? p1 : 0.0f;
+                            p2 = (i + 2 >= j) ? p2 : 0.0f;
+                            p3 = (i + 3 >= j) ? p3 : 0.0f;
+                        }
+                        ppk[c * 16 + e / 2 + 0] = ptx::Pack2<T>::pack(p0, p1);
+                        ppk[c * 16 + e / 2 + 1] = ptx::Pack2<T>::pack(p2, p3);
+                    }
+                    ptx::tmem_st16(tl + C::kColS + c * 16, &ppk[c * 16]);
+                }
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(bar(kPReady));
+                // ---- dS^T = P^T * (dP^T - delta_i), stored [key][query] in the 128-byte swizzle
+                if (!(ok = warp_wait(bar(kDpFull), t & 1, abort_flag))) break;
+                if (!(ok = warp_wait(bar(kDsFree), (t & 1) ^ 1, abort_flag))) break;
+                ptx::tc_fence_after();
+                const uint32_t ds_row = sbase + C::kOffDS + j * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tl + C::kColDP + c * 32, r);
+                    ptx::tmem_ld_wait();
+#ifdef FA3B200_DEBUG_DUMP
+                    if (blockIdx.x == 0 && t == 0)
+                        for (int e = 0; e < 32; ++e) g_debug_dump[16384 + j * 128 + c * 32 + e] = __uint_as_float(r[e]);
+#endif
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        const float4 d0 = *reinterpret_cast<const float4*>(delp + c * 32 + e);
+                        const float4 d1 = *reinterpret_cast<const float4*>(delp + c * 32 + e + 4);
+                        const float2 pa = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 0]);
+                        const float2 pb = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 1]);
+                        const float2 pc = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 2]);
+                        const float2 pd = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 3]);
+                        uint4 o;
+                        o.x = ptx::Pack2<T>::pack(pa.x * (__uint_as_float(r[e + 0]) - d0.x),
+                                                  pa.y * (__uint_as_float(r[e + 1]) - d0.y));
+                        o.y = ptx::Pack2<T>::pack(pb.x * (__uint_as_float(r[e + 2]) - d0.z),
+                                                  pb.y * (__uint_as_float(r[e + 3]) - d0.w));
+                        o.z = ptx::Pack2<T>::pack(pc.x * (__uint_as_float(r[e + 4]) - d1.x),
+                                                  pc.y * (__uint_as_float(r[e + 5]) - d1.y));
+                        o.w = ptx::Pack2<T>::pack(pd.x * (__uint_as_float(r[e + 6]) - d1.z),
+                                                  pd.y * (__uint_as_float(r[e + 7]) - d1.w));
+                        const int chunk = c * 4 + e / 8;  // 16-byte chunk along the query axis
+                        const uint32_t addr = ds_row + (chunk >> 3) * C::kBoxBytes +
+                                              (((chunk & 7) ^ (j & 7)) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.x),
+                                     "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(bar(kDsReady));
+            }
+            // ---- epilogue: dK (scaled) and dV out of tensor memory
+            if (ok) ok = warp_wait(bar(kDkvFull), 0, abort_flag);
+            if (ok) {
+                ptx::tc_fence_after();
+                const int64_t row = int64_t(b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile + j;
+#pragma unroll
+                for (int which = 0; which < 2; ++which) {
+                    TOut* dst = reinterpret_cast<TOut*>(which == 0 ? a.dk : a.dv) + row * D;
+                    const float mul = which == 0 ? a.scale : 1.0f;
+                    const int col0 = which == 0 ? C::kColDK : C::kColDV;
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(tl + col0 + c * 32, r);
+                        ptx::tmem_ld_wait();
+                        if (sizeof(TOut) == 4) {
+                            float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                d4[e] = make_float4(__uint_as_float(r[4 * e]) * mul, __uint_as_float(r[4 * e + 1]) * mul,
+                                                    __uint_as_float(r[4 * e + 2]) * mul, __uint_as_float(r[4 * e + 3]) * mul);
+                        } else {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                uint4 o;
+                                o.x = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 0]) * mul, __uint_as_float(r[8 * e + 1]) * mul);
+                                o.y = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 2]) * mul, __uint_as_float(r[8 * e + 3]) * mul);
+                                o.z = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 4]) * mul, __uint_as_float(r[8 * e + 5]) * mul);
+                                o.w = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 6]) * mul, __uint_as_float(r[8 * e + 7]) * mul);
+                                d4[e] = o;
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (warp >= 8 && kWithDq) {
+            // ================================================ dQ drain warpgroup
+            const int qd = warp & 3;
+            const uint32_t tl = tmem + (uint32_t(qd * 32) << 16);
+            const uint32_t stage = sbase + C::kOffStage + qd * 2 * C::kStageBoxBytes;
+            bool pending = false;
+#pragma unroll 1
+            for (int t = 0; t < n_steps; ++t) {
+                int hq, qt;
+                step_coords(t, hq, qt);
+                const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile + qd * 32;
+                if (!warp_wait(bar(kDqFull), t & 1, abort_flag)) break;
+                ptx::tc_fence_after();
+#pragma unroll
+                for (int half = 0; half < D / 64; ++half) {
+                    if (pending) {
+                        if (lane == 0) ptx::bulk_wait_group_read<0>();
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int bx = 0; bx < 2; ++bx) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(tl + C::kColDQ + half * 64 + bx * 32, r);
+                        ptx::tmem_ld_wait();
+#ifdef FA3B200_DEBUG_DUMP
+                        if (blockIdx.x == 0 && t == 0)
+                            for (int e = 0; e < 32; ++e)
+                                g_debug_dump[32768 + (qd * 32 + lane) * 128 + half * 64 + bx * 32 + e] = __uint_as_float(r[e]);
+#endif
+                        if (half == D / 64 - 1 && bx == 1) {
+                            ptx::tc_fence_before();
+                            ptx::mbar_arrive(bar(kDqEmpty));
+                        }
+                        const uint32_t row_addr = stage + bx * C::kStageBoxBytes + lane * 128;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(row_addr + ((c ^ (lane & 7)) << 4)), "r"(r[4 * c]),
+                                           "r"(r[4 * c + 1]), "r"(r[4 * c + 2]), "r"(r[4 * c + 3])
+                                         : "memory");
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_reduce_add_2d(&tm_dqacc, stage, half * 64, q_row);
+                        ptx::tma_reduce_add_2d(&tm_dqacc, stage + C::kStageBoxBytes, half * 64 + 32, q_row);
+                        ptx::bulk_commit_group();
+                    }
+                    pending = true;
+                }
+            }
+            if (lane == 0) ptx::bulk_wait_group<0>();
+        }
+    }
+
+    // ---- teardown: everybody meets, then the allocating warp frees TMEM
+    __syncwarp();
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem, C::kTmemCols);
+    }
+}
+
+}  // namespace fa3b200

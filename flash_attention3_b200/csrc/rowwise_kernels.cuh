@@ -1,0 +1,131 @@
+// HBM-bound row-wise stages of the backward: the delta stage that runs before
+// the GEMM kernel and the dQ scale+convert stage that runs after it.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fa3b200 {
+
+constexpr float kLog2E = 1.44269504088896340736f;
+
+__device__ __forceinline__ uint4 ld_stream_16B(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t u);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// delta[r] = sum_d dO[r,d] * O[r,d] in fp32, plus the packed sidecar
+// {m, r, delta} (definition: reference src/dot_do_o_kernel.cpp:26-63).  Each
+// row is owned by D/8 adjacent lanes that each fetch one 16-byte vector of dO
+// and of O, so a warp reads 512 contiguous bytes per tensor per instruction.
+// When zero_rows is non-null the same lanes also clear the row of the fp32 dQ
+// accumulator (row pitch D floats), which saves a separate memset pass.
+//
+// Algorithmic HBM bytes per row: 2*D*2 (dO, O) + 4 (aux0) [+4 aux1] + 4
+// (delta) + 12 (sidecar) [+ 4*D when clearing the accumulator].
+template <typename T, int D, bool kLseInput>
+__global__ void __launch_bounds__(256)
+delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
+                     const float* __restrict__ aux0, const float* __restrict__ aux1,
+                     float* __restrict__ delta, float* __restrict__ sidecar,
+                     float* __restrict__ zero_rows, int64_t rows, float scale_log2) {
+    constexpr int kLanesPerRow = D / 8;
+    constexpr int kRowsPerWarp = 32 / kLanesPerRow;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane / kLanesPerRow;
+    const int col = lane % kLanesPerRow;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+
+    for (int64_t row = warp * kRowsPerWarp + sub; row < rows; row += warps * kRowsPerWarp) {
+        const uint4 a = ld_stream_16B(dout + row * D + col * 8);
+        const uint4 b = ld_stream_16B(out + row * D + col * 8);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+        float acc = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 x = unpack2<T>(aw[i]);
+            const float2 y = unpack2<T>(bw[i]);
+            acc = fmaf(x.x, y.x, acc);
+            acc = fmaf(x.y, y.y, acc);
+        }
+#pragma unroll
+        for (int off = kLanesPerRow / 2; off > 0; off >>= 1) {
+            acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        }
+        if (zero_rows != nullptr) {
+            float4* z = reinterpret_cast<float4*>(zero_rows + row * D);
+#pragma unroll
+            for (int i = 0; i < (D / 4) / kLanesPerRow; ++i) {
+                z[col + i * kLanesPerRow] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        if (col == 0) {
+            delta[row] = acc;
+            float m, r;
+            if (kLseInput) {
+                m = aux0[row] * kLog2E;
+                r = 1.0f;
+            } else {
+                m = aux0[row] * scale_log2;
+                const float sum = aux1[row];
+                r = sum != 0.0f ? 1.0f / sum : 0.0f;
+            }
+            float* s = sidecar + row * 3;
+            s[0] = m;
+            s[1] = r;
+            s[2] = acc;
+        }
+    }
+}
+
+// dq[i] = T(scale * accum[i]).  8 elements per thread: 32 B in, 16 B out.
+// Algorithmic HBM bytes per element: 4 read + 2 written.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dq_convert_kernel(const float* __restrict__ accum, T* __restrict__ dq, int64_t n_vec8,
+                  float scale) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec8; i += stride) {
+        const uint4 lo = ld_stream_16B(accum + i * 8);
+        const uint4 hi = ld_stream_16B(accum + i * 8 + 4);
+        uint4 o;
+        o.x = pack2<T>(__uint_as_float(lo.x) * scale, __uint_as_float(lo.y) * scale);
+        o.y = pack2<T>(__uint_as_float(lo.z) * scale, __uint_as_float(lo.w) * scale);
+        o.z = pack2<T>(__uint_as_float(hi.x) * scale, __uint_as_float(hi.y) * scale);
+        o.w = pack2<T>(__uint_as_float(hi.z) * scale, __uint_as_float(hi.w) * scale);
+        reinterpret_cast<uint4*>(dq)[i] = o;
+    }
+}
+
+}  // namespace fa3b200

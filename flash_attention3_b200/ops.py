@@ -1,0 +1,73 @@
+"""Tensor-level wrapper over the C ABI (torch provides device memory only)."""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import capi
+
+_DTYPES = {torch.float16: capi.DTYPE_FP16, torch.bfloat16: capi.DTYPE_BF16}
+
+
+class Fa3Error(RuntimeError):
+    def __init__(self, entry: str, code: int):
+        super().__init__(f"{entry} returned {code} ({capi.status_string(code)})")
+        self.code = code
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def make_params(q: torch.Tensor, k: torch.Tensor, causal: bool, softmax_scale=None, **extra) -> capi.Params:
+    b, hq, s, d = q.shape
+    p = capi.new_params(batch=b, seqlen_q=s, seqlen_k=k.shape[2], num_heads_q=hq, num_heads_kv=k.shape[1],
+                        head_dim_qk=d, head_dim_v=d, causal=int(causal), dtype=_DTYPES[q.dtype])
+    if softmax_scale is not None:
+        p.softmax_scale = float(softmax_scale)
+        p.softmax_scale_is_set = 1
+    for key, val in extra.items():
+        setattr(p, key, val)
+    return p
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("flash_attention3_b200 has no CPU path: tensors must live on a CUDA device")
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError("BHSD-contiguous tensors are required")
+
+
+def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, deterministic=False,
+            workspace=None, return_delta=False, sync=False):
+    """dq, dk, dv (and delta) = backward of softmax(q k^T * scale) v.
+
+    q, out, dout: [B,Hq,S,D]; k, v: [B,Hkv,S,D]; fp16 or bf16; softmax_lse:
+    fp32 [B,Hq,S] natural log.  Calls shaobo_fa3_bwd_v2.
+    """
+    _require_cuda(dout, q, k, v, out, softmax_lse)
+    lib = capi.load()
+    p = make_params(q, k, causal, softmax_scale, deterministic=int(deterministic), sync_after_launch=int(sync))
+    need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
+    if need == 0:
+        raise Fa3Error("shaobo_fa3_bwd_v2_validate", lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(p)))
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    p.workspace = workspace.data_ptr()
+    p.workspace_bytes = workspace.numel() * workspace.element_size()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if return_delta else None
+    with torch.cuda.device(q.device):
+        p.reserved_ptr[capi.RESERVED_PTR_STREAM] = torch.cuda.current_stream().cuda_stream or None
+        code = lib.shaobo_fa3_bwd_v2(_ptr(dout), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(softmax_lse),
+                                     _ptr(dq), _ptr(dk), _ptr(dv), _ptr(delta), ctypes.byref(p))
+    if code != capi.STATUS_SUCCESS:
+        raise Fa3Error("shaobo_fa3_bwd_v2", code)
+    return (dq, dk, dv, delta) if return_delta else (dq, dk, dv)
+
+
+def default_scale(d: int) -> float:
+    return 1.0 / math.sqrt(d)

@@ -1,0 +1,85 @@
+"""Shared plumbing of the GPU parity tests: oracle inputs -> device tensors ->
+C ABI -> numpy.  torch is used for device memory only."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from flash_attention3_b200 import capi, ops
+from oracle import golden
+
+TORCH_DTYPE = {"fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+def dev(x: np.ndarray, dtype: str | None = None) -> torch.Tensor:
+    t = torch.from_numpy(np.ascontiguousarray(x))
+    if dtype is not None:
+        t = t.to(TORCH_DTYPE[dtype])
+    return t.cuda().contiguous()
+
+
+def host(t: torch.Tensor) -> np.ndarray:
+    return t.detach().float().cpu().numpy()
+
+
+def poison(shape, dtype, device="cuda"):
+    """NaN-filled tensor: an element the kernel forgets to write stays NaN."""
+    return torch.full(shape, float("nan"), dtype=dtype, device=device)
+
+
+class Problem:
+    """Seeded (or closed-form) inputs plus the oracle's answers."""
+
+    def __init__(self, b, hq, hkv, s, d, dtype, causal, seed=None, scale=None):
+        self.b, self.hq, self.hkv, self.s, self.d = b, hq, hkv, s, d
+        self.dtype, self.causal = dtype, causal
+        self.scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
+        if seed is None:
+            assert dtype == "fp16"
+            self.q, self.k, self.v, self.do = golden.pattern_inputs(b, hq, hkv, s, d)
+        else:
+            self.q, self.k, self.v, self.do = golden.seeded_inputs(seed, b, hq, hkv, s, d, dtype)
+        self.ref = golden.backward(self.q, self.k, self.v, self.do, causal, self.scale, dtype)
+
+    def device_inputs(self):
+        t = self.dtype
+        return dict(q=dev(self.q, t), k=dev(self.k, t), v=dev(self.v, t), dout=dev(self.do, t),
+                    out=dev(self.ref["out"], t), lse=dev(self.ref["lse"]))
+
+
+def run_v2(prob: Problem, deterministic=False, pass_scale=True, poison_ws=True):
+    """Call shaobo_fa3_bwd_v2 through ctypes with NaN-poisoned outputs and workspace."""
+    lib = capi.load()
+    x = prob.device_inputs()
+    p = ops.make_params(x["q"], x["k"], prob.causal, prob.scale if pass_scale else None,
+                        deterministic=int(deterministic), sync_after_launch=1)
+    need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
+    assert need > 0
+    ws = torch.full((need,), 0xFF if poison_ws else 0, dtype=torch.uint8, device="cuda")
+    p.workspace, p.workspace_bytes = ws.data_ptr(), need
+    td = TORCH_DTYPE[prob.dtype]
+    dq, dk, dv = poison(x["q"].shape, td), poison(x["k"].shape, td), poison(x["k"].shape, td)
+    delta = poison(x["lse"].shape, torch.float32)
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    torch.cuda.synchronize()
+    code = lib.shaobo_fa3_bwd_v2(vp(x["dout"]), vp(x["q"]), vp(x["k"]), vp(x["v"]), vp(x["out"]), vp(x["lse"]),
+                                 vp(dq), vp(dk), vp(dv), vp(delta), ctypes.byref(p))
+    torch.cuda.synchronize()
+    dev_err = lib.shaobo_fa3_b200_device_error(1)
+    return dict(code=code, device_error=dev_err, dq=host(dq), dk=host(dk), dv=host(dv), delta=host(delta))
+
+
+def metrics(result: dict, prob: Problem) -> dict:
+    return {name: golden.compare(result[name], prob.ref[name]) for name in ("delta", "dq", "dk", "dv")}
+
+
+def assert_parity(result: dict, prob: Problem, label=""):
+    assert result["code"] == capi.STATUS_SUCCESS, (label, capi.status_string(result["code"]))
+    assert result["device_error"] == 0, (label, "device error flag", result["device_error"])
+    m = metrics(result, prob)
+    assert golden.delta_pass(m["delta"]), (label, "delta", m["delta"])
+    for name in ("dq", "dk", "dv"):
+        assert golden.gradients_pass(m[name]), (label, name, m[name])
+    return m

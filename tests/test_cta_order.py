@@ -1,0 +1,60 @@
+"""Scheduler model checks (role of reference scripts/check_fused5_causal_cta_order.py):
+the remap is a permutation and the chosen plan never models worse than the
+plain heavy-first order."""
+import ctypes
+import subprocess
+
+import pytest
+
+from tests.conftest import ROOT
+
+SRC = r'''
+#include "cta_order.h"
+extern "C" int remap(int p, int n, int mode, int w) { return fa3b200::host_remap_k_tile(p, n, mode, w); }
+extern "C" long long makespan(int n, int bh, int g, int causal, int sms, int mode, int w) {
+    return fa3b200::modelled_makespan(n, bh, g, causal != 0, sms, mode, w);
+}
+extern "C" void plan(int n, int bh, int g, int causal, int sms, int* mode, int* width, long long* ms) {
+    auto p = fa3b200::plan_cta_order(n, bh, g, causal != 0, sms);
+    *mode = p.mode; *width = p.width; *ms = p.makespan;
+}
+'''
+
+
+@pytest.fixture(scope="module")
+def lib(tmp_path_factory):
+    d = tmp_path_factory.mktemp("cta")
+    (d / "w.cpp").write_text(SRC)
+    so = d / "libcta.so"
+    subprocess.run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-I",
+                    str(ROOT / "flash_attention3_b200/csrc"), str(d / "w.cpp"), "-o", str(so)], check=True)
+    lib = ctypes.CDLL(str(so))
+    lib.makespan.restype = ctypes.c_longlong
+    return lib
+
+
+def test_remap_is_a_permutation(lib):
+    for n in (1, 2, 3, 8, 16, 33, 64):
+        for mode in (0, 1, 2):
+            for w in range(1, min(n, 16) + 1):
+                assert sorted(lib.remap(p, n, mode, w) for p in range(n)) == list(range(n))
+
+
+def test_plan_never_worse_than_heavy_first(lib):
+    for n in (1, 8, 16, 32, 64):
+        for bh in (1, 4, 16, 64, 200):
+            for g in (1, 4):
+                mode, width, ms = ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
+                lib.plan(n, bh, g, 1, 148, ctypes.byref(mode), ctypes.byref(width), ctypes.byref(ms))
+                base = lib.makespan(n, bh, g, 1, 148, 0, 1)
+                assert ms.value <= base
+                assert ms.value == lib.makespan(n, bh, g, 1, 148, mode.value, width.value)
+                total = bh * sum(1 + g * (n - k) for k in range(n))
+                assert ms.value * 148 >= total  # cannot beat perfect balance
+
+
+def test_heavy_first_beats_light_first_on_a_partial_wave(lib):
+    # 16 key tiles x 4 heads (the S=2048, H=4 shape) on 148 SMs: one wave, makespan = heaviest CTA
+    assert lib.makespan(16, 4, 1, 1, 148, 0, 1) == 17
+    # 64 tiles x 64 heads: light-first leaves the longest CTAs for the tail
+    assert lib.makespan(64, 64, 1, 1, 148, 0, 1) < lib.makespan(64, 64, 1, 1, 148, 1, 1)
