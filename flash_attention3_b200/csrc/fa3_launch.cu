@@ -86,6 +86,28 @@ CtaOrderPlan cached_plan(int n_tiles, int bh, int group, bool causal, int sms) {
     return plan;
 }
 
+// Remembers, per CUDA device, that a one-time set-up step has been done
+// (function attributes are per device).
+struct DeviceOnce {
+    std::mutex mu;
+    uint64_t mask[2] = {0, 0};
+    static int device() {
+        int d = 0;
+        cudaGetDevice(&d);
+        return d & 127;
+    }
+    bool done() {
+        const int d = device();
+        std::lock_guard<std::mutex> lock(mu);
+        return (mask[d >> 6] >> (d & 63)) & 1;
+    }
+    void mark() {
+        const int d = device();
+        std::lock_guard<std::mutex> lock(mu);
+        mask[d >> 6] |= uint64_t(1) << (d & 63);
+    }
+};
+
 int finish(const ShaoboFa3Params* p, bool sync) {
     if (cudaGetLastError() != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
     if (sync && cudaStreamSynchronize(stream_of(p)) != cudaSuccess) {
@@ -151,13 +173,13 @@ int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
                    const CUtensorMap& mdo, const CUtensorMap& mdq, const FusedArgs& args,
                    int blocks, cudaStream_t st) {
     auto kernel = fused_bwd_kernel<T, D, kCausal, kWithDq, TOut>;
-    static bool configured = false;  // per instantiation
-    if (!configured) {
+    static DeviceOnce configured;  // per instantiation and device
+    if (!configured.done()) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  FusedCfg<D>::kSmemBytes) != cudaSuccess) {
             return SHAOBO_FA3_STATUS_HIP_ERROR;
         }
-        configured = true;
+        configured.mark();
     }
     kernel<<<blocks, FusedCfg<D>::kThreads, FusedCfg<D>::kSmemBytes, st>>>(mq, mk, mv, mdo, mdq, args);
     return SHAOBO_FA3_STATUS_SUCCESS;
@@ -181,7 +203,7 @@ int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtens
 // outputs (split path).
 int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
                  const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
-                 bool with_dq) {
+                 bool with_dq, bool dkv_f32 = false) {
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const uint64_t d = uint64_t(p->head_dim_qk);
@@ -224,8 +246,12 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
         return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks)
                   : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, args, blocks);
     }
-    return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks)
-              : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks);
+    if (dkv_f32) {
+        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks)
+                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks);
+    }
+    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks)
+              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, args, blocks);
 }
 
 // -------------------------------------------------------------- dQ kernel
@@ -233,13 +259,13 @@ template <typename T, int D, bool kCausal, typename TOut>
 int launch_dq_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                 const CUtensorMap& mdo, const DqArgs& args, int blocks, cudaStream_t st) {
     auto kernel = dq_bwd_kernel<T, D, kCausal, TOut>;
-    static bool configured = false;
-    if (!configured) {
+    static DeviceOnce configured;
+    if (!configured.done()) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  DqCfg<D>::kSmemBytes) != cudaSuccess) {
             return SHAOBO_FA3_STATUS_HIP_ERROR;
         }
-        configured = true;
+        configured.mark();
     }
     kernel<<<blocks, DqCfg<D>::kThreads, DqCfg<D>::kSmemBytes, st>>>(mq, mk, mv, mdo, args);
     return SHAOBO_FA3_STATUS_SUCCESS;
@@ -382,7 +408,7 @@ extern "C" int shaobo_fa3_bwd_dkv(const void* dout, const void* q, const void* k
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     const int status = launch_fused(params, dout, q, k, v, static_cast<const float*>(sidecar),
-                                    nullptr, dk, dv, false);
+                                    nullptr, dk, dv, false, true);
     if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
     return finish(params, params->sync_after_launch != 0);
 }
@@ -449,9 +475,14 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
         status = launch_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true);
         if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq);
     } else {
-        // Atomic-free split path: dQ by the three-GEMM kernel, dK/dV by the
-        // four-GEMM kernel into the fp32 workspace region, then converted.
-        return SHAOBO_FA3_STATUS_NOT_IMPLEMENTED;
+        // Atomic-free split path (bitwise reproducible): dK/dV by the four-GEMM
+        // kernel, dQ by the three-GEMM kernel; both write the input dtype directly.
+        launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
+                     sidecar, nullptr, true);
+        status = launch_fused(&launch, dout, q, k, v, sidecar, nullptr, dk, dv, false, false);
+        if (status == SHAOBO_FA3_STATUS_SUCCESS) {
+            status = launch_dq(&launch, dout, q, k, v, sidecar, dq, false);
+        }
     }
     if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
     return finish(&launch, params->sync_after_launch != 0);
