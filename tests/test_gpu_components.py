@@ -100,7 +100,7 @@ def _run_split(prob):
 def test_split_path_components_fp32_outputs(dtype, d, hq, hkv, s, causal):
     prob = helpers.Problem(1, hq, hkv, s, d, dtype, causal, seed=41 + s)
     r = _run_split(prob)
-    m = helpers.assert_parity(r, prob)
+    m = helpers.assert_parity(r, prob, out_dtype=None)
     # fp32 outputs: no output rounding, so the split path is tighter than the gates
     for name in ("dq", "dk", "dv"):
         assert m[name]["rel_l2"] <= 4e-3
