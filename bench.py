@@ -1,0 +1,373 @@
+#!/usr/bin/env python3
+"""Benchmark of the FlashAttention-3 backward hot path (shaobo_fa3_bwd_v2).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C2] [--impl reference]
+
+A step is one shaobo_fa3_bwd_v2 call (delta -> fused five-GEMM kernel -> dQ
+convert) over one synthetic batch.  The default workload is B=1, H=4, S=2048,
+D=128, causal, fp16 per GPU; with N GPUs every rank runs the same workload on
+its own batch shard (global batch N, no collective on the data path), so
+scaling is weak.  Rank 0 prints one JSON line.
+
+Keys beyond the base contract:
+  roofline      five-GEMM kernel: algorithmic FLOPs / CUDA-event time of that
+                kernel alone (stage events recorded by the library) against
+                the measured dense bf16 peak
+  cpu_baseline  the CPU oracle (NumPy restatement of the reference golden)
+                timed on this host on the same workload
+  e2e           the same call with host (pinned) inputs and outputs: H2D copies,
+                the call, D2H copies, all inside the timed region
+  also          TFLOP/s of the larger configurations (N=1 only, informative)
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import pathlib
+import statistics
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONFIGS = {
+    # name: (batch, heads_q, heads_kv, seqlen, head_dim, dtype, causal, description)
+    "C1": (1, 1, 1, 1024, 128, "fp16", True, "B=1,H=1,S=1024,D=128 causal fp16"),
+    "C2": (1, 4, 4, 2048, 128, "fp16", True, "B=1,H=4,S=2048,D=128 causal fp16"),
+    "C3d128": (4, 16, 16, 4096, 128, "bf16", False, "B=4,H=16,S=4096,D=128 non-causal bf16"),
+    "C3d64": (4, 16, 16, 4096, 64, "bf16", False, "B=4,H=16,S=4096,D=64 non-causal bf16"),
+    "C4": (2, 32, 8, 8192, 128, "bf16", True, "B=2,Hq=32,Hkv=8,S=8192,D=128 causal bf16 (GQA)"),
+    "C5shard": (2, 32, 32, 8192, 128, "bf16", True, "B=2 of 16,H=32,S=8192,D=128 causal bf16 (1/8 shard)"),
+    # profiler-sized case: ~0.2 GB on the device, working set above the 126 MB L2
+    "P1": (1, 16, 16, 4096, 128, "bf16", False, "B=1,H=16,S=4096,D=128 non-causal bf16 (profiling case)"),
+    "P2": (1, 16, 16, 4096, 128, "bf16", True, "B=1,H=16,S=4096,D=128 causal bf16 (profiling case)"),
+}
+METRIC = "fa3_bwd_tflops"
+UNIT = "TFLOP/s"
+L2_FLUSH_BYTES = 256 << 20  # larger than the 126 MB L2
+
+
+def bwd_flops(b, hq, s, d, causal):
+    f = 10.0 * b * hq * float(s) * float(s) * d
+    return f / 2 if causal else f
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return {"tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"],
+                "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"tflops_burst": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------
+# clocks: sampled with NVML while the timed region runs
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the oracle port timed on the host cores
+# ----------------------------------------------------------------------------
+def cpu_golden_rate(cfg, min_seconds, max_reps):
+    """TFLOP/s of the NumPy golden on (a bounded sample of) the workload."""
+    import numpy as np
+    from oracle import golden
+    b, hq, hkv, s, d, dtype, causal, _ = cfg
+    heads = min(b * hq, 4)  # bounded sample: at most four (batch, head) slices per repetition
+    q, k, v, do = golden.seeded_inputs(4321, 1, heads, max(1, heads * hkv // hq), s, d, dtype)
+    group = heads // k.shape[1]
+    scale = 1.0 / float(np.sqrt(d))
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        for h in range(heads):
+            golden.head_backward(q[0, h], k[0, h // group], v[0, h // group], do[0, h], causal, scale, dtype)
+        reps += 1
+        elapsed = time.perf_counter() - t0
+        if elapsed >= min_seconds or reps >= max_reps:
+            break
+    flops = bwd_flops(1, heads, s, d, causal) * reps
+    return {"value": flops / elapsed / 1e12, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{heads} (batch,head) slices of the workload x {reps} repetitions, {elapsed:.1f} s, "
+                      f"NumPy/BLAS on all host threads; the golden computes the full SxS matrix even when causal"}
+
+
+def run_reference_arm(args, cfg, rank, world):
+    if rank != 0:
+        return
+    b, hq, hkv, s, d, dtype, causal, desc = cfg
+    times = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        base = cpu_golden_rate(cfg, 0.0, 1)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    ms = 1e3 * sum(times) / len(times)
+    heads = min(b * hq, 4)
+    value = bwd_flops(1, heads, s, d, causal) / (ms * 1e-3) / 1e12
+    base.update({"value": value, "sample": f"each step = {heads} (batch,head) slices of the workload through the "
+                                             "NumPy golden (oracle port of the reference's CPU path)"})
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": desc + " per GPU", "l2": "n/a (CPU)"},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+class Workload:
+    def __init__(self, cfg, seed, torch, capi, ops, synthetic):
+        self.torch, self.capi = torch, capi
+        b, hq, hkv, s, d, dtype, causal, _ = cfg
+        self.cfg = cfg
+        td = torch.float16 if dtype == "fp16" else torch.bfloat16
+        self.q, self.k, self.v, self.do = synthetic.make_inputs(seed, b, hq, hkv, s, d, td)
+        self.out, self.lse = synthetic.forward_reference(self.q, self.k, self.v, causal)
+        self.lib = capi.load()
+        self.p = ops.make_params(self.q, self.k, causal)
+        need = self.lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(self.p))
+        self.ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        self.p.workspace, self.p.workspace_bytes = self.ws.data_ptr(), need
+        self.dq, self.dk, self.dv = torch.empty_like(self.q), torch.empty_like(self.k), torch.empty_like(self.v)
+        self.flops = bwd_flops(b, hq, s, d, causal)
+
+    def step(self):
+        vp = lambda t: ctypes.c_void_p(t.data_ptr())
+        code = self.lib.shaobo_fa3_bwd_v2(vp(self.do), vp(self.q), vp(self.k), vp(self.v), vp(self.out),
+                                          vp(self.lse), vp(self.dq), vp(self.dk), vp(self.dv), None,
+                                          ctypes.byref(self.p))
+        if code != 0:
+            raise RuntimeError(f"shaobo_fa3_bwd_v2 returned {code} ({self.capi.status_string(code)})")
+
+
+def time_steps(torch, wl, steps, warmup, flush):
+    """Per-step CUDA-event timing with an L2 flush (untimed) before every step."""
+    for _ in range(warmup):
+        flush.zero_()
+        wl.step()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush.zero_()
+        starts[i].record()
+        wl.step()
+        ends[i].record()
+    torch.cuda.synchronize()
+    return [starts[i].elapsed_time(ends[i]) for i in range(steps)]
+
+
+def time_stages(torch, wl, steps, flush):
+    """CUDA-event time of each of the three launches, averaged over `steps` calls."""
+    lib = wl.lib
+    lib.shaobo_fa3_b200_stage_timing(1)
+    acc = [0.0, 0.0, 0.0]
+    buf = (ctypes.c_float * 3)()
+    for _ in range(steps):
+        flush.zero_()
+        wl.step()
+        if lib.shaobo_fa3_b200_last_stage_ms(buf) != 0:
+            raise RuntimeError("stage timing unavailable")
+        for i in range(3):
+            acc[i] += buf[i]
+    lib.shaobo_fa3_b200_stage_timing(0)
+    return [a / steps for a in acc]
+
+
+def time_e2e(torch, wl, steps, warmup, flush):
+    """Host buffers in, host buffers out: pinned H2D of every input, the call, D2H of dq/dk/dv."""
+    dev_in = [wl.q, wl.k, wl.v, wl.do, wl.out, wl.lse]
+    host_in = [t.cpu().pin_memory() for t in dev_in]
+    dev_out = [wl.dq, wl.dk, wl.dv]
+    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in dev_out]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def one():
+        for h, d in zip(host_in, dev_in):
+            d.copy_(h, non_blocking=True)
+        wl.step()
+        for h, d in zip(host_out, dev_out):
+            h.copy_(d, non_blocking=True)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(steps):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        one()
+        e.record()
+        e.synchronize()
+        times.append(s.elapsed_time(e))
+    return times, h2d, d2h
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="C2", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip cpu_baseline, e2e and the 'also' configurations")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    cfg = CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, rank, world)
+        return
+
+    import torch
+    from flash_attention3_b200 import capi, ops, synthetic
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    b, hq, hkv, s, d, dtype, causal, desc = cfg
+    wl = Workload(cfg, 1234 + rank, torch, capi, ops, synthetic)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        times = time_steps(torch, wl, args.steps, args.warmup, flush)
+        barrier()
+    dev_err = wl.lib.shaobo_fa3_b200_device_error(1)
+    if dev_err != 0:
+        raise SystemExit(f"device error flag {dev_err}")
+    total_ms = sum(times)
+    if dist is not None:
+        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * wl.flops / (ms_per_step * 1e-3) / 1e12
+
+    stage_ms = time_stages(torch, wl, min(args.steps, 20), flush)
+    peaks = measured_peaks()
+    achieved = wl.flops / (stage_ms[1] * 1e-3) / 1e12
+    traffic = None
+    tpath = ROOT / "profiles" / "dram_traffic.json"
+    if tpath.exists():
+        traffic = json.loads(tpath.read_text()).get(args.config, {}).get("fused_bwd_kernel")
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["tflops_burst"], "traffic": traffic,
+                "kernel": "fused_bwd_kernel (S, dP, dV, dK, dQ)", "peak_source": peaks["source"] + " (burst bf16 GEMM)",
+                "kernel_ms": stage_ms[1],
+                "other_kernels_ms": {"delta_sidecar_kernel": stage_ms[0], "dq_convert_kernel": stage_ms[2]}}
+
+    e2e_times, h2d, d2h = time_e2e(torch, wl, max(3, min(args.steps, 20)), 3, flush)
+    e2e_ms = sum(e2e_times) / len(e2e_times)
+    if dist is not None:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e = {"value": world * wl.flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": desc + " per GPU", "global_batch": b * world, "sharding": "batch (no collective)",
+                   "l2": f"flushed before every step ({L2_FLUSH_BYTES >> 20} MiB write, untimed)",
+                   "frac_of_measured_peak": value / world / peaks["tflops_burst"],
+                   "frac_of_nominal_2250": value / world / 2250.0},
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": 3 * args.steps, "roofline": roofline,
+    }
+    if rank == 0 and world == 1 and not args.no_extra:
+        line["cpu_baseline"] = cpu_golden_rate(cfg, 10.0, 50)
+        also = {}
+        del wl
+        torch.cuda.empty_cache()
+        for name in ("C3d128", "C3d64", "C4", "C5shard"):
+            if name == args.config:
+                continue
+            w2 = Workload(CONFIGS[name], 77, torch, capi, ops, synthetic)
+            t2 = time_steps(torch, w2, 10, 3, flush)
+            ms = statistics.median(t2)
+            also[name] = {"ms_per_step": ms, "tflops": w2.flops / (ms * 1e-3) / 1e12,
+                          "workload": CONFIGS[name][7]}
+            del w2
+            torch.cuda.empty_cache()
+        line["also"] = also
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

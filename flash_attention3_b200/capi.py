@@ -55,7 +55,7 @@ class Capabilities(ctypes.Structure):
     ]
 
 
-# every symbol the two headers declare, plus the one extension
+# every symbol the headers under include/ declare
 EXPORTS = [
     "shaobo_fa3_params_init", "shaobo_fa3_bwd_get_capabilities", "shaobo_fa3_bwd_v2_validate",
     "shaobo_fa3_bwd_v2_workspace_bytes", "shaobo_fa3_bwd_v2", "shaobo_fa3_status_string",
@@ -63,6 +63,8 @@ EXPORTS = [
     "shaobo_fa3_bwd_dot_do_o", "shaobo_fa3_bwd_fused5_workspace_bytes", "shaobo_fa3_bwd_fused5",
     "shaobo_fa3_bwd_dkv_workspace_bytes", "shaobo_fa3_bwd_dkv",
     "shaobo_fa3_bwd_dq_workspace_bytes", "shaobo_fa3_bwd_dq",
+    # include/shaobo_fa3_b200_ext.h
+    "shaobo_fa3_b200_device_error", "shaobo_fa3_b200_stage_timing", "shaobo_fa3_b200_last_stage_ms",
 ]
 
 _lib = None
@@ -105,6 +107,10 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.shaobo_fa3_status_string.restype = ctypes.c_char_p
     lib.shaobo_fa3_b200_device_error.argtypes = [ctypes.c_int]
     lib.shaobo_fa3_b200_device_error.restype = ctypes.c_int
+    lib.shaobo_fa3_b200_stage_timing.argtypes = [ctypes.c_int]
+    lib.shaobo_fa3_b200_stage_timing.restype = ctypes.c_int
+    lib.shaobo_fa3_b200_last_stage_ms.argtypes = [ctypes.POINTER(ctypes.c_float)]
+    lib.shaobo_fa3_b200_last_stage_ms.restype = ctypes.c_int
     _lib = lib
     return lib
 

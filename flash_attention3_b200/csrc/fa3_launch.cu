@@ -17,6 +17,7 @@
 #include "fused_bwd_kernel.cuh"
 #include "dq_kernel.cuh"
 #include "rowwise_kernels.cuh"
+#include "shaobo_fa3_b200_ext.h"
 #include "shaobo_fa3_components.h"
 
 namespace fa3b200 {
@@ -107,6 +108,22 @@ struct DeviceOnce {
         mask[d >> 6] |= uint64_t(1) << (d & 63);
     }
 };
+
+// Optional per-stage timing of shaobo_fa3_bwd_v2 (off by default): when
+// enabled, four events bracket the three launches of a call on its stream.
+struct StageTimer {
+    bool enabled = false;
+    bool valid = false;
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+};
+StageTimer g_stage_timer;
+
+void stage_mark(int i, cudaStream_t st) {
+    if (g_stage_timer.enabled && g_stage_timer.ev[i] != nullptr) {
+        cudaEventRecord(g_stage_timer.ev[i], st);
+        if (i == 3) g_stage_timer.valid = true;
+    }
+}
 
 int finish(const ShaoboFa3Params* p, bool sync) {
     if (cudaGetLastError() != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
@@ -342,6 +359,43 @@ extern "C" int shaobo_fa3_b200_device_error(int clear) {
     return value;
 }
 
+// Extension (no counterpart in the reference): per-stage device timing of
+// shaobo_fa3_bwd_v2 for benchmarking.  enable != 0 creates four CUDA events on
+// the current device and makes every following v2 call record them around its
+// three launches; enable == 0 stops recording and destroys them.
+extern "C" int shaobo_fa3_b200_stage_timing(int enable) {
+    if (enable != 0 && !g_stage_timer.enabled) {
+        for (auto& e : g_stage_timer.ev) {
+            if (cudaEventCreate(&e) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
+        }
+        g_stage_timer.enabled = true;
+        g_stage_timer.valid = false;
+    } else if (enable == 0 && g_stage_timer.enabled) {
+        g_stage_timer.enabled = false;
+        for (auto& e : g_stage_timer.ev) {
+            cudaEventDestroy(e);
+            e = nullptr;
+        }
+    }
+    return SHAOBO_FA3_STATUS_SUCCESS;
+}
+
+// Milliseconds of the three stages of the last timed v2 call (waits for it):
+// fused path {delta, five-GEMM kernel, dQ convert}; deterministic path
+// {delta, dK/dV kernel, dQ kernel}.
+extern "C" int shaobo_fa3_b200_last_stage_ms(float* ms3) {
+    if (!g_stage_timer.enabled || !g_stage_timer.valid || ms3 == nullptr) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    if (cudaEventSynchronize(g_stage_timer.ev[3]) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
+    for (int i = 0; i < 3; ++i) {
+        if (cudaEventElapsedTime(&ms3[i], g_stage_timer.ev[i], g_stage_timer.ev[i + 1]) != cudaSuccess) {
+            return SHAOBO_FA3_STATUS_HIP_ERROR;
+        }
+    }
+    return SHAOBO_FA3_STATUS_SUCCESS;
+}
+
 #ifdef FA3B200_DEBUG_DUMP
 extern "C" int shaobo_fa3_b200_debug_dump(float* host_out) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
@@ -470,19 +524,29 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
     int status = SHAOBO_FA3_STATUS_SUCCESS;
     if (launch.deterministic == 0) {
         // delta + sidecar, and the dQ accumulator is cleared in the same pass
+        cudaStream_t st = stream_of(&launch);
+        stage_mark(0, st);
         launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
                      sidecar, accum, true);
+        stage_mark(1, st);
         status = launch_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true);
+        stage_mark(2, st);
         if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq);
+        stage_mark(3, st);
     } else {
         // Atomic-free split path (bitwise reproducible): dK/dV by the four-GEMM
         // kernel, dQ by the three-GEMM kernel; both write the input dtype directly.
+        cudaStream_t st = stream_of(&launch);
+        stage_mark(0, st);
         launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
                      sidecar, nullptr, true);
+        stage_mark(1, st);
         status = launch_fused(&launch, dout, q, k, v, sidecar, nullptr, dk, dv, false, false);
+        stage_mark(2, st);
         if (status == SHAOBO_FA3_STATUS_SUCCESS) {
             status = launch_dq(&launch, dout, q, k, v, sidecar, dq, false);
         }
+        stage_mark(3, st);
     }
     if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
     return finish(&launch, params->sync_after_launch != 0);
