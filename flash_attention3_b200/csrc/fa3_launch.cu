@@ -397,6 +397,15 @@ extern "C" int shaobo_fa3_b200_last_stage_ms(float* ms3) {
 }
 
 #ifdef FA3B200_DEBUG_DUMP
+extern "C" int shaobo_fa3_b200_debug_cycles(long long* host_out, int clear) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(host_out, g_debug_cycles, sizeof(long long) * 64) != cudaSuccess) return -1;
+    if (clear) {
+        long long zero[64] = {0};
+        cudaMemcpyToSymbol(g_debug_cycles, zero, sizeof(zero));
+    }
+    return 0;
+}
 extern "C" int shaobo_fa3_b200_debug_dump(float* host_out) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     return cudaMemcpyFromSymbol(host_out, g_debug_dump, sizeof(float) * 3 * 128 * 128) == cudaSuccess ? 0 : -1;

@@ -17,15 +17,20 @@
 // The softmax scale is applied once at the end (dK in the epilogue, dQ in the
 // convert kernel) instead of per element of dS.
 //
-// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
-// owner, warps 4-7 = softmax / dS warpgroup (thread j owns TMEM lane j = key j),
-// warps 8-11 = dQ drain warpgroup.  All hand-offs go through mbarriers; every
-// wait is bounded and a time-out raises an error flag instead of hanging.
+// Warp roles (512 threads, four warpgroups): warp 0 = TMA producer, warp 1 = MMA
+// issuer and TMEM owner; warps 4-7 and 8-11 = two softmax / dS warpgroups (thread
+// j of each owns TMEM lane j = key j; the first takes queries 0-63 of the tile,
+// the second queries 64-127); warps 12-15 = dQ drain warpgroup.  Registers are
+// re-split with setmaxnreg (96 / 120 / 120 / 168 per thread at D=128).  All hand-offs go
+// through mbarriers; every wait is bounded and a time-out raises an error flag
+// instead of hanging.
 //
 // Tensor-memory ledger (512 columns x 128 lanes x 32 bit):
 //     D = 128:  dK [0,128)  dV [128,256)  S/P [256,384)  dP and dQ share [384,512)
 //     D =  64:  dK [0,64)   dV [64,128)   S/P [128,256)  dP [256,384)  dQ [384,448)
-// P^T (16-bit, two per column) is written over the first half of S^T in place.
+// P^T (16-bit, two per column) is written over S^T in place: queries 0-63 on the
+// first 32 columns of the S region, queries 64-127 on columns 64-95, so that each
+// softmax warpgroup only overwrites columns it has already read itself.
 //
 // Shared-memory ledger (bytes; every tile is made of 16 KiB boxes of
 // [128 rows][64 x 16 bit] in the 128-byte swizzle):
@@ -58,8 +63,19 @@ __device__ int g_device_error = 0;
 
 #ifdef FA3B200_DEBUG_DUMP
 // Debug builds only: raw S^T, dP^T ([key][query]) and dQ ([query][d]) of the
-// first step of block 0.
+// first step of block 0, and per-role cycle counters of block 0.
 __device__ float g_debug_dump[3 * 128 * 128];
+__device__ long long g_debug_cycles[64];
+#define DBG_TICK() long long dbg_t0 = clock64()
+#define DBG_TOCK(slot)                                                        \
+    do {                                                                      \
+        const long long dbg_t1 = clock64();                                   \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_debug_cycles[slot] += dbg_t1 - dbg_t0; \
+        dbg_t0 = dbg_t1;                                                      \
+    } while (0)
+#else
+#define DBG_TICK() do {} while (0)
+#define DBG_TOCK(slot) do {} while (0)
 #endif
 
 struct FusedArgs {
@@ -91,7 +107,7 @@ __host__ __device__ inline int remap_k_tile(int physical, int count, int mode, i
 template <int D>
 struct FusedCfg {
     static constexpr int kTile = 128;
-    static constexpr int kThreads = 384;
+    static constexpr int kThreads = 512;
     static constexpr int kBoxBytes = 128 * 128;
     static constexpr int kBoxes = D / 64;
     static constexpr int kOperandBytes = kBoxes * kBoxBytes;
@@ -112,6 +128,12 @@ struct FusedCfg {
     static constexpr int kSmemBytes = kOffBar + 256;
     static_assert(kSmemBytes <= 232448, "shared-memory ledger exceeds 227 KiB");
     static_assert(kOffStage % 1024 == 0 && kOffDS % 1024 == 0, "swizzled regions need 1 KiB alignment");
+
+    // setmaxnreg split per warpgroup (producer+MMA / softmax x2 / drain); sums to <= 512
+    static constexpr int kRegsControl = 96;
+    static constexpr int kRegsCompute = D == 128 ? 120 : 136;
+    static constexpr int kRegsDrain = D == 128 ? 168 : 136;
+    static_assert(kRegsControl + 2 * kRegsCompute + kRegsDrain <= 512, "register file over-committed");
 
     static constexpr int kTmemCols = 512;
     static constexpr int kColDK = 0;
@@ -144,10 +166,11 @@ constexpr long long kWaitTimeoutCycles = 2000000000LL;  // about one second
 
 // Bounded mbarrier wait.  Returns false when the wait timed out here or was
 // abandoned because another thread of the CTA timed out.
+template <bool kBackoff = false>
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
                                              volatile uint32_t* abort_flag) {
 #pragma unroll 1
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 4; ++i) {
         if (ptx::mbar_try_wait(bar, parity)) return true;
     }
     const long long start = clock64();
@@ -156,6 +179,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
 #pragma unroll 1
         for (int i = 0; i < 16; ++i) {
             if (ptx::mbar_try_wait(bar, parity)) return true;
+            if (kBackoff) __nanosleep(32);  // keep a waiting warp off the issue ports
         }
         if (*abort_flag != 0) return false;
         if (clock64() - start > kWaitTimeoutCycles) {
@@ -166,9 +190,10 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
     }
 }
 
+template <bool kBackoff = true>
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t* abort_flag) {
-    const bool ok = bounded_wait(bar, parity, abort_flag);
+    const bool ok = bounded_wait<kBackoff>(bar, parity, abort_flag);
     return __all_sync(0xffffffffu, ok);
 }
 
@@ -176,7 +201,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity,
 // and dV outputs (T for the fused path, float for the split path).  kWithDq:
 // false turns the kernel into the four-GEMM dK/dV half of the split path.
 template <typename T, int D, bool kCausal, bool kWithDq, typename TOut>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(512, 1)
 fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                  const __grid_constant__ CUtensorMap tm_dqacc, const FusedArgs a) {
@@ -186,6 +211,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t sbase = ptx::smem_u32(smem);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int wg = warp >> 2;
     auto bar = [&](int i) -> uint32_t { return sbase + C::kOffBar + 8 * i; };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kNumBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -215,8 +241,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         ptx::mbar_init(bar(kSFull), 1);
         ptx::mbar_init(bar(kDpFull), 1);
-        ptx::mbar_init(bar(kPReady), 128);
-        ptx::mbar_init(bar(kDsReady), 128);
+        ptx::mbar_init(bar(kPReady), 256);
+        ptx::mbar_init(bar(kDsReady), 256);
         ptx::mbar_init(bar(kDsFree), 1);
         ptx::mbar_init(bar(kDqFull), 1);
         ptx::mbar_init(bar(kDqEmpty), 128);
@@ -239,8 +265,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         qt = q_begin + (t - g * steps_per_head);
     };
 
-    if (!misaligned) {
-        if (warp == 0) {
+    if (wg == 0) {
+        ptx::setmaxnreg_dec<C::kRegsControl>();
+        if (!misaligned && warp == 0) {
             // =================================================== TMA producer
             if (lane == 0) {
                 ptx::prefetch_tensormap(&tm_q);
@@ -277,7 +304,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     }
                 }
             }
-        } else if (warp == 1) {
+        } else if (!misaligned && warp == 1) {
             // ===================================================== MMA issuer
             if (lane == 0) {
                 constexpr uint32_t kIdSdP = ptx::instr_desc_f16(kBf16, 128, 128, false, false);
@@ -315,16 +342,19 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     ptx::tc_fence_after();
                     issue_dp(0);
                 }
+                DBG_TICK();
 #pragma unroll 1
                 for (int t = 0; ok && t < n_steps; ++t) {
                     const bool more = t + 1 < n_steps;
-                    // dV += P^T dO
+                    // dV += P^T dO.  P^T of queries 0-63 sits on columns [0,32) of the S
+                    // region, of queries 64-127 on columns [64,96).
                     if (!(ok = bounded_wait(bar(kPReady), t & 1, abort_flag))) break;
+                    DBG_TOCK(0);
                     ptx::tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)
-                        ptx::mma_ts(tmem + C::kColDV, tmem + C::kColS + kk * 8, mn_major(sDO(t), kk), kIdDkv,
-                                    (t > 0 || kk > 0) ? 1u : 0u);
+                        ptx::mma_ts(tmem + C::kColDV, tmem + C::kColS + (kk >> 2) * 64 + (kk & 3) * 8,
+                                    mn_major(sDO(t), kk), kIdDkv, (t > 0 || kk > 0) ? 1u : 0u);
                     ptx::tc_commit(bar(kDoEmpty + t % C::kDoStages));
                     // S(t+1) may overwrite S/P(t): MMAs execute in issue order.
                     if (more) {
@@ -333,8 +363,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         ptx::tc_fence_after();
                         issue_s(t + 1);
                     }
+                    DBG_TOCK(1);
                     // dK += dS^T Q
                     if (!(ok = bounded_wait(bar(kDsReady), t & 1, abort_flag))) break;
+                    DBG_TOCK(2);
                     ptx::tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)
@@ -353,27 +385,38 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         ptx::tc_commit(bar(kDqFull));
                     }
                     ptx::tc_commit(bar(kDsFree));
+                    DBG_TOCK(3);
                     if (more) {
                         if (!(ok = bounded_wait(bar(kDoFull + (t + 1) % C::kDoStages),
                                                 ((t + 1) / C::kDoStages) & 1, abort_flag))) break;
+                        DBG_TOCK(4);
                         if (kWithDq && D == 128) {  // dP(t+1) reuses the dQ(t) columns
                             if (!(ok = bounded_wait(bar(kDqEmpty), t & 1, abort_flag))) break;
                         }
+                        DBG_TOCK(5);
                         ptx::tc_fence_after();
                         issue_dp(t + 1);
+                        DBG_TOCK(6);
                     }
                 }
                 if (ok) ptx::tc_commit(bar(kDkvFull));
             }
-        } else if (warp >= 4 && warp < 8) {
-            // ========================================= softmax / dS warpgroup
-            const int j = threadIdx.x - 128;  // key row inside the tile == TMEM lane
+        }
+    } else if (wg == 1 || wg == 2) {
+        // ============================================ softmax / dS warpgroups
+        if (C::kRegsCompute < 128) ptx::setmaxnreg_dec<C::kRegsCompute>();
+        else ptx::setmaxnreg_inc<C::kRegsCompute>();
+        if (!misaligned) {
+            const int half = wg - 1;          // which 64 queries of the tile
+            const int j = threadIdx.x & 127;  // key row inside the tile == TMEM lane
             const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
+            const uint32_t s_cols = tl + C::kColS + half * 64;
+            const uint32_t dp_cols = tl + C::kColDP + half * 64;
             float* stats = reinterpret_cast<float*>(smem + C::kOffStats);
-            uint32_t ppk[64];
+            uint32_t ppk[32];
             const float* side_base = a.sidecar;
-            float s0, s1, s2;
-            {
+            float s0 = 0.f, s1 = 1.f, s2 = 0.f;
+            if (half == 0) {
                 int hq, qt;
                 step_coords(0, hq, qt);
                 const int64_t row = int64_t(b * a.heads_q + hq) * a.seqlen + qt * C::kTile + j;
@@ -382,47 +425,54 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 s2 = side_base[row * 3 + 2];
             }
             bool ok = true;
+            DBG_TICK();
 #pragma unroll 1
             for (int t = 0; t < n_steps; ++t) {
                 int hq, qt;
                 step_coords(t, hq, qt);
                 const int buf = t & 1;
-                float* negp = stats + buf * 128;
-                float* delp = stats + 256 + buf * 128;
-                negp[j] = __log2f(s1) - s0;  // P = exp2(x - m) * r = exp2(x + (log2 r - m))
-                delp[j] = s2;
-                ptx::mbar_arrive(bar(kStatsFull + buf));
-                if (t + 1 < n_steps) {
-                    int hq1, qt1;
-                    step_coords(t + 1, hq1, qt1);
-                    const int64_t row = int64_t(b * a.heads_q + hq1) * a.seqlen + qt1 * C::kTile + j;
-                    s0 = side_base[row * 3 + 0];
-                    s1 = side_base[row * 3 + 1];
-                    s2 = side_base[row * 3 + 2];
+                const float* negp = stats + buf * 128 + half * 64;
+                const float* delp = stats + 256 + buf * 128 + half * 64;
+                if (half == 0) {
+                    // row statistics of query row j of this tile, for both warpgroups
+                    stats[buf * 128 + j] = __log2f(s1) - s0;  // P = exp2(x - m) * r = exp2(x + (log2 r - m))
+                    stats[256 + buf * 128 + j] = s2;
+                    ptx::mbar_arrive(bar(kStatsFull + buf));
+                    if (t + 1 < n_steps) {
+                        int hq1, qt1;
+                        step_coords(t + 1, hq1, qt1);
+                        const int64_t row = int64_t(b * a.heads_q + hq1) * a.seqlen + qt1 * C::kTile + j;
+                        s0 = side_base[row * 3 + 0];
+                        s1 = side_base[row * 3 + 1];
+                        s2 = side_base[row * 3 + 2];
+                    }
                 }
                 if (!(ok = warp_wait(bar(kStatsFull + buf), (t >> 1) & 1, abort_flag))) break;
+                if (warp == 4) DBG_TOCK(8);
                 if (!(ok = warp_wait(bar(kSFull), t & 1, abort_flag))) break;
+                if (warp == 4) DBG_TOCK(9);
                 ptx::tc_fence_after();
                 const bool diagonal = kCausal && qt == kt;
-                // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked where query i < key j
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    ptx::tmem_ld32(tl + C::kColS + c * 32, r);
-                    ptx::tmem_ld_wait();
+                // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked where query i < key j.
+                                auto softmax_chunk = [&](int c, const uint32_t* r) {
 #ifdef FA3B200_DEBUG_DUMP
                     if (blockIdx.x == 0 && t == 0)
-                        for (int e = 0; e < 32; ++e) g_debug_dump[j * 128 + c * 32 + e] = __uint_as_float(r[e]);
+                        for (int e = 0; e < 32; ++e)
+                            g_debug_dump[j * 128 + half * 64 + c * 32 + e] = __uint_as_float(r[e]);
 #endif
 #pragma unroll
                     for (int e = 0; e < 32; e += 4) {
+#ifdef FA3B200_EXPERIMENT_NOSTATS
+                        const float4 n4 = make_float4(-8.f, -8.f, -8.f, -8.f);
+#else
                         const float4 n4 = *reinterpret_cast<const float4*>(negp + c * 32 + e);
+#endif
                         float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, n4.x));
                         float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, n4.y));
                         float p2 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 2]), a.scale_log2, n4.z));
                         float p3 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 3]), a.scale_log2, n4.w));
                         if (diagonal) {
-                            const int i = c * 32 + e;
+                            const int i = half * 64 + c * 32 + e;
                             p0 = (i + 0 >= j) ? p0 : 0.0f;
                             p1 = (i + 1 >= j) ? p1 : 0.0f;
                             p2 = (i + 2 >= j) ? p2 : 0.0f;
@@ -431,29 +481,43 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         ppk[c * 16 + e / 2 + 0] = ptx::Pack2<T>::pack(p0, p1);
                         ppk[c * 16 + e / 2 + 1] = ptx::Pack2<T>::pack(p2, p3);
                     }
-                    ptx::tmem_st16(tl + C::kColS + c * 16, &ppk[c * 16]);
+                    // P chunk c -> columns [16c, 16c+16) of this half's S columns (already read)
+                    ptx::tmem_st16(s_cols + c * 16, &ppk[c * 16]);
+                };
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(s_cols + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    softmax_chunk(c, r);
                 }
+                if (warp == 4) DBG_TOCK(18);
                 ptx::tmem_st_wait();
+                if (warp == 4) DBG_TOCK(19);
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(bar(kPReady));
+                if (warp == 4) DBG_TOCK(10);
                 // ---- dS^T = P^T * (dP^T - delta_i), stored [key][query] in the 128-byte swizzle
                 if (!(ok = warp_wait(bar(kDpFull), t & 1, abort_flag))) break;
+                if (warp == 4) DBG_TOCK(11);
                 if (!(ok = warp_wait(bar(kDsFree), (t & 1) ^ 1, abort_flag))) break;
+                if (warp == 4) DBG_TOCK(12);
                 ptx::tc_fence_after();
-                const uint32_t ds_row = sbase + C::kOffDS + j * 128;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    ptx::tmem_ld32(tl + C::kColDP + c * 32, r);
-                    ptx::tmem_ld_wait();
+                const uint32_t ds_row = sbase + C::kOffDS + half * C::kBoxBytes + j * 128;
+                auto ds_chunk = [&](int c, const uint32_t* r) {
 #ifdef FA3B200_DEBUG_DUMP
                     if (blockIdx.x == 0 && t == 0)
-                        for (int e = 0; e < 32; ++e) g_debug_dump[16384 + j * 128 + c * 32 + e] = __uint_as_float(r[e]);
+                        for (int e = 0; e < 32; ++e)
+                            g_debug_dump[16384 + j * 128 + half * 64 + c * 32 + e] = __uint_as_float(r[e]);
 #endif
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
+#ifdef FA3B200_EXPERIMENT_NOSTATS
+                        const float4 d0 = make_float4(.1f, .1f, .1f, .1f), d1 = d0;
+#else
                         const float4 d0 = *reinterpret_cast<const float4*>(delp + c * 32 + e);
                         const float4 d1 = *reinterpret_cast<const float4*>(delp + c * 32 + e + 4);
+#endif
                         const float2 pa = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 0]);
                         const float2 pb = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 1]);
                         const float2 pc = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 2]);
@@ -467,106 +531,124 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                                   pc.y * (__uint_as_float(r[e + 5]) - d1.y));
                         o.w = ptx::Pack2<T>::pack(pd.x * (__uint_as_float(r[e + 6]) - d1.z),
                                                   pd.y * (__uint_as_float(r[e + 7]) - d1.w));
-                        const int chunk = c * 4 + e / 8;  // 16-byte chunk along the query axis
-                        const uint32_t addr = ds_row + (chunk >> 3) * C::kBoxBytes +
-                                              (((chunk & 7) ^ (j & 7)) << 4);
+                        const int chunk = c * 4 + e / 8;  // 16-byte chunk inside this half's box
+                        const uint32_t addr = ds_row + ((chunk ^ (j & 7)) << 4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.x),
                                      "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
                     }
+                };
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(dp_cols + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    ds_chunk(c, r);
                 }
+                if (warp == 4) DBG_TOCK(20);
                 ptx::fence_proxy_async_smem();
+                if (warp == 4) DBG_TOCK(21);
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(bar(kDsReady));
+                if (warp == 4) DBG_TOCK(13);
             }
-            // ---- epilogue: dK (scaled) and dV out of tensor memory
+            // ---- epilogue: the first warpgroup writes dK (scaled), the second dV
             if (ok) ok = warp_wait(bar(kDkvFull), 0, abort_flag);
             if (ok) {
                 ptx::tc_fence_after();
                 const int64_t row = int64_t(b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile + j;
+                TOut* dst = reinterpret_cast<TOut*>(half == 0 ? a.dk : a.dv) + row * D;
+                const float mul = half == 0 ? a.scale : 1.0f;
+                const uint32_t col0 = tl + (half == 0 ? C::kColDK : C::kColDV);
 #pragma unroll
-                for (int which = 0; which < 2; ++which) {
-                    TOut* dst = reinterpret_cast<TOut*>(which == 0 ? a.dk : a.dv) + row * D;
-                    const float mul = which == 0 ? a.scale : 1.0f;
-                    const int col0 = which == 0 ? C::kColDK : C::kColDV;
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(col0 + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    if (sizeof(TOut) == 4) {
+                        float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t r[32];
-                        ptx::tmem_ld32(tl + col0 + c * 32, r);
-                        ptx::tmem_ld_wait();
-                        if (sizeof(TOut) == 4) {
-                            float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
+                        for (int e = 0; e < 8; ++e)
+                            d4[e] = make_float4(__uint_as_float(r[4 * e]) * mul, __uint_as_float(r[4 * e + 1]) * mul,
+                                                __uint_as_float(r[4 * e + 2]) * mul, __uint_as_float(r[4 * e + 3]) * mul);
+                    } else {
+                        uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                d4[e] = make_float4(__uint_as_float(r[4 * e]) * mul, __uint_as_float(r[4 * e + 1]) * mul,
-                                                    __uint_as_float(r[4 * e + 2]) * mul, __uint_as_float(r[4 * e + 3]) * mul);
-                        } else {
-                            uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+                        for (int e = 0; e < 4; ++e) {
+                            uint4 o;
+                            o.x = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 0]) * mul, __uint_as_float(r[8 * e + 1]) * mul);
+                            o.y = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 2]) * mul, __uint_as_float(r[8 * e + 3]) * mul);
+                            o.z = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 4]) * mul, __uint_as_float(r[8 * e + 5]) * mul);
+                            o.w = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 6]) * mul, __uint_as_float(r[8 * e + 7]) * mul);
+                            d4[e] = o;
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // ==================================================== dQ drain warpgroup
+        if (!kWithDq) {
+            ptx::setmaxnreg_dec<C::kRegsControl>();
+        } else {
+            ptx::setmaxnreg_inc<C::kRegsDrain>();
+            if (!misaligned) {
+                const int qd = warp & 3;
+                const uint32_t tl = tmem + (uint32_t(qd * 32) << 16);
+                const uint32_t stage = sbase + C::kOffStage + qd * 2 * C::kStageBoxBytes;
+                bool pending = false;
+                DBG_TICK();
+#pragma unroll 1
+                for (int t = 0; t < n_steps; ++t) {
+                    int hq, qt;
+                    step_coords(t, hq, qt);
+                    const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile + qd * 32;
+                    if (!warp_wait(bar(kDqFull), t & 1, abort_flag)) break;
+                    if (warp == 12) DBG_TOCK(16);
+                    ptx::tc_fence_after();
+                    // pull the whole dQ tile row into registers and hand the columns back at once
+                    uint32_t r[D / 32][32];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                uint4 o;
-                                o.x = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 0]) * mul, __uint_as_float(r[8 * e + 1]) * mul);
-                                o.y = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 2]) * mul, __uint_as_float(r[8 * e + 3]) * mul);
-                                o.z = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 4]) * mul, __uint_as_float(r[8 * e + 5]) * mul);
-                                o.w = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 6]) * mul, __uint_as_float(r[8 * e + 7]) * mul);
-                                d4[e] = o;
+                    for (int c = 0; c < D / 32; ++c) ptx::tmem_ld32(tl + C::kColDQ + c * 32, r[c]);
+                    ptx::tmem_ld_wait();
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(bar(kDqEmpty));
+#ifdef FA3B200_DEBUG_DUMP
+                    if (blockIdx.x == 0 && t == 0)
+                        for (int c = 0; c < D / 32; ++c)
+                            for (int e = 0; e < 32; ++e)
+                                g_debug_dump[32768 + (qd * 32 + lane) * 128 + c * 32 + e] = __uint_as_float(r[c][e]);
+#endif
+#pragma unroll
+                    for (int hf = 0; hf < D / 64; ++hf) {
+                        if (pending) {
+                            if (lane == 0) ptx::bulk_wait_group_read<0>();
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int bx = 0; bx < 2; ++bx) {
+                            const uint32_t row_addr = stage + bx * C::kStageBoxBytes + lane * 128;
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                             ::"r"(row_addr + ((c ^ (lane & 7)) << 4)), "r"(r[hf * 2 + bx][4 * c]),
+                                               "r"(r[hf * 2 + bx][4 * c + 1]), "r"(r[hf * 2 + bx][4 * c + 2]),
+                                               "r"(r[hf * 2 + bx][4 * c + 3])
+                                             : "memory");
                             }
                         }
-                    }
-                }
-            }
-        } else if (warp >= 8 && kWithDq) {
-            // ================================================ dQ drain warpgroup
-            const int qd = warp & 3;
-            const uint32_t tl = tmem + (uint32_t(qd * 32) << 16);
-            const uint32_t stage = sbase + C::kOffStage + qd * 2 * C::kStageBoxBytes;
-            bool pending = false;
-#pragma unroll 1
-            for (int t = 0; t < n_steps; ++t) {
-                int hq, qt;
-                step_coords(t, hq, qt);
-                const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile + qd * 32;
-                if (!warp_wait(bar(kDqFull), t & 1, abort_flag)) break;
-                ptx::tc_fence_after();
-#pragma unroll
-                for (int half = 0; half < D / 64; ++half) {
-                    if (pending) {
-                        if (lane == 0) ptx::bulk_wait_group_read<0>();
+                        ptx::fence_proxy_async_smem();
                         __syncwarp();
-                    }
-#pragma unroll
-                    for (int bx = 0; bx < 2; ++bx) {
-                        uint32_t r[32];
-                        ptx::tmem_ld32(tl + C::kColDQ + half * 64 + bx * 32, r);
-                        ptx::tmem_ld_wait();
-#ifdef FA3B200_DEBUG_DUMP
-                        if (blockIdx.x == 0 && t == 0)
-                            for (int e = 0; e < 32; ++e)
-                                g_debug_dump[32768 + (qd * 32 + lane) * 128 + half * 64 + bx * 32 + e] = __uint_as_float(r[e]);
-#endif
-                        if (half == D / 64 - 1 && bx == 1) {
-                            ptx::tc_fence_before();
-                            ptx::mbar_arrive(bar(kDqEmpty));
+                        if (lane == 0) {
+                            ptx::tma_reduce_add_2d(&tm_dqacc, stage, hf * 64, q_row);
+                            ptx::tma_reduce_add_2d(&tm_dqacc, stage + C::kStageBoxBytes, hf * 64 + 32, q_row);
+                            ptx::bulk_commit_group();
                         }
-                        const uint32_t row_addr = stage + bx * C::kStageBoxBytes + lane * 128;
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                         ::"r"(row_addr + ((c ^ (lane & 7)) << 4)), "r"(r[4 * c]),
-                                           "r"(r[4 * c + 1]), "r"(r[4 * c + 2]), "r"(r[4 * c + 3])
-                                         : "memory");
-                        }
+                        pending = true;
                     }
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        ptx::tma_reduce_add_2d(&tm_dqacc, stage, half * 64, q_row);
-                        ptx::tma_reduce_add_2d(&tm_dqacc, stage + C::kStageBoxBytes, half * 64 + 32, q_row);
-                        ptx::bulk_commit_group();
-                    }
-                    pending = true;
+                    if (warp == 12) DBG_TOCK(17);
                 }
+                if (lane == 0) ptx::bulk_wait_group<0>();
             }
-            if (lane == 0) ptx::bulk_wait_group<0>();
         }
     }
 
