@@ -256,6 +256,7 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     args.scale_log2 = p->softmax_scale * kLog2E;
     args.order_mode = plan.mode;
     args.order_width = plan.width;
+    args.head_major = plan.head_major;
     const int64_t blocks64 = int64_t(n_tiles) * bh;
     if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
     const int blocks = int(blocks64);

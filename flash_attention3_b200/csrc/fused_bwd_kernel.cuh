@@ -90,6 +90,7 @@ struct FusedArgs {
     float scale_log2;
     int order_mode;        // see cta_order.h
     int order_width;
+    int head_major;        // block index = head * n_tiles + tile slot (else tile slot * heads + head)
 };
 
 __host__ __device__ inline int remap_k_tile(int physical, int count, int mode, int width) {
@@ -219,8 +220,11 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // ---- which tile is ours ------------------------------------------------
     const int n_tiles = a.seqlen / C::kTile;
     const int bh_count = a.batch * a.heads_kv;
-    const int kt = remap_k_tile(int(blockIdx.x) / bh_count, n_tiles, a.order_mode, a.order_width);
-    const int bhi = int(blockIdx.x) % bh_count;
+    // head_major: all key tiles of one (batch, KV head) are adjacent block indices, so the
+    // CTAs that run at the same time share Q/dO tiles and dQ-accumulator lines in L2.
+    const int tile_slot = a.head_major ? int(blockIdx.x) % n_tiles : int(blockIdx.x) / bh_count;
+    const int bhi = a.head_major ? int(blockIdx.x) / n_tiles : int(blockIdx.x) % bh_count;
+    const int kt = remap_k_tile(tile_slot, n_tiles, a.order_mode, a.order_width);
     const int b = bhi / a.heads_kv;
     const int kvh = bhi % a.heads_kv;
     const int group = a.heads_q / a.heads_kv;
@@ -259,10 +263,19 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
+    // Query tiles are visited in ascending order starting at the diagonal (causal) or at a
+    // per-CTA rotation (non-causal), so that CTAs of one head that run together add into
+    // different dQ tiles at any moment.
     auto step_coords = [&](int t, int& hq, int& qt) {
         const int g = t / steps_per_head;
         hq = kvh * group + g;
-        qt = q_begin + (t - g * steps_per_head);
+        const int r = t - g * steps_per_head;
+        if (kCausal) {
+            qt = q_begin + r;
+        } else {
+            qt = r + kt;
+            if (qt >= n_tiles) qt -= n_tiles;
+        }
     };
 
     if (wg == 0) {
@@ -638,11 +651,13 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         }
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
+#ifndef FA3B200_EXPERIMENT_NOREDUCE
                         if (lane == 0) {
                             ptx::tma_reduce_add_2d(&tm_dqacc, stage, hf * 64, q_row);
                             ptx::tma_reduce_add_2d(&tm_dqacc, stage + C::kStageBoxBytes, hf * 64 + 32, q_row);
                             ptx::bulk_commit_group();
                         }
+#endif
                         pending = true;
                     }
                     if (warp == 12) DBG_TOCK(17);

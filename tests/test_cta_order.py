@@ -14,9 +14,12 @@ extern "C" int remap(int p, int n, int mode, int w) { return fa3b200::host_remap
 extern "C" long long makespan(int n, int bh, int g, int causal, int sms, int mode, int w) {
     return fa3b200::modelled_makespan(n, bh, g, causal != 0, sms, mode, w);
 }
-extern "C" void plan(int n, int bh, int g, int causal, int sms, int* mode, int* width, long long* ms) {
+extern "C" long long makespan_hm(int n, int bh, int g, int causal, int sms) {
+    return fa3b200::modelled_makespan(n, bh, g, causal != 0, sms, 0, 1, true);
+}
+extern "C" void plan(int n, int bh, int g, int causal, int sms, int* mode, int* width, long long* ms, int* hm) {
     auto p = fa3b200::plan_cta_order(n, bh, g, causal != 0, sms);
-    *mode = p.mode; *width = p.width; *ms = p.makespan;
+    *mode = p.mode; *width = p.width; *ms = p.makespan; *hm = p.head_major;
 }
 '''
 
@@ -30,6 +33,7 @@ def lib(tmp_path_factory):
                     str(ROOT / "flash_attention3_b200/csrc"), str(d / "w.cpp"), "-o", str(so)], check=True)
     lib = ctypes.CDLL(str(so))
     lib.makespan.restype = ctypes.c_longlong
+    lib.makespan_hm.restype = ctypes.c_longlong
     return lib
 
 
@@ -44,11 +48,17 @@ def test_plan_never_worse_than_heavy_first(lib):
     for n in (1, 8, 16, 32, 64):
         for bh in (1, 4, 16, 64, 200):
             for g in (1, 4):
-                mode, width, ms = ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
-                lib.plan(n, bh, g, 1, 148, ctypes.byref(mode), ctypes.byref(width), ctypes.byref(ms))
+                mode, width, ms, hm = ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong(), ctypes.c_int()
+                lib.plan(n, bh, g, 1, 148, ctypes.byref(mode), ctypes.byref(width), ctypes.byref(ms), ctypes.byref(hm))
                 base = lib.makespan(n, bh, g, 1, 148, 0, 1)
-                assert ms.value <= base
-                assert ms.value == lib.makespan(n, bh, g, 1, 148, mode.value, width.value)
+                # head-major may be chosen for cache locality at a modelled cost of at most 8 %
+                assert ms.value * 100 <= base * 108
+                if not hm.value:
+                    assert ms.value <= base
+                if hm.value:
+                    assert ms.value == lib.makespan_hm(n, bh, g, 1, 148)
+                else:
+                    assert ms.value == lib.makespan(n, bh, g, 1, 148, mode.value, width.value)
                 total = bh * sum(1 + g * (n - k) for k in range(n))
                 assert ms.value * 148 >= total  # cannot beat perfect balance
 
