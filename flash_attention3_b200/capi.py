@@ -16,6 +16,7 @@ AUX_SMAX_SSUM, AUX_LSE = 0, 1
 DKV_PATH_REFERENCE, DKV_PATH_CANONICAL = 1, 5
 DQ_PATH_REFERENCE, DQ_PATH_CANONICAL = 1, 6
 RESERVED_PTR_DELTA, RESERVED_PTR_SIDECAR, RESERVED_PTR_STREAM = 0, 3, 7
+STATIC_SCRATCH_BYTES = 32 << 20  # SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES
 
 FEATURE_BITS = {
     "FIXED_LENGTH": 1 << 0, "VARLEN": 1 << 1, "FP16": 1 << 2, "BF16": 1 << 3, "CAUSAL": 1 << 4,
@@ -65,6 +66,7 @@ EXPORTS = [
     "shaobo_fa3_bwd_dq_workspace_bytes", "shaobo_fa3_bwd_dq",
     # include/shaobo_fa3_b200_ext.h
     "shaobo_fa3_b200_device_error", "shaobo_fa3_b200_stage_timing", "shaobo_fa3_b200_last_stage_ms",
+    "shaobo_fa3_b200_bwd_v2_noalloc",
 ]
 
 _lib = None
@@ -96,6 +98,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         getattr(lib, name).restype = ctypes.c_size_t
     lib.shaobo_fa3_bwd_v2.argtypes = [vp] * 10 + [pp]
     lib.shaobo_fa3_bwd_v2.restype = ctypes.c_int
+    lib.shaobo_fa3_b200_bwd_v2_noalloc.argtypes = [vp] * 10 + [pp]
+    lib.shaobo_fa3_b200_bwd_v2_noalloc.restype = ctypes.c_int
     for name in ("shaobo_fa3_bwd", "shaobo_fa3_bwd_dkv", "shaobo_fa3_bwd_dq"):
         getattr(lib, name).argtypes = [vp] * 10 + [pp]
         getattr(lib, name).restype = ctypes.c_int

@@ -561,3 +561,67 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
     if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
     return finish(&launch, params->sync_after_launch != 0);
 }
+
+// ---------------------------------------------------------------------------
+// Backward for callers that cannot allocate device memory.
+//
+// Some hosts of this library never get to call cudaMalloc: a plugin that runs
+// inside another framework's pre-sized memory arena, a real-time loop where
+// allocation is forbidden after start-up, or a process whose memory budget is
+// fixed by its launcher.  shaobo_fa3_bwd_v2 needs scratch beyond its inputs and
+// outputs (the fp32 dQ accumulator, delta and the packed sidecar), which such a
+// caller has nowhere to get from.  This entry point keeps that scratch in a
+// fixed array that is part of the library image: it exists on every GPU that
+// loads the library, from load until the process exits, whether or not the
+// entry point is ever called.
+__device__ __align__(256) static unsigned char g_static_scratch[SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// Device address of g_static_scratch, resolved once per device.  In host code
+// the array's name is only a handle for the runtime, not an address a kernel
+// could use, so the address is asked for explicitly.
+struct StaticScratch {
+    std::mutex mu;
+    void* ptr[128] = {};
+    bool known[128] = {};
+    void* get() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 128) return nullptr;
+        std::lock_guard<std::mutex> lock(mu);
+        if (!known[dev]) {
+            void* p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            ptr[dev] = p;
+            known[dev] = true;
+        }
+        return ptr[dev];
+    }
+};
+StaticScratch g_scratch_lookup;
+
+}  // namespace
+
+extern "C" int shaobo_fa3_b200_bwd_v2_noalloc(const void* dout, const void* q, const void* k,
+                                              const void* v, const void* out,
+                                              const void* softmax_lse, void* dq, void* dk,
+                                              void* dv, void* softmax_d,
+                                              const ShaoboFa3Params* params) {
+    const int validation = validate_v2(params);
+    if (validation != SHAOBO_FA3_STATUS_SUCCESS) return validation;
+    const V2Workspace ws = v2_workspace(params);
+    if (!ws.valid) return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    if (ws.total_bytes > size_t(SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES)) {
+        // the problem needs more scratch than the built-in array holds
+        return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    }
+    void* scratch = g_scratch_lookup.get();
+    if (scratch == nullptr) return SHAOBO_FA3_STATUS_HIP_ERROR;
+    ShaoboFa3Params with_scratch = *params;
+    with_scratch.workspace = scratch;
+    with_scratch.workspace_bytes = size_t(SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES);
+    return shaobo_fa3_bwd_v2(dout, q, k, v, out, softmax_lse, dq, dk, dv, softmax_d, &with_scratch);
+}

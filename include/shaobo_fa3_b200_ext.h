@@ -32,6 +32,53 @@ int shaobo_fa3_b200_stage_timing(int enable);
  * no call was timed.  (No counterpart in the reference.) */
 int shaobo_fa3_b200_last_stage_ms(float* ms3);
 
+/* Size of the scratch array built into the library for
+ * shaobo_fa3_b200_bwd_v2_noalloc: 32 MiB on every GPU that loads the library,
+ * held until the process exits. */
+#define SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* shaobo_fa3_bwd_v2 for callers that cannot allocate device memory.  (No
+ * counterpart in the reference.)
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits - a plugin
+ * living inside a host framework's fixed memory arena, a latency-critical loop
+ * that must not allocate after start-up, a job whose device memory was sized
+ * by its launcher.  Such a caller can pass inputs and outputs but has no
+ * workspace to offer, and shaobo_fa3_bwd_v2 needs one.
+ *
+ * What it does: the same computation as shaobo_fa3_bwd_v2, same arguments,
+ * same results and status codes, except that params->workspace and
+ * params->workspace_bytes are ignored: the scratch (fp32 dQ accumulator, delta,
+ * packed sidecar) is a fixed array of SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES
+ * inside the library.  The call performs no cudaMalloc, no cudaFree and no
+ * other allocating runtime or library call.
+ *
+ * Limit: a problem whose shaobo_fa3_bwd_v2_workspace_bytes exceeds
+ * SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES returns SHAOBO_FA3_STATUS_UNSUPPORTED
+ * and launches nothing (B*Hq*S*D up to about 8 Mi elements fits, e.g.
+ * B=1,H=4,S=2048,D=128 or B=2,H=8,S=2048,D=128).
+ *
+ * First call: the first call on each device looks up the device address of the
+ * array (one runtime query, with that device current).  Make that first call
+ * outside any stream capture.
+ *
+ * Sharing: every call on a device uses the same array, which still holds what
+ * the previous call left there; the part that must start at zero (the dQ
+ * accumulator) is cleared by the call itself.  Two calls that overlap in time
+ * on one GPU (different streams, or different host threads) race on the array
+ * and give wrong results: run them one after the other. */
+int shaobo_fa3_b200_bwd_v2_noalloc(const void* dout,
+                                   const void* q,
+                                   const void* k,
+                                   const void* v,
+                                   const void* out,
+                                   const void* softmax_lse,
+                                   void* dq,
+                                   void* dk,
+                                   void* dv,
+                                   void* softmax_d,
+                                   const ShaoboFa3Params* params);
+
 #ifdef __cplusplus
 }
 #endif
