@@ -42,6 +42,8 @@ CONFIGS = {
     "C3d64": (4, 16, 16, 4096, 64, "bf16", False, "B=4,H=16,S=4096,D=64 non-causal bf16"),
     "C4": (2, 32, 8, 8192, 128, "bf16", True, "B=2,Hq=32,Hkv=8,S=8192,D=128 causal bf16 (GQA)"),
     "C5shard": (2, 32, 32, 8192, 128, "bf16", True, "B=2 of 16,H=32,S=8192,D=128 causal bf16 (1/8 shard)"),
+    # the large sharded configuration: strong scaling, the (batch x head) range is split over the ranks
+    "C5": (16, 32, 32, 8192, 128, "bf16", True, "B=16,H=32,S=8192,D=128 causal bf16, sharded by batch x head"),
     # profiler-sized case: ~0.2 GB on the device, working set above the 126 MB L2
     "P1": (1, 16, 16, 4096, 128, "bf16", False, "B=1,H=16,S=4096,D=128 non-causal bf16 (profiling case)"),
     "P2": (1, 16, 16, 4096, 128, "bf16", True, "B=1,H=16,S=4096,D=128 causal bf16 (profiling case)"),
@@ -290,6 +292,13 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     b, hq, hkv, s, d, dtype, causal, desc = cfg
+    strong = args.config == "C5"
+    if strong:
+        # this rank's contiguous (batch x KV head) range; for B=16 over 1/2/4/8 ranks these are whole batches
+        from flash_attention3_b200 import sharding
+        mine = sharding.plan(b, hkv, world)[rank]
+        assert len(mine) == 1 and mine[0].kv_head_count == hkv, "C5 shards are whole batches"
+        cfg = (mine[0].batch_count,) + cfg[1:]
     wl = Workload(cfg, 1234 + rank, torch, capi, ops, synthetic)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
 
@@ -306,13 +315,11 @@ def main():
     dev_err = wl.lib.shaobo_fa3_b200_device_error(1)
     if dev_err != 0:
         raise SystemExit(f"device error flag {dev_err}")
-    total_ms = sum(times)
-    if dist is not None:
-        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+    from flash_attention3_b200.sharding import max_over_ranks
+    total_ms = max_over_ranks(sum(times), dist, "cuda")
     ms_per_step = total_ms / args.steps
-    value = world * wl.flops / (ms_per_step * 1e-3) / 1e12
+    job_flops = bwd_flops(b, hq, s, d, causal) if strong else world * wl.flops
+    value = job_flops / (ms_per_step * 1e-3) / 1e12
 
     stage_ms = time_stages(torch, wl, min(args.steps, 20), flush)
     peaks = measured_peaks()
@@ -329,18 +336,17 @@ def main():
 
     e2e_times, h2d, d2h = time_e2e(torch, wl, max(3, min(args.steps, 20)), 3, flush)
     e2e_ms = sum(e2e_times) / len(e2e_times)
-    if dist is not None:
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e = {"value": world * wl.flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+    e2e_ms = max_over_ranks(e2e_ms, dist, "cuda")
+    e2e = {"value": job_flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if strong else "weak",
         "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-        "config": {"workload": desc + " per GPU", "global_batch": b * world, "sharding": "batch (no collective)",
+        "config": {"workload": desc if strong else desc + " per GPU", "global_batch": b if strong else b * world,
+                   "sharding": "batch (no collective)",
                    "l2": f"flushed before every step ({L2_FLUSH_BYTES >> 20} MiB write, untimed)",
                    "frac_of_measured_peak": value / world / peaks["tflops_burst"],
                    "frac_of_nominal_2250": value / world / 2250.0},
