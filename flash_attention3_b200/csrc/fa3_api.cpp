@@ -113,12 +113,37 @@ size_t dq_accum_bytes(const ShaoboFa3Params* p) {
     return out;
 }
 
+int split_factor(const ShaoboFa3Params* p) {
+    if (!fused_shape_ok(p) || p->deterministic != 0) return 1;
+    const long long tiles = p->seqlen_k / kSequenceAlignment;
+    const long long blocks = tiles * p->batch * p->num_heads_kv;
+    if (blocks >= kSplitSmCount) return 1;
+    const long long group = p->num_heads_q / p->num_heads_kv;
+    long long f = 2LL * kSplitSmCount / blocks;   // aim at about two CTAs per SM
+    const long long longest = group * tiles;      // steps of the heaviest key tile
+    if (f > longest) f = longest;
+    if (f > 8) f = 8;
+    return f < 1 ? 1 : int(f);
+}
+
+size_t dkv_accum_bytes(const ShaoboFa3Params* p) {
+    if (split_factor(p) <= 1) return 0;
+    size_t n = size_t(p->batch), out = 0;
+    if (!mul_ok(n, size_t(p->num_heads_kv), &n) || !mul_ok(n, size_t(p->seqlen_k), &n) ||
+        !mul_ok(n, size_t(p->head_dim_qk), &n) || !mul_ok(n, 2 * sizeof(float), &n) ||
+        !round_up_256(n, &out)) {
+        return 0;
+    }
+    return out;
+}
+
 V2Workspace v2_workspace(const ShaoboFa3Params* p) {
     V2Workspace w;
     if (validate_v2(p) != SHAOBO_FA3_STATUS_SUCCESS) return w;
     w.dq_accum_bytes = dq_accum_bytes(p);
     if (w.dq_accum_bytes == 0) return w;
-    w.delta_offset = w.dq_accum_bytes;  // already a multiple of 256
+    w.dkv_accum_bytes = dkv_accum_bytes(p);
+    if (!add_ok(w.dq_accum_bytes, w.dkv_accum_bytes, &w.delta_offset)) return V2Workspace{};
     bool ok = false;
     const size_t rows = row_count(p, &ok);
     size_t delta_bytes = 0, sidecar_bytes = 0, end_of_delta = 0;
@@ -199,7 +224,11 @@ extern "C" size_t shaobo_fa3_bwd_fused5_workspace_bytes(const ShaoboFa3Params* p
         params->layout != SHAOBO_FA3_LAYOUT_BHSD) {
         return 0;
     }
-    return dq_accum_bytes(params);
+    // dQ accumulator, then the dK/dV accumulators of split tiles
+    size_t total = 0;
+    const size_t dq = dq_accum_bytes(params);
+    if (dq == 0 || !add_ok(dq, dkv_accum_bytes(params), &total)) return 0;
+    return total;
 }
 
 extern "C" size_t shaobo_fa3_bwd_dkv_workspace_bytes(const ShaoboFa3Params* params) {

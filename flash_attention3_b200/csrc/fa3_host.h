@@ -37,13 +37,27 @@ bool fused_shape_ok(const ShaoboFa3Params* p);
 // overflow or unsupported shape.
 size_t dq_accum_bytes(const ShaoboFa3Params* p);
 
+// How many CTAs share one key tile.  Shapes with fewer (batch x KV head x key tile) units than a
+// B200 has SMs would leave most of the chip idle, so each tile's query steps are cut into up to 8
+// parts whose dK/dV partial sums meet in fp32 accumulators.  The decision depends on the
+// parameters only (148 SMs assumed), so the workspace formula and the launch always agree.
+// The deterministic path never splits.
+constexpr int kSplitSmCount = 148;
+int split_factor(const ShaoboFa3Params* p);
+
+// Bytes of the two fp32 accumulators [B,Hkv,S,D] (dK then dV) that split tiles add into; 0 when
+// split_factor is 1.
+size_t dkv_accum_bytes(const ShaoboFa3Params* p);
+
 // Carving of the caller's workspace by shaobo_fa3_bwd_v2:
 //   [0, dq_accum)                fp32 dQ accumulator
+//   [dq_accum, +dkv_accum)       fp32 dK and dV accumulators (only when tiles are split)
 //   [delta_offset, +rows*4)      delta, used when softmax_d is NULL
 //   [sidecar_offset, +rows*12)   packed sidecar
 // Each region starts on a 256-byte boundary.
 struct V2Workspace {
     size_t dq_accum_bytes = 0;
+    size_t dkv_accum_bytes = 0;
     size_t delta_offset = 0;
     size_t sidecar_offset = 0;
     size_t total_bytes = 0;

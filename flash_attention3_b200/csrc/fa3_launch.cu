@@ -136,59 +136,82 @@ int finish(const ShaoboFa3Params* p, bool sync) {
 // ------------------------------------------------------------------ delta
 template <typename T, int D>
 void launch_delta_t(const void* dout, const void* out, const float* aux0, const float* aux1,
-                    float* delta, float* sidecar, float* zero_rows, int64_t rows, bool lse,
-                    float scale_log2, cudaStream_t st) {
+                    float* delta, float* sidecar, float* zero_rows, float* zero_extra,
+                    int64_t zero_extra_bytes, int64_t rows, bool lse, float scale_log2,
+                    cudaStream_t st) {
     constexpr int kRowsPerBlock = 8 * (32 / (D / 8));
     int64_t blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
     const int64_t cap = int64_t(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
+    float4* ze = reinterpret_cast<float4*>(zero_extra);
+    const int64_t ze_n = zero_extra != nullptr ? zero_extra_bytes / 16 : 0;
     if (lse) {
         delta_sidecar_kernel<T, D, true><<<int(blocks), 256, 0, st>>>(
             static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
-            zero_rows, rows, scale_log2);
+            zero_rows, ze, ze_n, rows, scale_log2);
     } else {
         delta_sidecar_kernel<T, D, false><<<int(blocks), 256, 0, st>>>(
             static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
-            zero_rows, rows, scale_log2);
+            zero_rows, ze, ze_n, rows, scale_log2);
     }
 }
 
 void launch_delta(const ShaoboFa3Params* p, const void* dout, const void* out, const float* aux0,
-                  const float* aux1, float* delta, float* sidecar, float* zero_rows, bool lse) {
+                  const float* aux1, float* delta, float* sidecar, float* zero_rows, bool lse,
+                  float* zero_extra = nullptr, int64_t zero_extra_bytes = 0) {
     const int64_t rows = int64_t(p->batch) * p->num_heads_q * p->seqlen_q;
     const float scale_log2 = p->softmax_scale * kLog2E;
     cudaStream_t st = stream_of(p);
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     if (p->head_dim_qk == 128) {
-        if (bf) launch_delta_t<__nv_bfloat16, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, st);
-        else launch_delta_t<__half, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, st);
+        if (bf) launch_delta_t<__nv_bfloat16, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, st);
+        else launch_delta_t<__half, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, st);
     } else {
-        if (bf) launch_delta_t<__nv_bfloat16, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, st);
-        else launch_delta_t<__half, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, st);
+        if (bf) launch_delta_t<__nv_bfloat16, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, st);
+        else launch_delta_t<__half, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, st);
     }
 }
 
 // ---------------------------------------------------------------- convert
-void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq) {
-    const int64_t n8 = int64_t(p->batch) * p->num_heads_q * p->seqlen_q * p->head_dim_qk / 8;
-    int64_t blocks = (n8 + 255) / 256;
+// dq = T(scale * dq_accum); with split tiles also dk = T(dk_accum), dv = T(dv_accum) (the scale of
+// dK was applied before its partial sums were added).
+void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
+                    const float* dkv_accum = nullptr, void* dk = nullptr, void* dv = nullptr) {
+    ConvertSegments seg{};
+    seg.src[0] = accum;
+    seg.dst[0] = dq;
+    seg.n_vec8[0] = int64_t(p->batch) * p->num_heads_q * p->seqlen_q * p->head_dim_qk / 8;
+    seg.scale[0] = p->softmax_scale;
+    seg.count = 1;
+    int64_t total = seg.n_vec8[0];
+    if (dkv_accum != nullptr) {
+        const int64_t n = int64_t(p->batch) * p->num_heads_kv * p->seqlen_k * p->head_dim_qk;
+        seg.src[1] = dkv_accum;
+        seg.dst[1] = dk;
+        seg.src[2] = dkv_accum + n;
+        seg.dst[2] = dv;
+        seg.n_vec8[1] = seg.n_vec8[2] = n / 8;
+        seg.scale[1] = seg.scale[2] = 1.0f;
+        seg.count = 3;
+        total += 2 * (n / 8);
+    }
+    int64_t blocks = (total / seg.count + 255) / 256;
     const int64_t cap = int64_t(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
     cudaStream_t st = stream_of(p);
     if (p->dtype == SHAOBO_FA3_DTYPE_BF16) {
-        dq_convert_kernel<__nv_bfloat16><<<int(blocks), 256, 0, st>>>(
-            accum, static_cast<__nv_bfloat16*>(dq), n8, p->softmax_scale);
+        dq_convert_kernel<__nv_bfloat16><<<int(blocks), 256, 0, st>>>(seg);
     } else {
-        dq_convert_kernel<__half><<<int(blocks), 256, 0, st>>>(accum, static_cast<__half*>(dq), n8,
-                                                              p->softmax_scale);
+        dq_convert_kernel<__half><<<int(blocks), 256, 0, st>>>(seg);
     }
 }
 
 // ------------------------------------------------------- fused / dKV kernel
 template <typename T, int D, bool kCausal, bool kWithDq, typename TOut>
 int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                   const CUtensorMap& mdo, const CUtensorMap& mdq, const FusedArgs& args,
-                   int blocks, cudaStream_t st) {
+                   const CUtensorMap& mdo, const CUtensorMap& mdq, const CUtensorMap& mdk,
+                   const CUtensorMap& mdv, const FusedArgs& args, int blocks, cudaStream_t st) {
     auto kernel = fused_bwd_kernel<T, D, kCausal, kWithDq, TOut>;
     static DeviceOnce configured;  // per instantiation and device
     if (!configured.done()) {
@@ -198,35 +221,38 @@ int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
         }
         configured.mark();
     }
-    kernel<<<blocks, FusedCfg<D>::kThreads, FusedCfg<D>::kSmemBytes, st>>>(mq, mk, mv, mdo, mdq, args);
+    kernel<<<blocks, FusedCfg<D>::kThreads, FusedCfg<D>::kSmemBytes, st>>>(mq, mk, mv, mdo, mdq, mdk, mdv, args);
     return SHAOBO_FA3_STATUS_SUCCESS;
 }
 
 template <typename T, bool kWithDq, typename TOut>
 int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorMap& mk,
                    const CUtensorMap& mv, const CUtensorMap& mdo, const CUtensorMap& mdq,
-                   const FusedArgs& args, int blocks) {
+                   const CUtensorMap& mdk, const CUtensorMap& mdv, const FusedArgs& args, int blocks) {
     cudaStream_t st = stream_of(p);
     if (p->head_dim_qk == 128) {
-        return p->causal ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st)
-                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st);
+        return p->causal ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st)
+                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st);
     }
-    return p->causal ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st)
-                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st);
+    return p->causal ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st)
+                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st);
 }
 
 // with_dq: fused five-GEMM kernel writing dK/dV in the input dtype and adding
 // dQ into dq_accum (already zero).  !with_dq: four-GEMM dK/dV kernel with fp32
 // outputs (split path).
+// dkv_accum non-null (fused path only): key tiles are split split_factor(p) ways and their
+// dK/dV partial sums are reduce-added into dkv_accum ([dK | dV], fp32, already zero) instead of
+// being written to dk / dv.
 int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
                  const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
-                 bool with_dq, bool dkv_f32 = false) {
+                 bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr) {
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const uint64_t d = uint64_t(p->head_dim_qk);
     const uint64_t q_rows = uint64_t(p->batch) * p->num_heads_q * p->seqlen_q;
     const uint64_t kv_rows = uint64_t(p->batch) * p->num_heads_kv * p->seqlen_k;
-    CUtensorMap mq, mk, mv, mdo, mdq;
+    CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
     if (!make_map(&mq, type, 2, q, q_rows, d, 64, 128) ||
         !make_map(&mk, type, 2, k, kv_rows, d, 64, 128) ||
         !make_map(&mv, type, 2, v, kv_rows, d, 64, 128) ||
@@ -239,6 +265,16 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
         }
     } else {
         mdq = mq;  // unused by the kernel
+    }
+    const int n_split = (with_dq && dkv_accum != nullptr) ? split_factor(p) : 1;
+    if (n_split > 1) {
+        if (!make_map(&mdk, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dkv_accum, kv_rows, d, 32, 32) ||
+            !make_map(&mdv, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dkv_accum + kv_rows * d, kv_rows, d, 32, 32)) {
+            return SHAOBO_FA3_STATUS_HIP_ERROR;
+        }
+    } else {
+        mdk = mq;  // unused by the kernel
+        mdv = mq;
     }
     const int n_tiles = p->seqlen_k / 128;
     const int bh = p->batch * p->num_heads_kv;
@@ -257,19 +293,20 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     args.order_mode = plan.mode;
     args.order_width = plan.width;
     args.head_major = plan.head_major;
-    const int64_t blocks64 = int64_t(n_tiles) * bh;
+    args.n_split = n_split;
+    const int64_t blocks64 = int64_t(n_tiles) * bh * n_split;
     if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
     const int blocks = int(blocks64);
     if (with_dq) {
-        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks)
-                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, args, blocks);
+        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks)
+                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks);
     }
     if (dkv_f32) {
-        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks)
-                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks);
+        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks)
+                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks);
     }
-    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks)
-              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, args, blocks);
+    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks)
+              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks);
 }
 
 // -------------------------------------------------------------- dQ kernel
@@ -442,18 +479,23 @@ extern "C" int shaobo_fa3_bwd_fused5(const void* dout, const void* q, const void
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     if (!stage_params_ok(params)) return SHAOBO_FA3_STATUS_UNSUPPORTED;
-    const size_t need = dq_accum_bytes(params);
-    if (need == 0 || params->workspace == nullptr || params->workspace_bytes < need) {
+    const size_t dq_bytes = dq_accum_bytes(params);
+    const size_t dkv_bytes = dkv_accum_bytes(params);
+    const size_t need = dq_bytes + dkv_bytes;
+    if (dq_bytes == 0 || params->workspace == nullptr || params->workspace_bytes < need) {
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     float* accum = static_cast<float*>(params->workspace);
+    float* dkv_accum = dkv_bytes != 0
+                           ? reinterpret_cast<float*>(static_cast<uint8_t*>(params->workspace) + dq_bytes)
+                           : nullptr;
     if (cudaMemsetAsync(accum, 0, need, stream_of(params)) != cudaSuccess) {
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
     int status = launch_fused(params, dout, q, k, v, static_cast<const float*>(packed_sidecar),
-                              accum, dk, dv, true);
+                              accum, dk, dv, true, false, dkv_accum);
     if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
-    launch_convert(params, accum, dq);
+    launch_convert(params, accum, dq, dkv_accum, dk, dv);
     return finish(params, params->sync_after_launch != 0);
 }
 
@@ -536,12 +578,15 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
         // delta + sidecar, and the dQ accumulator is cleared in the same pass
         cudaStream_t st = stream_of(&launch);
         stage_mark(0, st);
+        float* dkv_accum = ws.dkv_accum_bytes != 0
+                               ? reinterpret_cast<float*>(base + ws.dq_accum_bytes)
+                               : nullptr;
         launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
-                     sidecar, accum, true);
+                     sidecar, accum, true, dkv_accum, int64_t(ws.dkv_accum_bytes));
         stage_mark(1, st);
-        status = launch_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true);
+        status = launch_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true, false, dkv_accum);
         stage_mark(2, st);
-        if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq);
+        if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq, dkv_accum, dk, dv);
         stage_mark(3, st);
     } else {
         // Atomic-free split path (bitwise reproducible): dK/dV by the four-GEMM

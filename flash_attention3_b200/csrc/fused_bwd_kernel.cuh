@@ -21,7 +21,7 @@
 // issuer and TMEM owner; warps 4-7 and 8-11 = two softmax / dS warpgroups (thread
 // j of each owns TMEM lane j = key j; the first takes queries 0-63 of the tile,
 // the second queries 64-127); warps 12-15 = dQ drain warpgroup.  Registers are
-// re-split with setmaxnreg (96 / 120 / 120 / 168 per thread at D=128).  All hand-offs go
+// re-split with setmaxnreg (96 / 112 / 112 / 176 per thread at D=128).  All hand-offs go
 // through mbarriers; every wait is bounded and a time-out raises an error flag
 // instead of hanging.
 //
@@ -91,6 +91,8 @@ struct FusedArgs {
     int order_mode;        // see cta_order.h
     int order_width;
     int head_major;        // block index = head * n_tiles + tile slot (else tile slot * heads + head)
+    int n_split;           // > 1: the steps of one key tile are cut into n_split CTAs whose dK/dV
+                           // partial sums are reduce-added (fp32) into accumulators
 };
 
 __host__ __device__ inline int remap_k_tile(int physical, int count, int mode, int width) {
@@ -132,8 +134,8 @@ struct FusedCfg {
 
     // setmaxnreg split per warpgroup (producer+MMA / softmax x2 / drain); sums to <= 512
     static constexpr int kRegsControl = 96;
-    static constexpr int kRegsCompute = D == 128 ? 120 : 136;
-    static constexpr int kRegsDrain = D == 128 ? 168 : 136;
+    static constexpr int kRegsCompute = D == 128 ? 112 : 136;
+    static constexpr int kRegsDrain = D == 128 ? 176 : 136;
     static_assert(kRegsControl + 2 * kRegsCompute + kRegsDrain <= 512, "register file over-committed");
 
     static constexpr int kTmemCols = 512;
@@ -205,7 +207,8 @@ template <typename T, int D, bool kCausal, bool kWithDq, typename TOut>
 __global__ void __launch_bounds__(512, 1)
 fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                 const __grid_constant__ CUtensorMap tm_dqacc, const FusedArgs a) {
+                 const __grid_constant__ CUtensorMap tm_dqacc, const __grid_constant__ CUtensorMap tm_dkacc,
+                 const __grid_constant__ CUtensorMap tm_dvacc, const FusedArgs a) {
     using C = FusedCfg<D>;
     constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -222,19 +225,26 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int bh_count = a.batch * a.heads_kv;
     // head_major: all key tiles of one (batch, KV head) are adjacent block indices, so the
     // CTAs that run at the same time share Q/dO tiles and dQ-accumulator lines in L2.
-    const int tile_slot = a.head_major ? int(blockIdx.x) % n_tiles : int(blockIdx.x) / bh_count;
-    const int bhi = a.head_major ? int(blockIdx.x) / n_tiles : int(blockIdx.x) % bh_count;
+    const int part = a.n_split > 1 ? int(blockIdx.x) % a.n_split : 0;
+    const int blk = a.n_split > 1 ? int(blockIdx.x) / a.n_split : int(blockIdx.x);
+    const int tile_slot = a.head_major ? blk % n_tiles : blk / bh_count;
+    const int bhi = a.head_major ? blk / n_tiles : blk % bh_count;
     const int kt = remap_k_tile(tile_slot, n_tiles, a.order_mode, a.order_width);
     const int b = bhi / a.heads_kv;
     const int kvh = bhi % a.heads_kv;
     const int group = a.heads_q / a.heads_kv;
     const int q_begin = kCausal ? kt : 0;
     const int steps_per_head = n_tiles - q_begin;
-    const int n_steps = group * steps_per_head;
-    const bool misaligned = (sbase & 1023u) != 0;
+    // this CTA's share of the tile's steps (all of them unless the tile is split)
+    const int total_steps = group * steps_per_head;
+    const int t_begin = a.n_split > 1 ? int((long long)total_steps * part / a.n_split) : 0;
+    const int t_end = a.n_split > 1 ? int((long long)total_steps * (part + 1) / a.n_split) : total_steps;
+    const int n_steps = t_end - t_begin;
+    // "misaligned" also covers a CTA without work: every role is skipped, set-up and teardown still run
+    const bool misaligned = (sbase & 1023u) != 0 || n_steps == 0;
 
     if (threadIdx.x == 0) {
-        if (misaligned) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
+        if ((sbase & 1023u) != 0) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
         ptx::mbar_init(bar(kKvFull), 1);
         for (int s = 0; s < 2; ++s) {
             ptx::mbar_init(bar(kQFull + s), 1);
@@ -266,7 +276,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // Query tiles are visited in ascending order starting at the diagonal (causal) or at a
     // per-CTA rotation (non-causal), so that CTAs of one head that run together add into
     // different dQ tiles at any moment.
-    auto step_coords = [&](int t, int& hq, int& qt) {
+    auto step_coords = [&](int t_local, int& hq, int& qt) {
+        const int t = t_begin + t_local;
         const int g = t / steps_per_head;
         hq = kvh * group + g;
         const int r = t - g * steps_per_head;
@@ -566,7 +577,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
             // ---- epilogue: the first warpgroup writes dK (scaled), the second dV
             if (ok) ok = warp_wait(bar(kDkvFull), 0, abort_flag);
-            if (ok) {
+            if (ok && a.n_split <= 1) {
                 ptx::tc_fence_after();
                 const int64_t row = int64_t(b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile + j;
                 TOut* dst = reinterpret_cast<TOut*>(half == 0 ? a.dk : a.dv) + row * D;
@@ -661,6 +672,54 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         pending = true;
                     }
                     if (warp == 12) DBG_TOCK(17);
+                }
+                if (a.n_split > 1) {
+                    // Split tile: this CTA holds partial dK / dV sums.  Once every MMA has completed,
+                    // add them (dK scaled) into the fp32 accumulators with the same staging + TMA
+                    // reduce-add machinery that dQ uses; warp w handles key rows [32w, 32w+32).
+                    if (warp_wait(bar(kDkvFull), 0, abort_flag)) {
+                        ptx::tc_fence_after();
+                        const int row0 = (b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile + qd * 32;
+#pragma unroll 1
+                        for (int which = 0; which < 2; ++which) {
+                            const void* map = which == 0 ? static_cast<const void*>(&tm_dkacc)
+                                                         : static_cast<const void*>(&tm_dvacc);
+                            const float mul = which == 0 ? a.scale : 1.0f;
+                            const uint32_t col0 = tl + (which == 0 ? C::kColDK : C::kColDV);
+#pragma unroll 1
+                            for (int c = 0; c < D / 32; c += 2) {
+                                if (pending) {
+                                    if (lane == 0) ptx::bulk_wait_group_read<0>();
+                                    __syncwarp();
+                                }
+#pragma unroll
+                                for (int bx = 0; bx < 2; ++bx) {
+                                    uint32_t r[32];
+                                    ptx::tmem_ld32(col0 + (c + bx) * 32, r);
+                                    ptx::tmem_ld_wait();
+                                    const uint32_t row_addr = stage + bx * C::kStageBoxBytes + lane * 128;
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) {
+                                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
+                                                     ::"r"(row_addr + ((e ^ (lane & 7)) << 4)),
+                                                       "f"(__uint_as_float(r[4 * e]) * mul),
+                                                       "f"(__uint_as_float(r[4 * e + 1]) * mul),
+                                                       "f"(__uint_as_float(r[4 * e + 2]) * mul),
+                                                       "f"(__uint_as_float(r[4 * e + 3]) * mul)
+                                                     : "memory");
+                                    }
+                                }
+                                ptx::fence_proxy_async_smem();
+                                __syncwarp();
+                                if (lane == 0) {
+                                    ptx::tma_reduce_add_2d(map, stage, c * 32, row0);
+                                    ptx::tma_reduce_add_2d(map, stage + C::kStageBoxBytes, c * 32 + 32, row0);
+                                    ptx::bulk_commit_group();
+                                }
+                                pending = true;
+                            }
+                        }
+                    }
                 }
                 if (lane == 0) ptx::bulk_wait_group<0>();
             }

@@ -48,7 +48,8 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
 // row is owned by D/8 adjacent lanes that each fetch one 16-byte vector of dO
 // and of O, so a warp reads 512 contiguous bytes per tensor per instruction.
 // When zero_rows is non-null the same lanes also clear the row of the fp32 dQ
-// accumulator (row pitch D floats), which saves a separate memset pass.
+// accumulator (row pitch D floats), which saves a separate memset pass; a
+// second, unrelated range (zero_extra) can be cleared by the same launch.
 //
 // Algorithmic HBM bytes per row: 2*D*2 (dO, O) + 4 (aux0) [+4 aux1] + 4
 // (delta) + 12 (sidecar) [+ 4*D when clearing the accumulator].
@@ -57,7 +58,8 @@ __global__ void __launch_bounds__(256)
 delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
                      const float* __restrict__ aux0, const float* __restrict__ aux1,
                      float* __restrict__ delta, float* __restrict__ sidecar,
-                     float* __restrict__ zero_rows, int64_t rows, float scale_log2) {
+                     float* __restrict__ zero_rows, float4* __restrict__ zero_extra,
+                     int64_t zero_extra_vec4, int64_t rows, float scale_log2) {
     constexpr int kLanesPerRow = D / 8;
     constexpr int kRowsPerWarp = 32 / kLanesPerRow;
     const int lane = threadIdx.x & 31;
@@ -65,6 +67,12 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
     const int col = lane % kLanesPerRow;
     const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+
+    // optional second region to clear (the fp32 dK/dV accumulators of split tiles)
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_extra_vec4;
+         i += int64_t(gridDim.x) * blockDim.x) {
+        zero_extra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 
     for (int64_t row = warp * kRowsPerWarp + sub; row < rows; row += warps * kRowsPerWarp) {
         const uint4 a = ld_stream_16B(dout + row * D + col * 8);
@@ -109,13 +117,29 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
     }
 }
 
-// dq[i] = T(scale * accum[i]).  8 elements per thread: 32 B in, 16 B out.
+// Up to three (fp32 accumulator -> storage dtype) conversions in one launch:
+// dQ (scaled) always; dK and dV as well when tiles were split.
+struct ConvertSegments {
+    const float* src[3];
+    void* dst[3];
+    int64_t n_vec8[3];
+    float scale[3];
+    int count;
+};
+
+// dst[i] = T(scale * accum[i]).  8 elements per thread: 32 B in, 16 B out.
 // Algorithmic HBM bytes per element: 4 read + 2 written.
 template <typename T>
 __global__ void __launch_bounds__(256)
-dq_convert_kernel(const float* __restrict__ accum, T* __restrict__ dq, int64_t n_vec8,
-                  float scale) {
+dq_convert_kernel(const ConvertSegments seg) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+#pragma unroll
+    for (int sgi = 0; sgi < 3; ++sgi) {
+    if (sgi >= seg.count) break;
+    const float* __restrict__ accum = seg.src[sgi];
+    T* __restrict__ dq = static_cast<T*>(seg.dst[sgi]);
+    const int64_t n_vec8 = seg.n_vec8[sgi];
+    const float scale = seg.scale[sgi];
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec8; i += stride) {
         const uint4 lo = ld_stream_16B(accum + i * 8);
         const uint4 hi = ld_stream_16B(accum + i * 8 + 4);
@@ -125,6 +149,7 @@ dq_convert_kernel(const float* __restrict__ accum, T* __restrict__ dq, int64_t n
         o.z = pack2<T>(__uint_as_float(hi.x) * scale, __uint_as_float(hi.y) * scale);
         o.w = pack2<T>(__uint_as_float(hi.z) * scale, __uint_as_float(hi.w) * scale);
         reinterpret_cast<uint4*>(dq)[i] = o;
+    }
     }
 }
 

@@ -51,9 +51,14 @@ def test_workspace_formula():
     p = _params()
     rows = 1 * 4 * 1024
     accum = rows * 128 * 4
-    expected = accum + ((rows * 4 + 255) // 256) * 256 + rows * 12
+    # 8 key tiles x 2 KV heads = 16 units < 148 SMs: tiles are split, so fp32 dK/dV accumulators are added
+    dkv_accum = 2 * (1 * 2 * 1024 * 128 * 4)
+    expected = accum + dkv_accum + ((rows * 4 + 255) // 256) * 256 + rows * 12
     assert lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p)) == expected
-    assert lib.shaobo_fa3_bwd_fused5_workspace_bytes(ctypes.byref(p)) == accum
+    assert lib.shaobo_fa3_bwd_fused5_workspace_bytes(ctypes.byref(p)) == accum + dkv_accum
+    # the deterministic path never splits and needs no dK/dV accumulators
+    pd = _params(deterministic=1)
+    assert lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(pd)) == expected - dkv_accum
     # linear in S (the reference's per-K-tile partials were quadratic)
     p2 = _params(seqlen_q=8192, seqlen_k=8192, batch=16, num_heads_q=32, num_heads_kv=32)
     w = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p2))
@@ -61,7 +66,7 @@ def test_workspace_formula():
     # monotone in every dimension, 256-byte aligned sub-buffers
     prev = 0
     for s in (128, 256, 512, 1024):
-        cur = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(_params(seqlen_q=s, seqlen_k=s)))
+        cur = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(_params(seqlen_q=s, seqlen_k=s, deterministic=1)))
         assert cur > prev
         prev = cur
     for d in (64, 128):

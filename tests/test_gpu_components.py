@@ -118,12 +118,25 @@ def test_v2_deterministic_is_bitwise_reproducible(dtype, d, hq, hkv, s, causal):
             assert np.array_equal(runs[0][name], r[name]), name
 
 
-def test_dkv_dv_of_fused_path_are_bitwise_reproducible():
-    """Only dQ goes through fp32 reduce-adds; dK and dV of the fused path have a fixed order."""
-    prob = helpers.Problem(1, 4, 2, 512, 128, "bf16", True, seed=61)
+def test_dk_dv_of_fused_path_are_bitwise_reproducible_when_tiles_are_not_split():
+    """With at least 148 (batch x KV head x key tile) units a key tile belongs to one CTA: only dQ
+    goes through fp32 reduce-adds, dK and dV have a fixed summation order."""
+    prob = helpers.Problem(2, 16, 16, 640, 64, "bf16", True, seed=61)   # 2*16*5 = 160 units
     a, b = helpers.run_v2(prob), helpers.run_v2(prob)
+    helpers.assert_parity(a, prob)
     for name in ("dk", "dv", "delta"):
         assert np.array_equal(a[name], b[name])
+
+
+@pytest.mark.parametrize("b,hq,hkv,s,d,dtype,causal", [
+    (1, 4, 4, 2048, 128, "fp16", True),    # 64 units -> 4-way split
+    (1, 1, 1, 1024, 128, "fp16", True),    # 8 units -> 8-way split, some parts empty
+    (1, 8, 2, 384, 64, "bf16", False),     # GQA: the steps of 4 query heads are cut across CTAs
+    (1, 2, 2, 128, 128, "bf16", True),     # a single step per tile: 1 working part, the rest idle
+])
+def test_split_tiles_match_the_oracle(b, hq, hkv, s, d, dtype, causal):
+    prob = helpers.Problem(b, hq, hkv, s, d, dtype, causal, seed=71 + s)
+    helpers.assert_parity(helpers.run_v2(prob), prob)
 
 
 def test_component_status_codes():

@@ -70,8 +70,9 @@ def test_default_scale_matches_explicit_scale():
     a = helpers.run_v2(prob, pass_scale=True)
     b = helpers.run_v2(prob, pass_scale=False)  # softmax_scale_is_set = 0 -> 1/sqrt(D)
     helpers.assert_parity(b, prob)
-    for name in ("dk", "dv", "delta"):
-        assert np.array_equal(a[name], b[name])
+    assert np.array_equal(a["delta"], b["delta"])
+    for name in ("dq", "dk", "dv"):  # small shape: tiles are split, sums go through fp32 reduce-adds
+        assert golden.compare(a[name], b[name])["rel_l2"] < 2e-3
 
 
 def test_softmax_d_is_optional():
@@ -87,8 +88,9 @@ def test_softmax_d_is_optional():
     code = lib.shaobo_fa3_bwd_v2(vp(x["dout"]), vp(x["q"]), vp(x["k"]), vp(x["v"]), vp(x["out"]), vp(x["lse"]),
                                  vp(dq), vp(dk), vp(dv), None, ctypes.byref(p))
     assert code == 0
-    # delta then lives in the workspace right after the dQ accumulator
-    off = 256 * 128 * 4
+    # delta then lives in the workspace right after the dQ accumulator and the dK/dV accumulators
+    # (2 key tiles < 148 SMs, so tiles are split)
+    off = 256 * 128 * 4 + 2 * 256 * 128 * 4
     delta = ws[off:off + 256 * 4].view(torch.float32).cpu().numpy()
     assert golden.delta_pass(golden.compare(delta, prob.ref["delta"][0, 0]))
     assert golden.check_gradient(helpers.host(dq), prob.ref["dq"], "fp16")["pass"]

@@ -47,12 +47,13 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
         for attempt in range(2):
             got = _call_noalloc(prob, x)
             assert got["code"] == capi.STATUS_SUCCESS and got["device_error"] == 0, (attempt, got["code"])
-            # dK, dV and delta have a fixed summation order: identical bits
-            for name in ("dk", "dv", "delta"):
-                assert np.array_equal(got[name], expected[name]), (attempt, name)
-            # dQ goes through fp32 reduce-adds whose order may differ from run to run
-            m = golden.compare(got["dq"], expected["dq"])
-            assert m["nonfinite"] == 0 and m["rel_l2"] <= golden.GRAD_REL_L2 and m["max_abs"] <= golden.GRAD_MAX_ABS, m
+            # delta has a fixed summation order: identical bits
+            assert np.array_equal(got["delta"], expected["delta"]), attempt
+            # dQ (and, on shapes this small, dK and dV) go through fp32 reduce-adds whose order
+            # may differ from run to run
+            for name in ("dq", "dk", "dv"):
+                m = golden.compare(got[name], expected[name])
+                assert m["nonfinite"] == 0 and m["rel_l2"] <= golden.GRAD_REL_L2 and m["max_abs"] <= golden.GRAD_MAX_ABS, (name, m)
             # and it meets the same gates against the CPU oracle as every other path
             helpers.assert_parity(got, prob, f"noalloc attempt {attempt}")
 
