@@ -113,21 +113,31 @@ size_t dq_accum_bytes(const ShaoboFa3Params* p) {
     return out;
 }
 
-int split_factor(const ShaoboFa3Params* p) {
-    if (!fused_shape_ok(p) || p->deterministic != 0) return 1;
+SplitPlan split_plan(const ShaoboFa3Params* p) {
+    SplitPlan plan;
+    if (!fused_shape_ok(p) || p->deterministic != 0) return plan;
     const long long tiles = p->seqlen_k / kSequenceAlignment;
-    const long long blocks = tiles * p->batch * p->num_heads_kv;
-    if (blocks >= kSplitSmCount) return 1;
+    const long long heads = (long long)p->batch * p->num_heads_kv;
+    if (tiles * heads >= kSplitSmCount) return plan;
     const long long group = p->num_heads_q / p->num_heads_kv;
-    long long f = 2LL * kSplitSmCount / blocks;   // aim at about two CTAs per SM
-    const long long longest = group * tiles;      // steps of the heaviest key tile
-    if (f > longest) f = longest;
-    if (f > 8) f = 8;
-    return f < 1 ? 1 : int(f);
+    const long long longest = group * tiles;  // steps of the heaviest key tile
+    for (long long chunk = 1; chunk < longest; ++chunk) {
+        long long per_head = 0;
+        for (long long kt = 0; kt < tiles; ++kt) {
+            const long long steps = group * (p->causal != 0 ? tiles - kt : tiles);
+            per_head += (steps + chunk - 1) / chunk;
+        }
+        if (per_head * heads <= kSplitSmCount) {
+            plan.chunk_steps = int(chunk);
+            plan.chunks_per_head = int(per_head);
+            return plan;
+        }
+    }
+    return plan;  // a chunk as long as the heaviest tile is no split at all
 }
 
 size_t dkv_accum_bytes(const ShaoboFa3Params* p) {
-    if (split_factor(p) <= 1) return 0;
+    if (split_plan(p).chunk_steps == 0) return 0;
     size_t n = size_t(p->batch), out = 0;
     if (!mul_ok(n, size_t(p->num_heads_kv), &n) || !mul_ok(n, size_t(p->seqlen_k), &n) ||
         !mul_ok(n, size_t(p->head_dim_qk), &n) || !mul_ok(n, 2 * sizeof(float), &n) ||

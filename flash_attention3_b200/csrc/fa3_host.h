@@ -37,16 +37,21 @@ bool fused_shape_ok(const ShaoboFa3Params* p);
 // overflow or unsupported shape.
 size_t dq_accum_bytes(const ShaoboFa3Params* p);
 
-// How many CTAs share one key tile.  Shapes with fewer (batch x KV head x key tile) units than a
-// B200 has SMs would leave most of the chip idle, so each tile's query steps are cut into up to 8
-// parts whose dK/dV partial sums meet in fp32 accumulators.  The decision depends on the
-// parameters only (148 SMs assumed), so the workspace formula and the launch always agree.
-// The deterministic path never splits.
+// Splitting of key tiles on small problems.  Shapes with fewer (batch x KV head x key tile) units
+// than a B200 has SMs would leave most of the chip idle, so the query steps of every key tile are
+// cut into chunks of `chunk_steps` steps, one CTA per chunk, whose dK/dV partial sums meet in fp32
+// accumulators.  The chunk size is the smallest one whose CTA count still fits one wave of 148
+// SMs.  The decision depends on the parameters only, so the workspace formula and the launch
+// always agree.  The deterministic path never splits.
 constexpr int kSplitSmCount = 148;
-int split_factor(const ShaoboFa3Params* p);
+struct SplitPlan {
+    int chunk_steps = 0;      // 0 = no splitting
+    int chunks_per_head = 0;  // CTAs per (batch, KV head)
+};
+SplitPlan split_plan(const ShaoboFa3Params* p);
 
 // Bytes of the two fp32 accumulators [B,Hkv,S,D] (dK then dV) that split tiles add into; 0 when
-// split_factor is 1.
+// tiles are not split.
 size_t dkv_accum_bytes(const ShaoboFa3Params* p);
 
 // Carving of the caller's workspace by shaobo_fa3_bwd_v2:

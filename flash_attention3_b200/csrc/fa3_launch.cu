@@ -199,11 +199,19 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
     const int64_t cap = int64_t(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    cudaStream_t st = stream_of(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(blocks));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream_of(p);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;  // the kernel waits for the GEMM kernel itself
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (p->dtype == SHAOBO_FA3_DTYPE_BF16) {
-        dq_convert_kernel<__nv_bfloat16><<<int(blocks), 256, 0, st>>>(seg);
+        cudaLaunchKernelEx(&cfg, dq_convert_kernel<__nv_bfloat16>, seg);
     } else {
-        dq_convert_kernel<__half><<<int(blocks), 256, 0, st>>>(seg);
+        cudaLaunchKernelEx(&cfg, dq_convert_kernel<__half>, seg);
     }
 }
 
@@ -211,7 +219,8 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
 template <typename T, int D, bool kCausal, bool kWithDq, typename TOut>
 int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                    const CUtensorMap& mdo, const CUtensorMap& mdq, const CUtensorMap& mdk,
-                   const CUtensorMap& mdv, const FusedArgs& args, int blocks, cudaStream_t st) {
+                   const CUtensorMap& mdv, const FusedArgs& args, int blocks, cudaStream_t st,
+                   bool pdl) {
     auto kernel = fused_bwd_kernel<T, D, kCausal, kWithDq, TOut>;
     static DeviceOnce configured;  // per instantiation and device
     if (!configured.done()) {
@@ -221,32 +230,47 @@ int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
         }
         configured.mark();
     }
-    kernel<<<blocks, FusedCfg<D>::kThreads, FusedCfg<D>::kSmemBytes, st>>>(mq, mk, mv, mdo, mdq, mdk, mdv, args);
+    // Programmatic dependent launch: set-up and the first loads overlap the tail of the kernel in front
+    // (the delta kernel); the kernel itself waits before it touches what that kernel writes.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(FusedCfg<D>::kThreads);
+    cfg.dynamicSmemBytes = FusedCfg<D>::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, mdo, mdq, mdk, mdv, args) != cudaSuccess) {
+        return SHAOBO_FA3_STATUS_HIP_ERROR;
+    }
     return SHAOBO_FA3_STATUS_SUCCESS;
 }
 
 template <typename T, bool kWithDq, typename TOut>
 int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorMap& mk,
                    const CUtensorMap& mv, const CUtensorMap& mdo, const CUtensorMap& mdq,
-                   const CUtensorMap& mdk, const CUtensorMap& mdv, const FusedArgs& args, int blocks) {
+                   const CUtensorMap& mdk, const CUtensorMap& mdv, const FusedArgs& args, int blocks,
+                   bool pdl) {
     cudaStream_t st = stream_of(p);
     if (p->head_dim_qk == 128) {
-        return p->causal ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st)
-                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st);
+        return p->causal ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
+                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
     }
-    return p->causal ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st)
-                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st);
+    return p->causal ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
+                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
 }
 
 // with_dq: fused five-GEMM kernel writing dK/dV in the input dtype and adding
 // dQ into dq_accum (already zero).  !with_dq: four-GEMM dK/dV kernel with fp32
 // outputs (split path).
-// dkv_accum non-null (fused path only): key tiles are split split_factor(p) ways and their
+// dkv_accum non-null (fused path only): key tiles are split as split_plan(p) says and their
 // dK/dV partial sums are reduce-added into dkv_accum ([dK | dV], fp32, already zero) instead of
 // being written to dk / dv.
 int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
                  const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
-                 bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr) {
+                 bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr, bool pdl = false) {
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const uint64_t d = uint64_t(p->head_dim_qk);
@@ -266,8 +290,8 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     } else {
         mdq = mq;  // unused by the kernel
     }
-    const int n_split = (with_dq && dkv_accum != nullptr) ? split_factor(p) : 1;
-    if (n_split > 1) {
+    const SplitPlan split = (with_dq && dkv_accum != nullptr) ? split_plan(p) : SplitPlan{};
+    if (split.chunk_steps > 0) {
         if (!make_map(&mdk, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dkv_accum, kv_rows, d, 32, 32) ||
             !make_map(&mdv, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dkv_accum + kv_rows * d, kv_rows, d, 32, 32)) {
             return SHAOBO_FA3_STATUS_HIP_ERROR;
@@ -293,20 +317,21 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     args.order_mode = plan.mode;
     args.order_width = plan.width;
     args.head_major = plan.head_major;
-    args.n_split = n_split;
-    const int64_t blocks64 = int64_t(n_tiles) * bh * n_split;
+    args.chunk_steps = split.chunk_steps;
+    args.chunks_per_head = split.chunks_per_head;
+    const int64_t blocks64 = split.chunk_steps > 0 ? int64_t(split.chunks_per_head) * bh : int64_t(n_tiles) * bh;
     if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
     const int blocks = int(blocks64);
     if (with_dq) {
-        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks)
-                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks);
+        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
+                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
     }
     if (dkv_f32) {
-        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks)
-                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks);
+        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
+                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
     }
-    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks)
-              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks);
+    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
+              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
 }
 
 // -------------------------------------------------------------- dQ kernel
@@ -584,7 +609,7 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
         launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
                      sidecar, accum, true, dkv_accum, int64_t(ws.dkv_accum_bytes));
         stage_mark(1, st);
-        status = launch_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true, false, dkv_accum);
+        status = launch_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true, false, dkv_accum, true);
         stage_mark(2, st);
         if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq, dkv_accum, dk, dv);
         stage_mark(3, st);

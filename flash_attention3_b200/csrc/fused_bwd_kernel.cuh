@@ -91,8 +91,9 @@ struct FusedArgs {
     int order_mode;        // see cta_order.h
     int order_width;
     int head_major;        // block index = head * n_tiles + tile slot (else tile slot * heads + head)
-    int n_split;           // > 1: the steps of one key tile are cut into n_split CTAs whose dK/dV
-                           // partial sums are reduce-added (fp32) into accumulators
+    int chunk_steps;       // > 0: the steps of a key tile are cut into chunks of this many steps, one CTA
+                           // per chunk, and dK/dV partial sums are reduce-added (fp32) into accumulators
+    int chunks_per_head;   // number of chunks of one (batch, KV head) when chunk_steps > 0
 };
 
 __host__ __device__ inline int remap_k_tile(int physical, int count, int mode, int width) {
@@ -145,6 +146,8 @@ struct FusedCfg {
     static constexpr int kColDP = 2 * D + 128;
     static constexpr int kColDQ = D == 128 ? kColDP : kColDP + 128;
     static_assert(kColDQ + D <= kTmemCols, "tensor-memory ledger exceeds 512 columns");
+    // split-tile epilogue: 4 warps x (dK + dV) x D/32 boxes of 4 KiB are staged over the dead Q/dO/dS^T buffers
+    static_assert(4 * 2 * (D / 32) * kStageBoxBytes <= kOffStage - kOffQ, "epilogue scratch does not fit");
 };
 
 enum Bar : int {
@@ -225,20 +228,36 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int bh_count = a.batch * a.heads_kv;
     // head_major: all key tiles of one (batch, KV head) are adjacent block indices, so the
     // CTAs that run at the same time share Q/dO tiles and dQ-accumulator lines in L2.
-    const int part = a.n_split > 1 ? int(blockIdx.x) % a.n_split : 0;
-    const int blk = a.n_split > 1 ? int(blockIdx.x) / a.n_split : int(blockIdx.x);
-    const int tile_slot = a.head_major ? blk % n_tiles : blk / bh_count;
-    const int bhi = a.head_major ? blk / n_tiles : blk % bh_count;
-    const int kt = remap_k_tile(tile_slot, n_tiles, a.order_mode, a.order_width);
+    const bool split = a.chunk_steps > 0;
+    const int group = a.heads_q / a.heads_kv;
+    int kt, bhi, t_begin_split = 0;
+    if (!split) {
+        const int blk = int(blockIdx.x);
+        const int tile_slot = a.head_major ? blk % n_tiles : blk / bh_count;
+        bhi = a.head_major ? blk / n_tiles : blk % bh_count;
+        kt = remap_k_tile(tile_slot, n_tiles, a.order_mode, a.order_width);
+    } else {
+        // chunk list of one head: key tile 0 first (most steps), each tile cut into ceil(steps/chunk) chunks
+        bhi = int(blockIdx.x) / a.chunks_per_head;
+        int rest = int(blockIdx.x) % a.chunks_per_head;
+        kt = 0;
+        while (true) {
+            const int steps = group * (kCausal ? n_tiles - kt : n_tiles);
+            const int chunks = (steps + a.chunk_steps - 1) / a.chunk_steps;
+            if (rest < chunks) break;
+            rest -= chunks;
+            ++kt;
+        }
+        t_begin_split = rest * a.chunk_steps;
+    }
     const int b = bhi / a.heads_kv;
     const int kvh = bhi % a.heads_kv;
-    const int group = a.heads_q / a.heads_kv;
     const int q_begin = kCausal ? kt : 0;
     const int steps_per_head = n_tiles - q_begin;
     // this CTA's share of the tile's steps (all of them unless the tile is split)
     const int total_steps = group * steps_per_head;
-    const int t_begin = a.n_split > 1 ? int((long long)total_steps * part / a.n_split) : 0;
-    const int t_end = a.n_split > 1 ? int((long long)total_steps * (part + 1) / a.n_split) : total_steps;
+    const int t_begin = t_begin_split;
+    const int t_end = split ? min(total_steps, t_begin + a.chunk_steps) : total_steps;
     const int n_steps = t_end - t_begin;
     // "misaligned" also covers a CTA without work: every role is skipped, set-up and teardown still run
     const bool misaligned = (sbase & 1023u) != 0 || n_steps == 0;
@@ -272,6 +291,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // The kernel behind this one (dQ convert) may begin to launch; it waits for our completion itself.
+    ptx::launch_dependents();
 
     // Query tiles are visited in ascending order starting at the diagonal (causal) or at a
     // per-CTA rotation (non-causal), so that CTAs of one head that run together add into
@@ -440,6 +461,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             uint32_t ppk[32];
             const float* side_base = a.sidecar;
             float s0 = 0.f, s1 = 1.f, s2 = 0.f;
+            // the sidecar comes from the delta kernel, which may still be running (programmatic launch);
+            // Q, K, V, dO are inputs of the call, so the TMA and MMA warps did not have to wait
+            ptx::grid_dependency_wait();
             if (half == 0) {
                 int hq, qt;
                 step_coords(0, hq, qt);
@@ -577,7 +601,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
             // ---- epilogue: the first warpgroup writes dK (scaled), the second dV
             if (ok) ok = warp_wait(bar(kDkvFull), 0, abort_flag);
-            if (ok && a.n_split <= 1) {
+            if (ok && !split) {
                 ptx::tc_fence_after();
                 const int64_t row = int64_t(b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile + j;
                 TOut* dst = reinterpret_cast<TOut*>(half == 0 ? a.dk : a.dv) + row * D;
@@ -620,6 +644,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 const uint32_t tl = tmem + (uint32_t(qd * 32) << 16);
                 const uint32_t stage = sbase + C::kOffStage + qd * 2 * C::kStageBoxBytes;
                 bool pending = false;
+                // the accumulators are cleared by the delta kernel: do not add into them before it is done
+                ptx::grid_dependency_wait();
                 DBG_TICK();
 #pragma unroll 1
                 for (int t = 0; t < n_steps; ++t) {
@@ -673,51 +699,48 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     }
                     if (warp == 12) DBG_TOCK(17);
                 }
-                if (a.n_split > 1) {
-                    // Split tile: this CTA holds partial dK / dV sums.  Once every MMA has completed,
-                    // add them (dK scaled) into the fp32 accumulators with the same staging + TMA
-                    // reduce-add machinery that dQ uses; warp w handles key rows [32w, 32w+32).
+                if (split) {
+                    // Split tile: this CTA holds partial dK / dV sums.  Once every MMA has completed the
+                    // Q / dO / dS^T buffers are dead; warp w stages its 32 key rows of dK (scaled) and
+                    // dV there as [32 rows][32 fp32] boxes and adds them into the fp32 accumulators
+                    // with TMA reduce-adds, all in flight together.
                     if (warp_wait(bar(kDkvFull), 0, abort_flag)) {
                         ptx::tc_fence_after();
                         const int row0 = (b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile + qd * 32;
-#pragma unroll 1
-                        for (int which = 0; which < 2; ++which) {
-                            const void* map = which == 0 ? static_cast<const void*>(&tm_dkacc)
-                                                         : static_cast<const void*>(&tm_dvacc);
+                        constexpr int kBoxesPerTensor = D / 32;
+                        const uint32_t scratch = sbase + C::kOffQ + qd * (2 * kBoxesPerTensor * C::kStageBoxBytes);
+#pragma unroll
+                        for (int bx = 0; bx < 2 * kBoxesPerTensor; ++bx) {
+                            const int which = bx / kBoxesPerTensor;  // 0: dK, 1: dV
+                            const int c = bx % kBoxesPerTensor;
                             const float mul = which == 0 ? a.scale : 1.0f;
-                            const uint32_t col0 = tl + (which == 0 ? C::kColDK : C::kColDV);
-#pragma unroll 1
-                            for (int c = 0; c < D / 32; c += 2) {
-                                if (pending) {
-                                    if (lane == 0) ptx::bulk_wait_group_read<0>();
-                                    __syncwarp();
-                                }
+                            uint32_t r[32];
+                            ptx::tmem_ld32(tl + (which == 0 ? C::kColDK : C::kColDV) + c * 32, r);
+                            ptx::tmem_ld_wait();
+                            const uint32_t row_addr = scratch + bx * C::kStageBoxBytes + lane * 128;
 #pragma unroll
-                                for (int bx = 0; bx < 2; ++bx) {
-                                    uint32_t r[32];
-                                    ptx::tmem_ld32(col0 + (c + bx) * 32, r);
-                                    ptx::tmem_ld_wait();
-                                    const uint32_t row_addr = stage + bx * C::kStageBoxBytes + lane * 128;
-#pragma unroll
-                                    for (int e = 0; e < 8; ++e) {
-                                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
-                                                     ::"r"(row_addr + ((e ^ (lane & 7)) << 4)),
-                                                       "f"(__uint_as_float(r[4 * e]) * mul),
-                                                       "f"(__uint_as_float(r[4 * e + 1]) * mul),
-                                                       "f"(__uint_as_float(r[4 * e + 2]) * mul),
-                                                       "f"(__uint_as_float(r[4 * e + 3]) * mul)
-                                                     : "memory");
-                                    }
-                                }
-                                ptx::fence_proxy_async_smem();
-                                __syncwarp();
-                                if (lane == 0) {
-                                    ptx::tma_reduce_add_2d(map, stage, c * 32, row0);
-                                    ptx::tma_reduce_add_2d(map, stage + C::kStageBoxBytes, c * 32 + 32, row0);
-                                    ptx::bulk_commit_group();
-                                }
-                                pending = true;
+                            for (int e = 0; e < 8; ++e) {
+                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
+                                             ::"r"(row_addr + ((e ^ (lane & 7)) << 4)),
+                                               "f"(__uint_as_float(r[4 * e]) * mul),
+                                               "f"(__uint_as_float(r[4 * e + 1]) * mul),
+                                               "f"(__uint_as_float(r[4 * e + 2]) * mul),
+                                               "f"(__uint_as_float(r[4 * e + 3]) * mul)
+                                             : "memory");
                             }
+                        }
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+#pragma unroll
+                            for (int bx = 0; bx < 2 * kBoxesPerTensor; ++bx) {
+                                const int which = bx / kBoxesPerTensor;
+                                const int c = bx % kBoxesPerTensor;
+                                ptx::tma_reduce_add_2d(which == 0 ? static_cast<const void*>(&tm_dkacc)
+                                                                  : static_cast<const void*>(&tm_dvacc),
+                                                       scratch + bx * C::kStageBoxBytes, c * 32, row0);
+                            }
+                            ptx::bulk_commit_group();
                         }
                     }
                 }

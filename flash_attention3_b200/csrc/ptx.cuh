@@ -203,6 +203,18 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(bool bf16, int m, int n, b
            (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialisation
+// attribute may start while its predecessor in the stream still runs; grid_dependency_wait()
+// blocks until the predecessor has completed and its writes are visible, and
+// launch_dependents() lets the successor's CTAs begin to launch.  Both are no-ops for a kernel
+// launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Per-warpgroup register re-allocation (all 128 threads of the warpgroup).
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {

@@ -67,6 +67,8 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
     const int col = lane % kLanesPerRow;
     const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    // let the GEMM kernel behind this one start its set-up (it waits before it reads our outputs)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // optional second region to clear (the fp32 dK/dV accumulators of split tiles)
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_extra_vec4;
@@ -132,6 +134,8 @@ struct ConvertSegments {
 template <typename T>
 __global__ void __launch_bounds__(256)
 dq_convert_kernel(const ConvertSegments seg) {
+    // launched programmatically behind the GEMM kernel: wait until all of it has completed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
 #pragma unroll
     for (int sgi = 0; sgi < 3; ++sgi) {
