@@ -24,13 +24,20 @@ enum CtaOrderMode : int {
     kOrderSerpentine = 2,
 };
 
+#ifndef FA3B200_DQ_L2_BUDGET_MB
+#define FA3B200_DQ_L2_BUDGET_MB 64
+#endif
+// dQ-accumulator bytes that the CTAs running at the same time may spread over (about half of L2)
+constexpr long long kDqL2BudgetBytes = (long long)(FA3B200_DQ_L2_BUDGET_MB) << 20;
+
 struct CtaOrderPlan {
     int mode = kOrderHeavyFirst;
     int width = 1;
-    // Block index = head * n_tiles + tile slot when set, tile slot * heads + head otherwise.
-    // Head-major keeps the CTAs that run together on a few heads, so their Q/dO tiles and
-    // dQ-accumulator lines stay in L2; tile-major is the globally heaviest-first order.
-    int head_major = 0;
+    // Heads are taken in groups of `head_group`; inside a group the order is tile slot major, head
+    // minor: block = (group * n_tiles + tile slot) * head_group + head in group.  head_group = all
+    // heads is the globally heaviest-first order; a small group keeps the CTAs that run together on
+    // a few heads, so their Q/dO tiles and the dQ-accumulator lines they add into stay in L2.
+    int head_group = 1;
     long long makespan = 0;  // modelled, in query-tile steps
 };
 
@@ -48,13 +55,17 @@ inline int host_remap_k_tile(int physical, int count, int mode, int width) {
 // on `sms` machines; cost of a block = steps of its logical key tile + a fixed
 // prologue/epilogue charge.
 inline long long modelled_makespan(int n_tiles, int bh_count, int group, bool causal, int sms,
-                                   int mode, int width, bool head_major = false) {
+                                   int mode, int width, int head_group = 0) {
+    if (head_group <= 0 || head_group > bh_count) head_group = bh_count;
     std::priority_queue<long long, std::vector<long long>, std::greater<long long>> free_at;
     for (int i = 0; i < sms; ++i) free_at.push(0);
     long long makespan = 0;
     const long long blocks = (long long)n_tiles * bh_count;
+    const long long per_group = (long long)n_tiles * head_group;
     for (long long idx = 0; idx < blocks; ++idx) {
-        const int physical = head_major ? int(idx % n_tiles) : int(idx / bh_count);
+        const long long hg = idx / per_group;
+        const int heads_here = int(std::min<long long>(head_group, bh_count - hg * head_group));
+        const int physical = int((idx - hg * per_group) / heads_here);
         const int kt = host_remap_k_tile(physical, n_tiles, mode, width);
         const long long cost = 1 + (long long)group * (causal ? n_tiles - kt : n_tiles);
         const long long start = free_at.top();
@@ -65,8 +76,11 @@ inline long long modelled_makespan(int n_tiles, int bh_count, int group, bool ca
     return makespan;
 }
 
-inline CtaOrderPlan plan_cta_order(int n_tiles, int bh_count, int group, bool causal, int sms) {
+// dq_bytes_per_head: bytes of fp32 dQ accumulator that the CTAs of one (batch, KV head) add into.
+inline CtaOrderPlan plan_cta_order(int n_tiles, int bh_count, int group, bool causal, int sms,
+                                   long long dq_bytes_per_head = 0) {
     CtaOrderPlan best;
+    best.head_group = bh_count;
     best.makespan = modelled_makespan(n_tiles, bh_count, group, causal, sms, kOrderHeavyFirst, 1);
     const long long heavy_first = best.makespan;
     const int max_width = std::min(n_tiles, 16);
@@ -79,16 +93,22 @@ inline CtaOrderPlan plan_cta_order(int n_tiles, int bh_count, int group, bool ca
             best.makespan = m;
         }
     }
-    // Prefer the cache-friendly head-major order (measured: +14 % throughput on S=4096..8192
-    // MHA shapes) unless the model says its makespan is more than 8 % longer than
-    // plain heaviest-first.
-    const long long hm =
-        modelled_makespan(n_tiles, bh_count, group, causal, sms, kOrderHeavyFirst, 1, true);
-    if (hm * 100 <= heavy_first * 108) {
-        best.mode = kOrderHeavyFirst;
-        best.width = 1;
-        best.head_major = 1;
-        best.makespan = hm;
+    // Cache-friendly grouping: as many heads per group as keep the group's dQ accumulator within
+    // about half of the 126 MB L2 (measured: up to +14 % throughput on S=4096..8192 shapes),
+    // unless the model says the makespan gets more than 8 % longer than plain heaviest-first.
+    if (dq_bytes_per_head > 0) {
+        long long g = (kDqL2BudgetBytes) / dq_bytes_per_head;
+        if (g < 1) g = 1;
+        if (g < bh_count) {
+            const long long hm = modelled_makespan(n_tiles, bh_count, group, causal, sms,
+                                                   kOrderHeavyFirst, 1, int(g));
+            if (hm * 100 <= heavy_first * 108) {
+                best.mode = kOrderHeavyFirst;
+                best.width = 1;
+                best.head_group = int(g);
+                best.makespan = hm;
+            }
+        }
     }
     return best;
 }

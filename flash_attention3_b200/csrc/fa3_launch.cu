@@ -75,14 +75,14 @@ int sm_count() {
     return n;
 }
 
-CtaOrderPlan cached_plan(int n_tiles, int bh, int group, bool causal, int sms) {
+CtaOrderPlan cached_plan(int n_tiles, int bh, int group, bool causal, int sms, long long dq_bytes) {
     static std::mutex mu;
-    static std::map<std::tuple<int, int, int, bool, int>, CtaOrderPlan> cache;
-    const auto key = std::make_tuple(n_tiles, bh, group, causal, sms);
+    static std::map<std::tuple<int, int, int, bool, int, long long>, CtaOrderPlan> cache;
+    const auto key = std::make_tuple(n_tiles, bh, group, causal, sms, dq_bytes);
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
-    const CtaOrderPlan plan = plan_cta_order(n_tiles, bh, group, causal, sms);
+    const CtaOrderPlan plan = plan_cta_order(n_tiles, bh, group, causal, sms, dq_bytes);
     cache[key] = plan;
     return plan;
 }
@@ -303,7 +303,10 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     const int n_tiles = p->seqlen_k / 128;
     const int bh = p->batch * p->num_heads_kv;
     const int group = p->num_heads_q / p->num_heads_kv;
-    const CtaOrderPlan plan = cached_plan(n_tiles, bh, group, p->causal != 0, sm_count());
+    // bytes of dQ accumulator behind one (batch, KV head): only the fused path adds into it
+    const long long dq_bytes_per_head =
+        with_dq ? (long long)group * p->seqlen_q * p->head_dim_qk * 4 : 0;
+    const CtaOrderPlan plan = cached_plan(n_tiles, bh, group, p->causal != 0, sm_count(), dq_bytes_per_head);
     FusedArgs args;
     args.sidecar = sidecar;
     args.dk = dk;
@@ -316,7 +319,7 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     args.scale_log2 = p->softmax_scale * kLog2E;
     args.order_mode = plan.mode;
     args.order_width = plan.width;
-    args.head_major = plan.head_major;
+    args.head_group = plan.head_group;
     args.chunk_steps = split.chunk_steps;
     args.chunks_per_head = split.chunks_per_head;
     const int64_t blocks64 = split.chunk_steps > 0 ? int64_t(split.chunks_per_head) * bh : int64_t(n_tiles) * bh;

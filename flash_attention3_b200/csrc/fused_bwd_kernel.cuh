@@ -90,7 +90,7 @@ struct FusedArgs {
     float scale_log2;
     int order_mode;        // see cta_order.h
     int order_width;
-    int head_major;        // block index = head * n_tiles + tile slot (else tile slot * heads + head)
+    int head_group;        // heads per scheduling group: block = (group * n_tiles + tile slot) * head_group + head
     int chunk_steps;       // > 0: the steps of a key tile are cut into chunks of this many steps, one CTA
                            // per chunk, and dK/dV partial sums are reduce-added (fp32) into accumulators
     int chunks_per_head;   // number of chunks of one (batch, KV head) when chunk_steps > 0
@@ -226,15 +226,17 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // ---- which tile is ours ------------------------------------------------
     const int n_tiles = a.seqlen / C::kTile;
     const int bh_count = a.batch * a.heads_kv;
-    // head_major: all key tiles of one (batch, KV head) are adjacent block indices, so the
-    // CTAs that run at the same time share Q/dO tiles and dQ-accumulator lines in L2.
     const bool split = a.chunk_steps > 0;
     const int group = a.heads_q / a.heads_kv;
     int kt, bhi, t_begin_split = 0;
     if (!split) {
-        const int blk = int(blockIdx.x);
-        const int tile_slot = a.head_major ? blk % n_tiles : blk / bh_count;
-        bhi = a.head_major ? blk / n_tiles : blk % bh_count;
+        // groups of head_group heads; inside a group tile slot major, head minor (see cta_order.h)
+        const int per_group = n_tiles * a.head_group;
+        const int hg = int(blockIdx.x) / per_group;
+        const int rem = int(blockIdx.x) - hg * per_group;
+        const int heads_here = min(a.head_group, bh_count - hg * a.head_group);
+        const int tile_slot = rem / heads_here;
+        bhi = hg * a.head_group + (rem - tile_slot * heads_here);
         kt = remap_k_tile(tile_slot, n_tiles, a.order_mode, a.order_width);
     } else {
         // chunk list of one head: key tile 0 first (most steps), each tile cut into ceil(steps/chunk) chunks

@@ -14,12 +14,13 @@ extern "C" int remap(int p, int n, int mode, int w) { return fa3b200::host_remap
 extern "C" long long makespan(int n, int bh, int g, int causal, int sms, int mode, int w) {
     return fa3b200::modelled_makespan(n, bh, g, causal != 0, sms, mode, w);
 }
-extern "C" long long makespan_hm(int n, int bh, int g, int causal, int sms) {
-    return fa3b200::modelled_makespan(n, bh, g, causal != 0, sms, 0, 1, true);
+extern "C" long long makespan_hg(int n, int bh, int g, int causal, int sms, int head_group) {
+    return fa3b200::modelled_makespan(n, bh, g, causal != 0, sms, 0, 1, head_group);
 }
-extern "C" void plan(int n, int bh, int g, int causal, int sms, int* mode, int* width, long long* ms, int* hm) {
-    auto p = fa3b200::plan_cta_order(n, bh, g, causal != 0, sms);
-    *mode = p.mode; *width = p.width; *ms = p.makespan; *hm = p.head_major;
+extern "C" void plan(int n, int bh, int g, int causal, int sms, long long dq_bytes, int* mode, int* width,
+                     long long* ms, int* hg) {
+    auto p = fa3b200::plan_cta_order(n, bh, g, causal != 0, sms, dq_bytes);
+    *mode = p.mode; *width = p.width; *ms = p.makespan; *hg = p.head_group;
 }
 '''
 
@@ -33,7 +34,7 @@ def lib(tmp_path_factory):
                     str(ROOT / "flash_attention3_b200/csrc"), str(d / "w.cpp"), "-o", str(so)], check=True)
     lib = ctypes.CDLL(str(so))
     lib.makespan.restype = ctypes.c_longlong
-    lib.makespan_hm.restype = ctypes.c_longlong
+    lib.makespan_hg.restype = ctypes.c_longlong
     return lib
 
 
@@ -48,17 +49,20 @@ def test_plan_never_worse_than_heavy_first(lib):
     for n in (1, 8, 16, 32, 64):
         for bh in (1, 4, 16, 64, 200):
             for g in (1, 4):
-                mode, width, ms, hm = ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong(), ctypes.c_int()
-                lib.plan(n, bh, g, 1, 148, ctypes.byref(mode), ctypes.byref(width), ctypes.byref(ms), ctypes.byref(hm))
+                mode, width, ms, hg = ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong(), ctypes.c_int()
+                dq_bytes = g * n * 128 * 128 * 4  # fp32 dQ accumulator behind one KV head at D=128
+                lib.plan(n, bh, g, 1, 148, ctypes.c_longlong(dq_bytes), ctypes.byref(mode), ctypes.byref(width),
+                         ctypes.byref(ms), ctypes.byref(hg))
                 base = lib.makespan(n, bh, g, 1, 148, 0, 1)
-                # head-major may be chosen for cache locality at a modelled cost of at most 8 %
+                # heads may be grouped for cache locality at a modelled cost of at most 8 %
                 assert ms.value * 100 <= base * 108
-                if not hm.value:
+                assert 1 <= hg.value <= bh
+                if hg.value == bh:
                     assert ms.value <= base
-                if hm.value:
-                    assert ms.value == lib.makespan_hm(n, bh, g, 1, 148)
-                else:
                     assert ms.value == lib.makespan(n, bh, g, 1, 148, mode.value, width.value)
+                else:
+                    assert ms.value == lib.makespan_hg(n, bh, g, 1, 148, hg.value)
+                    assert hg.value * dq_bytes <= 64 << 20 or hg.value == 1  # kDqL2BudgetBytes
                 total = bh * sum(1 + g * (n - k) for k in range(n))
                 assert ms.value * 148 >= total  # cannot beat perfect balance
 
