@@ -472,6 +472,10 @@ extern "C" int shaobo_fa3_b200_debug_cycles(long long* host_out, int clear) {
     }
     return 0;
 }
+extern "C" int shaobo_fa3_b200_debug_stamps(long long* host_out) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    return cudaMemcpyFromSymbol(host_out, g_debug_stamps, sizeof(long long) * 3 * 4 * 16) == cudaSuccess ? 0 : -1;
+}
 extern "C" int shaobo_fa3_b200_debug_dump(float* host_out) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     return cudaMemcpyFromSymbol(host_out, g_debug_dump, sizeof(float) * 3 * 128 * 128) == cudaSuccess ? 0 : -1;

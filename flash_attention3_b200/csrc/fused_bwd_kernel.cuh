@@ -66,14 +66,16 @@ __device__ int g_device_error = 0;
 // first step of block 0, and per-role cycle counters of block 0.
 __device__ float g_debug_dump[3 * 128 * 128];
 __device__ long long g_debug_cycles[64];
+__device__ long long g_debug_stamps[3][4][16];   // [role][step-8][event]
+#define DBG_STAMPS_DECL() long long dbg_stamp[4][16]; for (int a_ = 0; a_ < 4; ++a_) for (int b_ = 0; b_ < 16; ++b_) dbg_stamp[a_][b_] = 0
+#define DBG_STAMP(ev) do { if (blockIdx.x == 0 && t >= 8 && t < 12) dbg_stamp[t - 8][ev] = clock64(); } while (0)
+#define DBG_STAMPS_FLUSH(role) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) for (int a_ = 0; a_ < 4; ++a_) for (int b_ = 0; b_ < 16; ++b_) g_debug_stamps[role][a_][b_] = dbg_stamp[a_][b_]; } while (0)
 #define DBG_TICK() long long dbg_t0 = clock64()
-#define DBG_TOCK(slot)                                                        \
-    do {                                                                      \
-        const long long dbg_t1 = clock64();                                   \
-        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_debug_cycles[slot] += dbg_t1 - dbg_t0; \
-        dbg_t0 = dbg_t1;                                                      \
-    } while (0)
+#define DBG_TOCK(slot) do { (void)dbg_t0; } while (0)
 #else
+#define DBG_STAMPS_DECL() do {} while (0)
+#define DBG_STAMP(ev) do {} while (0)
+#define DBG_STAMPS_FLUSH(role) do {} while (0)
 #define DBG_TICK() do {} while (0)
 #define DBG_TOCK(slot) do {} while (0)
 #endif
@@ -334,7 +336,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     step_coords(t, hq, qt);
                     const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile;
                     const int s = t % C::kQStages;
-                    if (!bounded_wait(bar(kQEmpty + s), ((t / C::kQStages) & 1) ^ 1, abort_flag)) break;
+                    if (!bounded_wait<true>(bar(kQEmpty + s), ((t / C::kQStages) & 1) ^ 1, abort_flag)) break;
                     ptx::mbar_arrive_expect_tx(bar(kQFull + s), C::kOperandBytes);
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
@@ -342,7 +344,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                          bar(kQFull + s), bx * 64, q_row);
                     }
                     const int sd = t % C::kDoStages;
-                    if (!bounded_wait(bar(kDoEmpty + sd), ((t / C::kDoStages) & 1) ^ 1, abort_flag)) break;
+                    if (!bounded_wait<true>(bar(kDoEmpty + sd), ((t / C::kDoStages) & 1) ^ 1, abort_flag)) break;
                     ptx::mbar_arrive_expect_tx(bar(kDoFull + sd), C::kOperandBytes);
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
@@ -353,100 +355,122 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
         } else if (!misaligned && warp == 1) {
             // ===================================================== MMA issuer
-            if (lane == 0) {
+            // The whole warp runs this role converged; MMAs and commits elect their lane inside the asm.
+            {
                 constexpr uint32_t kIdSdP = ptx::instr_desc_f16(kBf16, 128, 128, false, false);
                 constexpr uint32_t kIdDkv = ptx::instr_desc_f16(kBf16, 128, D, false, true);
                 constexpr uint32_t kIdDq = ptx::instr_desc_f16(kBf16, 128, D, true, true);
-                auto k_major = [&](uint32_t base, int kk) -> uint64_t {
-                    return ptx::smem_desc_sw128(base + (kk >> 2) * C::kBoxBytes + (kk & 3) * 32, 16, 1024);
-                };
-                auto mn_major = [&](uint32_t base, int kk) -> uint64_t {
-                    return ptx::smem_desc_sw128(base + kk * 2048, C::kBoxBytes, 1024);
-                };
-                const uint32_t sK = sbase + C::kOffK, sV = sbase + C::kOffV, sDS = sbase + C::kOffDS;
+                // Descriptor low words (address >> 4 | LBO) of every operand tile; a K step advances them
+                // by a compile-time constant: K-major +2 per 16 elements inside a box and +box/16 per box,
+                // MN-major +128 per 16 rows.  One constant high word serves every descriptor.
+                constexpr uint32_t kHi = ptx::kDescHiSw128;
+                constexpr uint32_t kBoxStep = C::kBoxBytes >> 4;
+                auto k_step = [](int kk) -> uint32_t { return uint32_t(kk >> 2) * kBoxStep + uint32_t(kk & 3) * 2u; };
+                auto mn_step = [](int kk) -> uint32_t { return uint32_t(kk) * 128u; };
+                const uint32_t loK_k = ptx::desc_lo_k_major(sbase + C::kOffK);
+                const uint32_t loV_k = ptx::desc_lo_k_major(sbase + C::kOffV);
+                const uint32_t loDS_k = ptx::desc_lo_k_major(sbase + C::kOffDS);
+                const uint32_t loK_mn = ptx::desc_lo_mn_major(sbase + C::kOffK, C::kBoxBytes);
+                const uint32_t loDS_mn = ptx::desc_lo_mn_major(sbase + C::kOffDS, C::kBoxBytes);
                 auto sQ = [&](int t) { return sbase + C::kOffQ + (t % C::kQStages) * C::kOperandBytes; };
                 auto sDO = [&](int t) { return sbase + C::kOffDO + (t % C::kDoStages) * C::kOperandBytes; };
                 auto issue_s = [&](int t) {
+                    const uint32_t loQ = ptx::desc_lo_k_major(sQ(t));
+                    ptx::mma_ss_lean<false>(tmem + C::kColS, loK_k, loQ, kHi, kIdSdP);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk)
-                        ptx::mma_ss(tmem + C::kColS, k_major(sK, kk), k_major(sQ(t), kk), kIdSdP, kk > 0);
-                    ptx::tc_commit(bar(kSFull));
+                    for (int kk = 1; kk < D / 16; ++kk)
+                        ptx::mma_ss_lean<true>(tmem + C::kColS, loK_k + k_step(kk), loQ + k_step(kk), kHi, kIdSdP);
+                    ptx::tc_commit_elect(bar(kSFull));
                 };
                 auto issue_dp = [&](int t) {
+                    const uint32_t loDO = ptx::desc_lo_k_major(sDO(t));
+                    ptx::mma_ss_lean<false>(tmem + C::kColDP, loV_k, loDO, kHi, kIdSdP);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk)
-                        ptx::mma_ss(tmem + C::kColDP, k_major(sV, kk), k_major(sDO(t), kk), kIdSdP, kk > 0);
-                    ptx::tc_commit(bar(kDpFull));
+                    for (int kk = 1; kk < D / 16; ++kk)
+                        ptx::mma_ss_lean<true>(tmem + C::kColDP, loV_k + k_step(kk), loDO + k_step(kk), kHi, kIdSdP);
+                    ptx::tc_commit_elect(bar(kDpFull));
                 };
-                bool ok = bounded_wait(bar(kKvFull), 0, abort_flag) &&
-                          bounded_wait(bar(kQFull + 0), 0, abort_flag);
+                bool ok = warp_wait<false>(bar(kKvFull), 0, abort_flag) &&
+                          warp_wait<false>(bar(kQFull + 0), 0, abort_flag);
                 if (ok) {
                     ptx::tc_fence_after();
                     issue_s(0);
-                    ok = bounded_wait(bar(kDoFull + 0), 0, abort_flag);
+                    ok = warp_wait<false>(bar(kDoFull + 0), 0, abort_flag);
                 }
                 if (ok) {
                     ptx::tc_fence_after();
                     issue_dp(0);
                 }
                 DBG_TICK();
+                DBG_STAMPS_DECL();
 #pragma unroll 1
                 for (int t = 0; ok && t < n_steps; ++t) {
                     const bool more = t + 1 < n_steps;
+                    DBG_STAMP(0);
                     // dV += P^T dO.  P^T of queries 0-63 sits on columns [0,32) of the S
                     // region, of queries 64-127 on columns [64,96).
-                    if (!(ok = bounded_wait(bar(kPReady), t & 1, abort_flag))) break;
-                    DBG_TOCK(0);
+                    if (!(ok = warp_wait<false>(bar(kPReady), t & 1, abort_flag))) break;
+                    DBG_STAMP(1);
                     ptx::tc_fence_after();
+                    {
+                        const uint32_t loDO = ptx::desc_lo_mn_major(sDO(t), C::kBoxBytes);
+                        ptx::mma_ts_lean_rt(tmem + C::kColDV, tmem + C::kColS, loDO, kHi, kIdDkv, t > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)
-                        ptx::mma_ts(tmem + C::kColDV, tmem + C::kColS + (kk >> 2) * 64 + (kk & 3) * 8,
-                                    mn_major(sDO(t), kk), kIdDkv, (t > 0 || kk > 0) ? 1u : 0u);
-                    ptx::tc_commit(bar(kDoEmpty + t % C::kDoStages));
+                        for (int kk = 1; kk < 8; ++kk)
+                            ptx::mma_ts_lean<true>(tmem + C::kColDV, tmem + C::kColS + (kk >> 2) * 64 + (kk & 3) * 8,
+                                                   loDO + mn_step(kk), kHi, kIdDkv);
+                    }
+                    ptx::tc_commit_elect(bar(kDoEmpty + t % C::kDoStages));
+                    DBG_STAMP(2);
                     // S(t+1) may overwrite S/P(t): MMAs execute in issue order.
                     if (more) {
-                        if (!(ok = bounded_wait(bar(kQFull + (t + 1) % C::kQStages),
+                        if (!(ok = warp_wait<false>(bar(kQFull + (t + 1) % C::kQStages),
                                                 ((t + 1) / C::kQStages) & 1, abort_flag))) break;
                         ptx::tc_fence_after();
                         issue_s(t + 1);
                     }
-                    DBG_TOCK(1);
+                    DBG_STAMP(3);
                     // dK += dS^T Q
-                    if (!(ok = bounded_wait(bar(kDsReady), t & 1, abort_flag))) break;
-                    DBG_TOCK(2);
+                    if (!(ok = warp_wait<false>(bar(kDsReady), t & 1, abort_flag))) break;
+                    DBG_STAMP(4);
                     ptx::tc_fence_after();
+                    {
+                        const uint32_t loQ = ptx::desc_lo_mn_major(sQ(t), C::kBoxBytes);
+                        ptx::mma_ss_lean_rt(tmem + C::kColDK, loDS_k, loQ, kHi, kIdDkv, t > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)
-                        ptx::mma_ss(tmem + C::kColDK, k_major(sDS, kk), mn_major(sQ(t), kk), kIdDkv,
-                                    (t > 0 || kk > 0) ? 1u : 0u);
-                    ptx::tc_commit(bar(kQEmpty + t % C::kQStages));
+                        for (int kk = 1; kk < 8; ++kk)
+                            ptx::mma_ss_lean<true>(tmem + C::kColDK, loDS_k + k_step(kk), loQ + mn_step(kk), kHi, kIdDkv);
+                    }
+                    ptx::tc_commit_elect(bar(kQEmpty + t % C::kQStages));
                     if (kWithDq) {
                         if (D == 64) {  // own dQ region: wait for the drain of step t-1
-                            if (!(ok = bounded_wait(bar(kDqEmpty), (t & 1) ^ 1, abort_flag))) break;
+                            if (!(ok = warp_wait<false>(bar(kDqEmpty), (t & 1) ^ 1, abort_flag))) break;
                             ptx::tc_fence_after();
                         }
                         // dQ = dS K  (overwrites dP(t) when D = 128: dP(t) was consumed before kDsReady)
+                        ptx::mma_ss_lean<false>(tmem + C::kColDQ, loDS_mn, loK_mn, kHi, kIdDq);
 #pragma unroll
-                        for (int kk = 0; kk < 8; ++kk)
-                            ptx::mma_ss(tmem + C::kColDQ, mn_major(sDS, kk), mn_major(sK, kk), kIdDq, kk > 0);
-                        ptx::tc_commit(bar(kDqFull));
+                        for (int kk = 1; kk < 8; ++kk)
+                            ptx::mma_ss_lean<true>(tmem + C::kColDQ, loDS_mn + mn_step(kk), loK_mn + mn_step(kk), kHi, kIdDq);
+                        ptx::tc_commit_elect(bar(kDqFull));
                     }
-                    ptx::tc_commit(bar(kDsFree));
-                    DBG_TOCK(3);
+                    ptx::tc_commit_elect(bar(kDsFree));
+                    DBG_STAMP(5);
                     if (more) {
-                        if (!(ok = bounded_wait(bar(kDoFull + (t + 1) % C::kDoStages),
+                        if (!(ok = warp_wait<false>(bar(kDoFull + (t + 1) % C::kDoStages),
                                                 ((t + 1) / C::kDoStages) & 1, abort_flag))) break;
-                        DBG_TOCK(4);
+                        DBG_STAMP(6);
                         if (kWithDq && D == 128) {  // dP(t+1) reuses the dQ(t) columns
-                            if (!(ok = bounded_wait(bar(kDqEmpty), t & 1, abort_flag))) break;
+                            if (!(ok = warp_wait<false>(bar(kDqEmpty), t & 1, abort_flag))) break;
                         }
-                        DBG_TOCK(5);
+                        DBG_STAMP(7);
                         ptx::tc_fence_after();
                         issue_dp(t + 1);
-                        DBG_TOCK(6);
+                        DBG_STAMP(8);
                     }
                 }
-                if (ok) ptx::tc_commit(bar(kDkvFull));
+                if (lane == 0) DBG_STAMPS_FLUSH(0);
+                if (ok) ptx::tc_commit_elect(bar(kDkvFull));
             }
         }
     } else if (wg == 1 || wg == 2) {
@@ -476,11 +500,13 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
             bool ok = true;
             DBG_TICK();
+            DBG_STAMPS_DECL();
 #pragma unroll 1
             for (int t = 0; t < n_steps; ++t) {
                 int hq, qt;
                 step_coords(t, hq, qt);
                 const int buf = t & 1;
+                DBG_STAMP(0);
                 const float* negp = stats + buf * 128 + half * 64;
                 const float* delp = stats + 256 + buf * 128 + half * 64;
                 if (half == 0) {
@@ -498,9 +524,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     }
                 }
                 if (!(ok = warp_wait(bar(kStatsFull + buf), (t >> 1) & 1, abort_flag))) break;
-                if (warp == 4) DBG_TOCK(8);
+                DBG_STAMP(1);
                 if (!(ok = warp_wait(bar(kSFull), t & 1, abort_flag))) break;
-                if (warp == 4) DBG_TOCK(9);
+                DBG_STAMP(2);
                 ptx::tc_fence_after();
                 const bool diagonal = kCausal && qt == kt;
                 // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked where query i < key j.
@@ -541,17 +567,16 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     ptx::tmem_ld_wait();
                     softmax_chunk(c, r);
                 }
-                if (warp == 4) DBG_TOCK(18);
+                DBG_STAMP(3);
                 ptx::tmem_st_wait();
-                if (warp == 4) DBG_TOCK(19);
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(bar(kPReady));
-                if (warp == 4) DBG_TOCK(10);
+                DBG_STAMP(4);
                 // ---- dS^T = P^T * (dP^T - delta_i), stored [key][query] in the 128-byte swizzle
                 if (!(ok = warp_wait(bar(kDpFull), t & 1, abort_flag))) break;
-                if (warp == 4) DBG_TOCK(11);
+                DBG_STAMP(5);
                 if (!(ok = warp_wait(bar(kDsFree), (t & 1) ^ 1, abort_flag))) break;
-                if (warp == 4) DBG_TOCK(12);
+                DBG_STAMP(6);
                 ptx::tc_fence_after();
                 const uint32_t ds_row = sbase + C::kOffDS + half * C::kBoxBytes + j * 128;
                 auto ds_chunk = [&](int c, const uint32_t* r) {
@@ -594,13 +619,13 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     ptx::tmem_ld_wait();
                     ds_chunk(c, r);
                 }
-                if (warp == 4) DBG_TOCK(20);
+                DBG_STAMP(7);
                 ptx::fence_proxy_async_smem();
-                if (warp == 4) DBG_TOCK(21);
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(bar(kDsReady));
-                if (warp == 4) DBG_TOCK(13);
+                DBG_STAMP(8);
             }
+            if (warp == 4) DBG_STAMPS_FLUSH(1);
             // ---- epilogue: the first warpgroup writes dK (scaled), the second dV
             if (ok) ok = warp_wait(bar(kDkvFull), 0, abort_flag);
             if (ok && !split) {
@@ -649,13 +674,15 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 // the accumulators are cleared by the delta kernel: do not add into them before it is done
                 ptx::grid_dependency_wait();
                 DBG_TICK();
+                DBG_STAMPS_DECL();
 #pragma unroll 1
                 for (int t = 0; t < n_steps; ++t) {
                     int hq, qt;
                     step_coords(t, hq, qt);
                     const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile + qd * 32;
+                    DBG_STAMP(0);
                     if (!warp_wait(bar(kDqFull), t & 1, abort_flag)) break;
-                    if (warp == 12) DBG_TOCK(16);
+                    DBG_STAMP(1);
                     ptx::tc_fence_after();
                     // pull the whole dQ tile row into registers and hand the columns back at once
                     uint32_t r[D / 32][32];
@@ -664,6 +691,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     ptx::tmem_ld_wait();
                     ptx::tc_fence_before();
                     ptx::mbar_arrive(bar(kDqEmpty));
+                    DBG_STAMP(2);
 #ifdef FA3B200_DEBUG_DUMP
                     if (blockIdx.x == 0 && t == 0)
                         for (int c = 0; c < D / 32; ++c)
@@ -699,8 +727,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #endif
                         pending = true;
                     }
-                    if (warp == 12) DBG_TOCK(17);
+                    DBG_STAMP(3);
                 }
+                if (warp == 12) DBG_STAMPS_FLUSH(2);
                 if (split) {
                     // Split tile: this CTA holds partial dK / dV sums.  Once every MMA has completed the
                     // Q / dO / dS^T buffers are dead; warp w stages its 32 key rows of dK (scaled) and

@@ -110,6 +110,14 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                  ::"r"(bar) : "memory");
 }
+// Whole converged warp: the elected lane arrives on an mbarrier when all MMAs it issued so far
+// have completed (the election is deterministic, so it is the lane the lean MMA forms elect).
+__device__ __forceinline__ void tc_commit_elect(uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar) : "memory");
+}
 // Single thread: D[tmem] (+)= A[smem] * B[smem].
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                        uint32_t idesc, uint32_t accumulate) {
@@ -129,6 +137,81 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// Lean issue forms for the MMA-issuing warp.  They are executed by the whole, converged warp and
+// elect the issuing lane inside the asm block: with a converged warp the descriptors live in uniform
+// registers and one MMA costs a couple of issue slots, whereas a single divergent lane needs many
+// more and is starved by the math warps that share its scheduler (measured: 122 instead of 333
+// cycles per MMA with two busy math warps on the same scheduler).  A descriptor is passed as its two 32-bit
+// halves: `lo` (start address >> 4 | LBO field) advances by a compile-time constant per K step,
+// `hi` (SBO, version, swizzle) is one constant per layout.  kAcc is the accumulate flag.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-B swizzle
+__host__ __device__ constexpr uint32_t desc_lo_k_major(uint32_t addr) { return ((addr & 0x3FFFF) >> 4) | (1u << 16); }
+__host__ __device__ constexpr uint32_t desc_lo_mn_major(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+template <bool kAcc>
+__device__ __forceinline__ void mma_ss_lean(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                            uint32_t idesc) {
+    if (kAcc) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.eq.u32 p, 0, 0;\n\t"
+            "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+            ".reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.u32 p, 0, 0;\n\t"
+            "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+            ".reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc) : "memory");
+    }
+}
+__device__ __forceinline__ void mma_ss_lean_rt(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        ".reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+template <bool kAcc>
+__device__ __forceinline__ void mma_ts_lean(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                            uint32_t idesc) {
+    if (kAcc) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+            "setp.eq.u32 p, 0, 0;\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            ".reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+            "setp.ne.u32 p, 0, 0;\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            ".reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc) : "memory");
+    }
+}
+__device__ __forceinline__ void mma_ts_lean_rt(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        ".reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread l of the warp receives the
