@@ -151,32 +151,37 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 }
             }
         } else if (warp == 1) {
-            if (lane == 0) {
+            // MMA issuer: the whole warp runs the role converged; the lean issue forms and the commits
+            // elect their lane inside the asm (a lone divergent lane is starved by the math warps).
+            {
                 constexpr uint32_t kIdSdP = ptx::instr_desc_f16(kBf16, 128, 128, false, false);
                 constexpr uint32_t kIdDq = ptx::instr_desc_f16(kBf16, 128, D, false, true);
-                auto k_major = [&](uint32_t base, int kk) -> uint64_t {
-                    return ptx::smem_desc_sw128(base + (kk >> 2) * C::kBoxBytes + (kk & 3) * 32, 16, 1024);
-                };
-                auto mn_major = [&](uint32_t base, int kk) -> uint64_t {
-                    return ptx::smem_desc_sw128(base + kk * 2048, C::kBoxBytes, 1024);
-                };
-                const uint32_t sQ = sbase + C::kOffQ, sDO = sbase + C::kOffDO;
+                constexpr uint32_t kHi = ptx::kDescHiSw128;
+                constexpr uint32_t kBoxStep = C::kBoxBytes >> 4;
+                auto k_step = [](int kk) -> uint32_t { return uint32_t(kk >> 2) * kBoxStep + uint32_t(kk & 3) * 2u; };
+                auto mn_step = [](int kk) -> uint32_t { return uint32_t(kk) * 128u; };
+                const uint32_t loQ = ptx::desc_lo_k_major(sbase + C::kOffQ);
+                const uint32_t loDO = ptx::desc_lo_k_major(sbase + C::kOffDO);
                 auto sK = [&](int t) { return sbase + C::kOffK + (t & 1) * C::kOperandBytes; };
                 auto sV = [&](int t) { return sbase + C::kOffV + (t & 1) * C::kOperandBytes; };
                 auto issue_s = [&](int t) {
+                    const uint32_t loK = ptx::desc_lo_k_major(sK(t));
+                    ptx::mma_ss_lean<false>(tmem + C::kColS, loQ, loK, kHi, kIdSdP);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk)
-                        ptx::mma_ss(tmem + C::kColS, k_major(sQ, kk), k_major(sK(t), kk), kIdSdP, kk > 0);
-                    ptx::tc_commit(bar(kDqbSFull));
+                    for (int kk = 1; kk < D / 16; ++kk)
+                        ptx::mma_ss_lean<true>(tmem + C::kColS, loQ + k_step(kk), loK + k_step(kk), kHi, kIdSdP);
+                    ptx::tc_commit_elect(bar(kDqbSFull));
                 };
                 auto issue_dp = [&](int t) {
+                    const uint32_t loV = ptx::desc_lo_k_major(sV(t));
+                    ptx::mma_ss_lean<false>(tmem + C::kColDP, loDO, loV, kHi, kIdSdP);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk)
-                        ptx::mma_ss(tmem + C::kColDP, k_major(sDO, kk), k_major(sV(t), kk), kIdSdP, kk > 0);
-                    ptx::tc_commit(bar(kDqbDpFull));
+                    for (int kk = 1; kk < D / 16; ++kk)
+                        ptx::mma_ss_lean<true>(tmem + C::kColDP, loDO + k_step(kk), loV + k_step(kk), kHi, kIdSdP);
+                    ptx::tc_commit_elect(bar(kDqbDpFull));
                 };
-                bool ok = bounded_wait(bar(kDqbQFull), 0, abort_flag) &&
-                          bounded_wait(bar(kDqbKvFull + 0), 0, abort_flag);
+                bool ok = warp_wait<false>(bar(kDqbQFull), 0, abort_flag) &&
+                          warp_wait<false>(bar(kDqbKvFull + 0), 0, abort_flag);
                 if (ok) {
                     ptx::tc_fence_after();
                     issue_s(0);
@@ -187,21 +192,24 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     const bool more = t + 1 < n_steps;
                     if (more) {
                         // S(t) is in registers: S(t+1) may overwrite it
-                        if (!(ok = bounded_wait(bar(kDqbSFree), t & 1, abort_flag))) break;
-                        if (!(ok = bounded_wait(bar(kDqbKvFull + ((t + 1) & 1)), ((t + 1) >> 1) & 1, abort_flag))) break;
+                        if (!(ok = warp_wait<false>(bar(kDqbSFree), t & 1, abort_flag))) break;
+                        if (!(ok = warp_wait<false>(bar(kDqbKvFull + ((t + 1) & 1)), ((t + 1) >> 1) & 1, abort_flag))) break;
                         ptx::tc_fence_after();
                         issue_s(t + 1);
                     }
-                    if (!(ok = bounded_wait(bar(kDqbDsReady), t & 1, abort_flag))) break;
+                    if (!(ok = warp_wait<false>(bar(kDqbDsReady), t & 1, abort_flag))) break;
                     ptx::tc_fence_after();
+                    {
+                        const uint32_t loK = ptx::desc_lo_mn_major(sK(t), C::kBoxBytes);
+                        ptx::mma_ts_lean_rt(tmem + C::kColDQ, tmem + C::kColDP, loK, kHi, kIdDq, t > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)
-                        ptx::mma_ts(tmem + C::kColDQ, tmem + C::kColDP + kk * 8, mn_major(sK(t), kk), kIdDq,
-                                    (t > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 1; kk < 8; ++kk)
+                            ptx::mma_ts_lean<true>(tmem + C::kColDQ, tmem + C::kColDP + kk * 8, loK + mn_step(kk), kHi, kIdDq);
+                    }
                     if (more) issue_dp(t + 1);  // after dQ(t) in issue order: dS(t) is consumed first
-                    ptx::tc_commit(bar(kDqbKvEmpty + (t & 1)));
+                    ptx::tc_commit_elect(bar(kDqbKvEmpty + (t & 1)));
                 }
-                if (ok) ptx::tc_commit(bar(kDqbDone));
+                if (ok) ptx::tc_commit_elect(bar(kDqbDone));
             }
         } else if (warp >= 4) {
             const int i = threadIdx.x - 128;  // query row inside the tile == TMEM lane
