@@ -1,0 +1,40 @@
+"""The torch.library custom op and the autograd.Function built on the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import golden
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def test_autograd_backward_matches_the_oracle():
+    from flash_attention3_b200 import torch_binding
+    prob = helpers.Problem(1, 4, 2, 256, 64, "bf16", True, seed=301)
+    x = prob.device_inputs()
+    q, k, v = (x[n].clone().requires_grad_(True) for n in ("q", "k", "v"))
+    out = torch_binding.attention(q, k, v, causal=True, softmax_scale=prob.scale)
+    # the torch forward agrees with the oracle's forward (same rounding point)
+    assert golden.compare(helpers.host(out), prob.ref["out"])["rel_l2"] < 3e-3
+    out.backward(x["dout"])
+    torch.cuda.synchronize()
+    for name, grad in (("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
+        m = golden.check_gradient(helpers.host(grad), prob.ref[name], "bf16")
+        assert m["pass"], (name, m)
+
+
+def test_custom_op_is_registered_with_a_fake_implementation():
+    from flash_attention3_b200 import torch_binding  # noqa: F401
+    prob = helpers.Problem(1, 2, 2, 128, 128, "fp16", False, seed=302)
+    x = prob.device_inputs()
+    dq, dk, dv = torch.ops.fa3b200.attention_bwd(x["dout"], x["q"], x["k"], x["v"], x["out"], x["lse"], False,
+                                                 prob.scale, True)
+    assert golden.check_gradient(helpers.host(dq), prob.ref["dq"], "fp16")["pass"]
+    # shape propagation without running the kernel (meta tensors)
+    metas = [t.to("meta") for t in (x["dout"], x["q"], x["k"], x["v"], x["out"], x["lse"])]
+    mq, mk, mv = torch.ops.fa3b200.attention_bwd(*metas, False, prob.scale, False)
+    assert mq.shape == x["q"].shape and mk.shape == x["k"].shape and mv.device.type == "meta"
+    torch.library.opcheck(torch.ops.fa3b200.attention_bwd,
+                          (x["dout"], x["q"], x["k"], x["v"], x["out"], x["lse"], False, prob.scale, True),
+                          test_utils=("test_schema", "test_faketensor"))
