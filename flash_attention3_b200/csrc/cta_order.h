@@ -1,7 +1,7 @@
 // Host-side choice of the CTA launch order for the causal backward.
 //
-// A CTA that owns key tile kt walks (n_tiles - kt) query tiles per query head,
-// so work per CTA falls linearly with kt.  The B200 block scheduler hands the
+// A CTA that owns key tile kt walks the query tiles that see it (n_tiles - kt of
+// them per query head when seqlen_q == seqlen_k), so work per CTA falls with kt.  The B200 block scheduler hands the
 // next block index to whichever SM frees up first, which is greedy list
 // scheduling; the plan below simulates exactly that for a few candidate orders
 // and keeps the one with the smallest modelled makespan.  This plays the role
@@ -16,7 +16,19 @@
 #include <queue>
 #include <vector>
 
+#include "geometry.h"
+
 namespace fa3b200 {
+
+// Tile grid of one head: which query tiles each key tile visits.
+struct TileWork {
+    int n_k_tiles = 0;
+    int n_q_tiles = 0;
+    int causal_off = 0;  // seqlen_k - seqlen_q
+    bool causal = false;
+    int steps(int kt) const { return q_tiles_of_k_tile(kt, n_q_tiles, causal_off, causal); }
+    static TileWork square(int n_tiles, bool causal) { return TileWork{n_tiles, n_tiles, 0, causal}; }
+};
 
 enum CtaOrderMode : int {
     kOrderHeavyFirst = 0,  // key tile index ascending: longest work first (LPT)
@@ -54,8 +66,9 @@ inline int host_remap_k_tile(int physical, int count, int mode, int width) {
 // Greedy list scheduling of blocks 0..n-1 (block = physical tile * bh + head)
 // on `sms` machines; cost of a block = steps of its logical key tile + a fixed
 // prologue/epilogue charge.
-inline long long modelled_makespan(int n_tiles, int bh_count, int group, bool causal, int sms,
+inline long long modelled_makespan(const TileWork& work, int bh_count, int group, int sms,
                                    int mode, int width, int head_group = 0) {
+    const int n_tiles = work.n_k_tiles;
     if (head_group <= 0 || head_group > bh_count) head_group = bh_count;
     std::priority_queue<long long, std::vector<long long>, std::greater<long long>> free_at;
     for (int i = 0; i < sms; ++i) free_at.push(0);
@@ -67,7 +80,7 @@ inline long long modelled_makespan(int n_tiles, int bh_count, int group, bool ca
         const int heads_here = int(std::min<long long>(head_group, bh_count - hg * head_group));
         const int physical = int((idx - hg * per_group) / heads_here);
         const int kt = host_remap_k_tile(physical, n_tiles, mode, width);
-        const long long cost = 1 + (long long)group * (causal ? n_tiles - kt : n_tiles);
+        const long long cost = 1 + (long long)group * work.steps(kt);
         const long long start = free_at.top();
         free_at.pop();
         free_at.push(start + cost);
@@ -76,17 +89,25 @@ inline long long modelled_makespan(int n_tiles, int bh_count, int group, bool ca
     return makespan;
 }
 
+inline long long modelled_makespan(int n_tiles, int bh_count, int group, bool causal, int sms,
+                                   int mode, int width, int head_group = 0) {
+    return modelled_makespan(TileWork::square(n_tiles, causal), bh_count, group, sms, mode, width,
+                             head_group);
+}
+
 // dq_bytes_per_head: bytes of fp32 dQ accumulator that the CTAs of one (batch, KV head) add into.
-inline CtaOrderPlan plan_cta_order(int n_tiles, int bh_count, int group, bool causal, int sms,
+inline CtaOrderPlan plan_cta_order(const TileWork& work, int bh_count, int group, int sms,
                                    long long dq_bytes_per_head = 0) {
+    const int n_tiles = work.n_k_tiles;
+    const bool causal = work.causal;
     CtaOrderPlan best;
     best.head_group = bh_count;
-    best.makespan = modelled_makespan(n_tiles, bh_count, group, causal, sms, kOrderHeavyFirst, 1);
+    best.makespan = modelled_makespan(work, bh_count, group, sms, kOrderHeavyFirst, 1);
     const long long heavy_first = best.makespan;
     const int max_width = std::min(n_tiles, 16);
     for (int width = 2; causal && width <= max_width; ++width) {
         const long long m =
-            modelled_makespan(n_tiles, bh_count, group, causal, sms, kOrderSerpentine, width);
+            modelled_makespan(work, bh_count, group, sms, kOrderSerpentine, width);
         if (m < best.makespan) {
             best.mode = kOrderSerpentine;
             best.width = width;
@@ -102,8 +123,7 @@ inline CtaOrderPlan plan_cta_order(int n_tiles, int bh_count, int group, bool ca
         if (g_max < 1) g_max = 1;
         if (g_max > bh_count - 1) g_max = bh_count - 1;
         for (long long g = 1; g <= g_max; ++g) {
-            const long long m = modelled_makespan(n_tiles, bh_count, group, causal, sms,
-                                                  kOrderHeavyFirst, 1, int(g));
+            const long long m = modelled_makespan(work, bh_count, group, sms, kOrderHeavyFirst, 1, int(g));
             if (m * 100 <= heavy_first * 102) {
                 best.mode = kOrderHeavyFirst;
                 best.width = 1;
@@ -114,6 +134,11 @@ inline CtaOrderPlan plan_cta_order(int n_tiles, int bh_count, int group, bool ca
         }
     }
     return best;
+}
+
+inline CtaOrderPlan plan_cta_order(int n_tiles, int bh_count, int group, bool causal, int sms,
+                                   long long dq_bytes_per_head = 0) {
+    return plan_cta_order(TileWork::square(n_tiles, causal), bh_count, group, sms, dq_bytes_per_head);
 }
 
 }  // namespace fa3b200

@@ -29,12 +29,14 @@
 namespace fa3b200 {
 
 struct DqArgs {
-    const float* sidecar;  // [B,Hq,S,3]
-    void* dq;              // [B,Hq,S,D]
+    const float* sidecar;  // [B,Hq,Sq,3]
+    void* dq;              // [B,Hq,Sq,D] or [B,Sq,Hq,D], see q_strides
+    TensorStrides q_strides;  // element strides of dq
     int batch;
     int heads_q;
     int heads_kv;
-    int seqlen;
+    int seqlen_q;
+    int seqlen_k;
     float scale;
     float scale_log2;
 };
@@ -86,15 +88,18 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kDqbNum);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
-    const int n_tiles = a.seqlen / C::kTile;
+    const int n_q_tiles = tiles_of(a.seqlen_q);
+    const int n_k_tiles = tiles_of(a.seqlen_k);
+    const int causal_off = a.seqlen_k - a.seqlen_q;  // query i sees key j iff j <= i + causal_off
     const int bh_count = a.batch * a.heads_q;
     // heaviest query tiles (most visible keys) are launched first
-    const int qt = kCausal ? n_tiles - 1 - int(blockIdx.x) / bh_count : int(blockIdx.x) / bh_count;
+    const int qt = kCausal ? n_q_tiles - 1 - int(blockIdx.x) / bh_count : int(blockIdx.x) / bh_count;
     const int bhi = int(blockIdx.x) % bh_count;
     const int b = bhi / a.heads_q;
     const int hq = bhi % a.heads_q;
     const int kvh = hq / (a.heads_q / a.heads_kv);
-    const int n_steps = kCausal ? qt + 1 : n_tiles;  // key tiles 0 .. n_steps-1, diagonal last
+    // key tiles 0 .. n_steps-1, the diagonal ones last; 0 when no key is visible (causal, Sq > Sk)
+    const int n_steps = k_tiles_of_q_tile(qt, n_k_tiles, causal_off, kCausal);
     const bool misaligned = (sbase & 1023u) != 0;
 
     if (threadIdx.x == 0) {
@@ -120,11 +125,11 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile;
+    const int q_row = qt * C::kTile;  // row inside the head
 
     if (!misaligned) {
         if (warp == 0) {
-            if (lane == 0) {
+            if (lane == 0 && n_steps > 0) {  // nothing is loaded for a tile that sees no key
                 ptx::prefetch_tensormap(&tm_q);
                 ptx::prefetch_tensormap(&tm_k);
                 ptx::prefetch_tensormap(&tm_v);
@@ -132,21 +137,21 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::mbar_arrive_expect_tx(bar(kDqbQFull), 2 * C::kOperandBytes);
 #pragma unroll
                 for (int bx = 0; bx < C::kBoxes; ++bx) {
-                    ptx::tma_load_2d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kDqbQFull), bx * 64, q_row);
-                    ptx::tma_load_2d(sbase + C::kOffDO + bx * C::kBoxBytes, &tm_do, bar(kDqbQFull), bx * 64, q_row);
+                    ptx::tma_load_4d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kDqbQFull), bx * 64, q_row, hq, b);
+                    ptx::tma_load_4d(sbase + C::kOffDO + bx * C::kBoxBytes, &tm_do, bar(kDqbQFull), bx * 64, q_row, hq, b);
                 }
 #pragma unroll 1
                 for (int t = 0; t < n_steps; ++t) {
                     const int s = t & 1;
-                    const int kv_row = (b * a.heads_kv + kvh) * a.seqlen + t * C::kTile;
+                    const int kv_row = t * C::kTile;
                     if (!bounded_wait(bar(kDqbKvEmpty + s), ((t >> 1) & 1) ^ 1, abort_flag)) break;
                     ptx::mbar_arrive_expect_tx(bar(kDqbKvFull + s), 2 * C::kOperandBytes);
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
-                        ptx::tma_load_2d(sbase + C::kOffK + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_k,
-                                         bar(kDqbKvFull + s), bx * 64, kv_row);
-                        ptx::tma_load_2d(sbase + C::kOffV + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_v,
-                                         bar(kDqbKvFull + s), bx * 64, kv_row);
+                        ptx::tma_load_4d(sbase + C::kOffK + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_k,
+                                         bar(kDqbKvFull + s), bx * 64, kv_row, kvh, b);
+                        ptx::tma_load_4d(sbase + C::kOffV + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_v,
+                                         bar(kDqbKvFull + s), bx * 64, kv_row, kvh, b);
                     }
                 }
             }
@@ -180,7 +185,7 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                         ptx::mma_ss_lean<true>(tmem + C::kColDP, loDO + k_step(kk), loV + k_step(kk), kHi, kIdSdP);
                     ptx::tc_commit_elect(bar(kDqbDpFull));
                 };
-                bool ok = warp_wait<false>(bar(kDqbQFull), 0, abort_flag) &&
+                bool ok = n_steps > 0 && warp_wait<false>(bar(kDqbQFull), 0, abort_flag) &&
                           warp_wait<false>(bar(kDqbKvFull + 0), 0, abort_flag);
                 if (ok) {
                     ptx::tc_fence_after();
@@ -209,21 +214,28 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     if (more) issue_dp(t + 1);  // after dQ(t) in issue order: dS(t) is consumed first
                     ptx::tc_commit_elect(bar(kDqbKvEmpty + (t & 1)));
                 }
-                if (ok) ptx::tc_commit_elect(bar(kDqbDone));
+                if (ok) ptx::tc_commit_elect(bar(kDqbDone));  // never reached without steps: nobody waits then
             }
         } else if (warp >= 4) {
             const int i = threadIdx.x - 128;  // query row inside the tile == TMEM lane
             const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
-            const float* side = a.sidecar + (int64_t(q_row) + i) * 3;
-            const float neg = __log2f(side[1]) - side[0];
-            const float delta = side[2];
+            const int qi = q_row + i;  // query row inside the head
+            const bool q_valid = qi < a.seqlen_q;
+            // rows past the end of the sequence: P = exp2(-inf) = 0
+            const float* side = a.sidecar + (int64_t(b * a.heads_q + hq) * a.seqlen_q + (q_valid ? qi : 0)) * 3;
+            const float neg = q_valid ? __log2f(side[1]) - side[0] : -INFINITY;
+            const float delta = q_valid ? side[2] : 0.0f;
             uint32_t ppk[64];
             bool ok = true;
 #pragma unroll 1
             for (int t = 0; t < n_steps; ++t) {
                 if (!(ok = warp_wait(bar(kDqbSFull), t & 1, abort_flag))) break;
                 ptx::tc_fence_after();
-                const bool diagonal = kCausal && t == qt;
+                // element (query i, key j) survives iff j <= mask_to (diagonal and end of the key sequence)
+                const bool diagonal = tile_needs_mask(t, qt, a.seqlen_k, causal_off, kCausal);
+                const int last_key = a.seqlen_k - 1 - t * C::kTile;
+                const int diag_key = kCausal ? qi + causal_off - t * C::kTile : (1 << 30);
+                const int mask_to = last_key < diag_key ? last_key : diag_key;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t r[32];
@@ -235,8 +247,8 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                         float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, neg));
                         if (diagonal) {
                             const int j = c * 32 + e;
-                            p0 = (j + 0 <= i) ? p0 : 0.0f;
-                            p1 = (j + 1 <= i) ? p1 : 0.0f;
+                            p0 = (j + 0 <= mask_to) ? p0 : 0.0f;
+                            p1 = (j + 1 <= mask_to) ? p1 : 0.0f;
                         }
                         ppk[c * 16 + e / 2] = ptx::Pack2<T>::pack(p0, p1);
                     }
@@ -265,15 +277,25 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(bar(kDqbDsReady));
             }
-            if (ok) ok = warp_wait(bar(kDqbDone), 0, abort_flag);
-            if (ok) {
+            if (ok && n_steps > 0) ok = warp_wait(bar(kDqbDone), 0, abort_flag);
+            TOut* dst = reinterpret_cast<TOut*>(a.dq) + b * a.q_strides.batch + hq * a.q_strides.head +
+                        int64_t(qi) * a.q_strides.row;
+            if (ok && q_valid && n_steps == 0) {
+                // no visible key at all: the gradient of these rows is zero
+                uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                for (int e = 0; e < int(D * sizeof(TOut) / 16); ++e) d4[e] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (ok && n_steps > 0) {
+                // (tensor-memory loads are warp-wide: every lane runs them, only the stores of query
+                // rows past the end of the sequence are skipped)
                 ptx::tc_fence_after();
-                TOut* dst = reinterpret_cast<TOut*>(a.dq) + (int64_t(q_row) + i) * D;
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t r[32];
                     ptx::tmem_ld32(tl + C::kColDQ + c * 32, r);
                     ptx::tmem_ld_wait();
+                    if (q_valid) {
                     if (sizeof(TOut) == 4) {
                         float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
 #pragma unroll
@@ -292,6 +314,8 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                             d4[e] = o;
                         }
                     }
+                    }
+                    __syncwarp();  // reconverge before the next warp-wide load
                 }
             }
         }

@@ -84,11 +84,11 @@ int validate_v2(const ShaoboFa3Params* p) {
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     // ---- well-formed but outside the capability set: UNSUPPORTED ------------
-    if (!lengths_are_fixed(p) || !dtype_supported(p->dtype) ||
-        p->layout != SHAOBO_FA3_LAYOUT_BHSD || !head_dim_supported(p->head_dim_qk) ||
-        p->head_dim_v != p->head_dim_qk || p->seqlen_q != p->seqlen_k ||
-        p->seqlen_q % kSequenceAlignment != 0 || p->dropout_p != 0.0f ||
-        p->softcap != 0.0f || p->sm_margin != 0 || !window_is_plain(p)) {
+    // (wider than the reference, which also turns away the [B,S,H,D] layout, seqlen_q != seqlen_k
+    // and sequence lengths that are not multiples of 128: src/shaobo_fa3_bwd_api.cpp:109-118)
+    if (!lengths_are_fixed(p) || !dtype_supported(p->dtype) || !layout_supported(p->layout) ||
+        !head_dim_supported(p->head_dim_qk) || p->head_dim_v != p->head_dim_qk ||
+        p->dropout_p != 0.0f || p->softcap != 0.0f || p->sm_margin != 0 || !window_is_plain(p)) {
         return SHAOBO_FA3_STATUS_UNSUPPORTED;
     }
     return SHAOBO_FA3_STATUS_SUCCESS;
@@ -96,8 +96,7 @@ int validate_v2(const ShaoboFa3Params* p) {
 
 bool fused_shape_ok(const ShaoboFa3Params* p) {
     return p != nullptr && p->batch > 0 && p->num_heads_q > 0 && p->num_heads_kv > 0 &&
-           p->num_heads_q % p->num_heads_kv == 0 && p->seqlen_q > 0 &&
-           p->seqlen_q == p->seqlen_k && p->seqlen_k % kSequenceAlignment == 0 &&
+           p->num_heads_q % p->num_heads_kv == 0 && p->seqlen_q > 0 && p->seqlen_k > 0 &&
            head_dim_supported(p->head_dim_qk) && p->head_dim_v == p->head_dim_qk;
 }
 
@@ -116,15 +115,17 @@ size_t dq_accum_bytes(const ShaoboFa3Params* p) {
 SplitPlan split_plan(const ShaoboFa3Params* p) {
     SplitPlan plan;
     if (!fused_shape_ok(p) || p->deterministic != 0) return plan;
-    const long long tiles = p->seqlen_k / kSequenceAlignment;
+    const int tiles = tiles_of(p->seqlen_k);
+    const int q_tiles = tiles_of(p->seqlen_q);
+    const int causal_off = p->seqlen_k - p->seqlen_q;
     const long long heads = (long long)p->batch * p->num_heads_kv;
     if (tiles * heads >= kSplitSmCount) return plan;
     const long long group = p->num_heads_q / p->num_heads_kv;
-    const long long longest = group * tiles;  // steps of the heaviest key tile
+    const long long longest = group * q_tiles;  // steps of the heaviest key tile
     for (long long chunk = 1; chunk < longest; ++chunk) {
         long long per_head = 0;
-        for (long long kt = 0; kt < tiles; ++kt) {
-            const long long steps = group * (p->causal != 0 ? tiles - kt : tiles);
+        for (int kt = 0; kt < tiles; ++kt) {
+            const long long steps = group * q_tiles_of_k_tile(kt, q_tiles, causal_off, p->causal != 0);
             per_head += (steps + chunk - 1) / chunk;
         }
         if (per_head * heads <= kSplitSmCount) {
@@ -207,16 +208,17 @@ extern "C" int shaobo_fa3_bwd_get_capabilities(ShaoboFa3BwdCapabilities* caps) {
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     caps->api_version = SHAOBO_FA3_API_VERSION;
-    // The reference's set (src/shaobo_fa3_bwd_api.cpp:180-187) plus BF16.
+    // The reference's set (src/shaobo_fa3_bwd_api.cpp:180-187) plus BF16 and the [B,S,H,D] layout.
     caps->feature_mask = SHAOBO_FA3_BWD_FEATURE_FIXED_LENGTH | SHAOBO_FA3_BWD_FEATURE_FP16 |
                          SHAOBO_FA3_BWD_FEATURE_BF16 | SHAOBO_FA3_BWD_FEATURE_CAUSAL |
                          SHAOBO_FA3_BWD_FEATURE_GQA | SHAOBO_FA3_BWD_FEATURE_DETERMINISTIC |
                          SHAOBO_FA3_BWD_FEATURE_SOFTMAX_LSE | SHAOBO_FA3_BWD_FEATURE_BHSD |
+                         SHAOBO_FA3_BWD_FEATURE_BSHD |
                          SHAOBO_FA3_BWD_FEATURE_FULL_ATTENTION;
     caps->min_head_dim = kMinHeadDim;
     caps->max_head_dim = kMaxHeadDim;
     caps->head_dim_alignment = kMinHeadDim;
-    caps->sequence_alignment = kSequenceAlignment;
+    caps->sequence_alignment = 1;  // any length; tiles are 128 rows, the last one may be ragged
     return SHAOBO_FA3_STATUS_SUCCESS;
 }
 
@@ -230,8 +232,7 @@ extern "C" size_t shaobo_fa3_bwd_v2_workspace_bytes(const ShaoboFa3Params* param
 }
 
 extern "C" size_t shaobo_fa3_bwd_fused5_workspace_bytes(const ShaoboFa3Params* params) {
-    if (params == nullptr || !dtype_supported(params->dtype) ||
-        params->layout != SHAOBO_FA3_LAYOUT_BHSD) {
+    if (params == nullptr || !dtype_supported(params->dtype) || !layout_supported(params->layout)) {
         return 0;
     }
     // dQ accumulator, then the dK/dV accumulators of split tiles

@@ -5,12 +5,13 @@
 #include <cstddef>
 #include <cstdint>
 
+#include "geometry.h"
 #include "shaobo_fa3_api.h"
 
 namespace fa3b200 {
 
 constexpr size_t kWorkspaceAlignment = 256;  // same as reference src/shaobo_fa3_bwd_api.cpp:16
-constexpr int kSequenceAlignment = 128;      // K/Q tile edge; reference :18
+constexpr int kSequenceAlignment = 128;      // K/Q tile edge; reference :18 (lengths need not be multiples)
 constexpr int kMinHeadDim = 64;
 constexpr int kMaxHeadDim = 128;
 constexpr int kSidecarFields = 3;            // {m, r, delta}; reference src/dot_do_o_kernel.cpp:11
@@ -22,6 +23,9 @@ bool add_ok(size_t a, size_t b, size_t* out);
 bool round_up_256(size_t bytes, size_t* out);
 
 inline bool head_dim_supported(int d) { return d == 64 || d == 128; }
+inline bool layout_supported(int l) {
+    return l == SHAOBO_FA3_LAYOUT_BHSD || l == SHAOBO_FA3_LAYOUT_BSHD;
+}
 inline bool dtype_supported(int t) {
     return t == SHAOBO_FA3_DTYPE_FP16 || t == SHAOBO_FA3_DTYPE_BF16;
 }
@@ -30,7 +34,7 @@ inline bool dtype_supported(int t) {
 int validate_v2(const ShaoboFa3Params* p);
 
 // Shape test shared by the fused stage and its workspace formula: positive
-// dims, Hq % Hkv == 0, Sq == Sk, S % 128 == 0, D in {64,128}, Dqk == Dv.
+// dims, Hq % Hkv == 0, D in {64,128}, Dqk == Dv.
 bool fused_shape_ok(const ShaoboFa3Params* p);
 
 // Bytes of the fp32 dQ accumulator [B,Hq,S,D] rounded up to 256; 0 on

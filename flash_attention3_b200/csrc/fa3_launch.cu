@@ -42,19 +42,46 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Row-major [rows, cols] tensor, boxes of [box_rows][box_cols] with the
-// 128-byte swizzle (box_cols * element size must be 128 bytes).
-bool make_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base,
-              uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+// 16-bit [batch][head][row][D] tensor in either layout, addressed with coordinates (column, row,
+// head, batch); boxes of [128 rows][64 columns] with the 128-byte swizzle.  Rows past the end of a
+// sequence are outside the tensor for the copy engine and read as zero.
+bool make_map_16(CUtensorMap* map, CUtensorMapDataType type, const void* base, int batch, int heads,
+                 int seqlen, int d, bool bshd) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * uint64_t(elem_bytes)};
-    const cuuint32_t box[2] = {box_cols, box_rows};
-    const cuuint32_t elem_strides[2] = {1, 1};
-    return fn(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+    const TensorStrides st = strides_of(bshd, heads, seqlen, d);
+    const cuuint64_t dims[4] = {cuuint64_t(d), cuuint64_t(seqlen), cuuint64_t(heads), cuuint64_t(batch)};
+    const cuuint64_t strides[3] = {cuuint64_t(st.row) * 2, cuuint64_t(st.head) * 2, cuuint64_t(st.batch) * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    return fn(map, type, 4, const_cast<void*>(base), dims, strides, box, elem_strides,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// fp32 accumulator [batch*head][row][D] contiguous, coordinates (column, row, batch*head), boxes of
+// [32 rows][32 columns] with the 128-byte swizzle.  Reduce-adds drop the rows past the sequence end.
+bool make_map_accum(CUtensorMap* map, const float* base, int64_t batch_heads, int seqlen, int d) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(seqlen), cuuint64_t(batch_heads)};
+    const cuuint64_t strides[2] = {cuuint64_t(d) * 4, cuuint64_t(seqlen) * cuuint64_t(d) * 4};
+    const cuuint32_t box[3] = {32, 32, 1};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box,
+              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool is_bshd(const ShaoboFa3Params* p) { return p->layout == SHAOBO_FA3_LAYOUT_BSHD; }
+
+RowLayout row_layout(const ShaoboFa3Params* p, int heads, int seqlen) {
+    RowLayout l;
+    l.strides = strides_of(is_bshd(p), heads, seqlen, p->head_dim_qk);
+    l.heads = heads;
+    l.seqlen = seqlen;
+    l.contiguous = is_bshd(p) ? 0 : 1;
+    return l;
 }
 
 cudaStream_t stream_of(const ShaoboFa3Params* p) {
@@ -75,14 +102,15 @@ int sm_count() {
     return n;
 }
 
-CtaOrderPlan cached_plan(int n_tiles, int bh, int group, bool causal, int sms, long long dq_bytes) {
+CtaOrderPlan cached_plan(const TileWork& work, int bh, int group, int sms, long long dq_bytes) {
     static std::mutex mu;
-    static std::map<std::tuple<int, int, int, bool, int, long long>, CtaOrderPlan> cache;
-    const auto key = std::make_tuple(n_tiles, bh, group, causal, sms, dq_bytes);
+    static std::map<std::tuple<int, int, int, bool, int, int, int, long long>, CtaOrderPlan> cache;
+    const auto key = std::make_tuple(work.n_k_tiles, work.n_q_tiles, work.causal_off, work.causal, bh,
+                                     group, sms, dq_bytes);
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
-    const CtaOrderPlan plan = plan_cta_order(n_tiles, bh, group, causal, sms, dq_bytes);
+    const CtaOrderPlan plan = plan_cta_order(work, bh, group, sms, dq_bytes);
     cache[key] = plan;
     return plan;
 }
@@ -138,7 +166,7 @@ template <typename T, int D>
 void launch_delta_t(const void* dout, const void* out, const float* aux0, const float* aux1,
                     float* delta, float* sidecar, float* zero_rows, float* zero_extra,
                     int64_t zero_extra_bytes, int64_t rows, bool lse, float scale_log2,
-                    cudaStream_t st) {
+                    const RowLayout& layout, cudaStream_t st) {
     constexpr int kRowsPerBlock = 8 * (32 / (D / 8));
     int64_t blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
     const int64_t cap = int64_t(sm_count()) * 16;
@@ -148,11 +176,11 @@ void launch_delta_t(const void* dout, const void* out, const float* aux0, const 
     if (lse) {
         delta_sidecar_kernel<T, D, true><<<int(blocks), 256, 0, st>>>(
             static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
-            zero_rows, ze, ze_n, rows, scale_log2);
+            zero_rows, ze, ze_n, rows, scale_log2, layout);
     } else {
         delta_sidecar_kernel<T, D, false><<<int(blocks), 256, 0, st>>>(
             static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
-            zero_rows, ze, ze_n, rows, scale_log2);
+            zero_rows, ze, ze_n, rows, scale_log2, layout);
     }
 }
 
@@ -163,12 +191,13 @@ void launch_delta(const ShaoboFa3Params* p, const void* dout, const void* out, c
     const float scale_log2 = p->softmax_scale * kLog2E;
     cudaStream_t st = stream_of(p);
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
+    const RowLayout layout = row_layout(p, p->num_heads_q, p->seqlen_q);
     if (p->head_dim_qk == 128) {
-        if (bf) launch_delta_t<__nv_bfloat16, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, st);
-        else launch_delta_t<__half, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, st);
+        if (bf) launch_delta_t<__nv_bfloat16, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
+        else launch_delta_t<__half, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
     } else {
-        if (bf) launch_delta_t<__nv_bfloat16, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, st);
-        else launch_delta_t<__half, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, st);
+        if (bf) launch_delta_t<__nv_bfloat16, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
+        else launch_delta_t<__half, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
     }
 }
 
@@ -182,6 +211,8 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
     seg.dst[0] = dq;
     seg.n_vec8[0] = int64_t(p->batch) * p->num_heads_q * p->seqlen_q * p->head_dim_qk / 8;
     seg.scale[0] = p->softmax_scale;
+    seg.layout[0] = row_layout(p, p->num_heads_q, p->seqlen_q);
+    seg.head_dim = p->head_dim_qk;
     seg.count = 1;
     int64_t total = seg.n_vec8[0];
     if (dkv_accum != nullptr) {
@@ -192,6 +223,7 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
         seg.dst[2] = dv;
         seg.n_vec8[1] = seg.n_vec8[2] = n / 8;
         seg.scale[1] = seg.scale[2] = 1.0f;
+        seg.layout[1] = seg.layout[2] = row_layout(p, p->num_heads_kv, p->seqlen_k);
         seg.count = 3;
         total += 2 * (n / 8);
     }
@@ -273,18 +305,18 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
                  bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr, bool pdl = false) {
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const uint64_t d = uint64_t(p->head_dim_qk);
-    const uint64_t q_rows = uint64_t(p->batch) * p->num_heads_q * p->seqlen_q;
-    const uint64_t kv_rows = uint64_t(p->batch) * p->num_heads_kv * p->seqlen_k;
+    const int d = p->head_dim_qk;
+    const bool bshd = is_bshd(p);
+    const int64_t kv_heads_total = int64_t(p->batch) * p->num_heads_kv;
     CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
-    if (!make_map(&mq, type, 2, q, q_rows, d, 64, 128) ||
-        !make_map(&mk, type, 2, k, kv_rows, d, 64, 128) ||
-        !make_map(&mv, type, 2, v, kv_rows, d, 64, 128) ||
-        !make_map(&mdo, type, 2, dout, q_rows, d, 64, 128)) {
+    if (!make_map_16(&mq, type, q, p->batch, p->num_heads_q, p->seqlen_q, d, bshd) ||
+        !make_map_16(&mk, type, k, p->batch, p->num_heads_kv, p->seqlen_k, d, bshd) ||
+        !make_map_16(&mv, type, v, p->batch, p->num_heads_kv, p->seqlen_k, d, bshd) ||
+        !make_map_16(&mdo, type, dout, p->batch, p->num_heads_q, p->seqlen_q, d, bshd)) {
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
     if (with_dq) {
-        if (!make_map(&mdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dq_accum, q_rows, d, 32, 32)) {
+        if (!make_map_accum(&mdq, dq_accum, int64_t(p->batch) * p->num_heads_q, p->seqlen_q, d)) {
             return SHAOBO_FA3_STATUS_HIP_ERROR;
         }
     } else {
@@ -292,29 +324,38 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     }
     const SplitPlan split = (with_dq && dkv_accum != nullptr) ? split_plan(p) : SplitPlan{};
     if (split.chunk_steps > 0) {
-        if (!make_map(&mdk, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dkv_accum, kv_rows, d, 32, 32) ||
-            !make_map(&mdv, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dkv_accum + kv_rows * d, kv_rows, d, 32, 32)) {
+        const int64_t kv_elems = kv_heads_total * p->seqlen_k * d;
+        if (!make_map_accum(&mdk, dkv_accum, kv_heads_total, p->seqlen_k, d) ||
+            !make_map_accum(&mdv, dkv_accum + kv_elems, kv_heads_total, p->seqlen_k, d)) {
             return SHAOBO_FA3_STATUS_HIP_ERROR;
         }
     } else {
         mdk = mq;  // unused by the kernel
         mdv = mq;
     }
-    const int n_tiles = p->seqlen_k / 128;
+    const int n_tiles = tiles_of(p->seqlen_k);
+    TileWork work;
+    work.n_k_tiles = n_tiles;
+    work.n_q_tiles = tiles_of(p->seqlen_q);
+    work.causal_off = p->seqlen_k - p->seqlen_q;
+    work.causal = p->causal != 0;
     const int bh = p->batch * p->num_heads_kv;
     const int group = p->num_heads_q / p->num_heads_kv;
     // bytes of dQ accumulator behind one (batch, KV head): only the fused path adds into it
     const long long dq_bytes_per_head =
         with_dq ? (long long)group * p->seqlen_q * p->head_dim_qk * 4 : 0;
-    const CtaOrderPlan plan = cached_plan(n_tiles, bh, group, p->causal != 0, sm_count(), dq_bytes_per_head);
+    const CtaOrderPlan plan = cached_plan(work, bh, group, sm_count(), dq_bytes_per_head);
     FusedArgs args;
     args.sidecar = sidecar;
     args.dk = dk;
     args.dv = dv;
+    // fp32 dK/dV of the split path are always [B,Hkv,Sk,D]; 16-bit outputs follow the layout of K/V
+    args.kv_strides = strides_of(bshd && !dkv_f32, p->num_heads_kv, p->seqlen_k, d);
     args.batch = p->batch;
     args.heads_q = p->num_heads_q;
     args.heads_kv = p->num_heads_kv;
-    args.seqlen = p->seqlen_q;
+    args.seqlen_q = p->seqlen_q;
+    args.seqlen_k = p->seqlen_k;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
     args.order_mode = plan.mode;
@@ -371,26 +412,28 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
               const void* v, const float* sidecar, void* dq, bool out_f32) {
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const uint64_t d = uint64_t(p->head_dim_qk);
-    const uint64_t q_rows = uint64_t(p->batch) * p->num_heads_q * p->seqlen_q;
-    const uint64_t kv_rows = uint64_t(p->batch) * p->num_heads_kv * p->seqlen_k;
+    const int d = p->head_dim_qk;
+    const bool bshd = is_bshd(p);
     CUtensorMap mq, mk, mv, mdo;
-    if (!make_map(&mq, type, 2, q, q_rows, d, 64, 128) ||
-        !make_map(&mk, type, 2, k, kv_rows, d, 64, 128) ||
-        !make_map(&mv, type, 2, v, kv_rows, d, 64, 128) ||
-        !make_map(&mdo, type, 2, dout, q_rows, d, 64, 128)) {
+    if (!make_map_16(&mq, type, q, p->batch, p->num_heads_q, p->seqlen_q, d, bshd) ||
+        !make_map_16(&mk, type, k, p->batch, p->num_heads_kv, p->seqlen_k, d, bshd) ||
+        !make_map_16(&mv, type, v, p->batch, p->num_heads_kv, p->seqlen_k, d, bshd) ||
+        !make_map_16(&mdo, type, dout, p->batch, p->num_heads_q, p->seqlen_q, d, bshd)) {
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
     DqArgs args;
     args.sidecar = sidecar;
     args.dq = dq;
+    // fp32 dQ of the split path is always [B,Hq,Sq,D]; 16-bit dQ follows the layout of Q
+    args.q_strides = strides_of(bshd && !out_f32, p->num_heads_q, p->seqlen_q, d);
     args.batch = p->batch;
     args.heads_q = p->num_heads_q;
     args.heads_kv = p->num_heads_kv;
-    args.seqlen = p->seqlen_q;
+    args.seqlen_q = p->seqlen_q;
+    args.seqlen_k = p->seqlen_k;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
-    const int64_t blocks64 = int64_t(p->seqlen_q / 128) * p->batch * p->num_heads_q;
+    const int64_t blocks64 = int64_t(tiles_of(p->seqlen_q)) * p->batch * p->num_heads_q;
     if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
     const int blocks = int(blocks64);
     if (out_f32) {
@@ -402,7 +445,7 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
 }
 
 bool stage_params_ok(const ShaoboFa3Params* p) {
-    return p != nullptr && dtype_supported(p->dtype) && p->layout == SHAOBO_FA3_LAYOUT_BHSD &&
+    return p != nullptr && dtype_supported(p->dtype) && layout_supported(p->layout) &&
            (p->causal == 0 || p->causal == 1) && fused_shape_ok(p);
 }
 
@@ -488,7 +531,7 @@ extern "C" int shaobo_fa3_bwd_dot_do_o(const void* dout, const void* out, const 
     const bool ok = params != nullptr && params->batch > 0 && params->seqlen_q > 0 &&
                     params->num_heads_q > 0 && head_dim_supported(params->head_dim_qk) &&
                     params->head_dim_v == params->head_dim_qk && dtype_supported(params->dtype) &&
-                    params->layout == SHAOBO_FA3_LAYOUT_BHSD &&
+                    layout_supported(params->layout) &&
                     (params->softmax_aux_mode == SHAOBO_FA3_SOFTMAX_AUX_SMAX_SSUM ||
                      params->softmax_aux_mode == SHAOBO_FA3_SOFTMAX_AUX_LSE);
     if (!ok) return SHAOBO_FA3_STATUS_UNSUPPORTED;

@@ -48,6 +48,7 @@
 
 #include <type_traits>
 
+#include "geometry.h"
 #include "ptx.cuh"
 
 namespace fa3b200 {
@@ -81,13 +82,15 @@ __device__ long long g_debug_stamps[3][4][16];   // [role][step-8][event]
 #endif
 
 struct FusedArgs {
-    const float* sidecar;  // [B,Hq,S,3]
-    void* dk;              // [B,Hkv,S,D]
-    void* dv;              // [B,Hkv,S,D]
+    const float* sidecar;  // [B,Hq,Sq,3]
+    void* dk;              // [B,Hkv,Sk,D] or [B,Sk,Hkv,D], see kv_strides
+    void* dv;
+    TensorStrides kv_strides;  // element strides of dk / dv
     int batch;
     int heads_q;
     int heads_kv;
-    int seqlen;
+    int seqlen_q;
+    int seqlen_k;
     float scale;
     float scale_log2;
     int order_mode;        // see cta_order.h
@@ -226,7 +229,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     // ---- which tile is ours ------------------------------------------------
-    const int n_tiles = a.seqlen / C::kTile;
+    const int n_tiles = tiles_of(a.seqlen_k);      // key tiles
+    const int n_q_tiles = tiles_of(a.seqlen_q);
+    const int causal_off = a.seqlen_k - a.seqlen_q;  // query i sees key j iff j <= i + causal_off
     const int bh_count = a.batch * a.heads_kv;
     const bool split = a.chunk_steps > 0;
     const int group = a.heads_q / a.heads_kv;
@@ -246,7 +251,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         int rest = int(blockIdx.x) % a.chunks_per_head;
         kt = 0;
         while (true) {
-            const int steps = group * (kCausal ? n_tiles - kt : n_tiles);
+            const int steps = group * q_tiles_of_k_tile(kt, n_q_tiles, causal_off, kCausal);
             const int chunks = (steps + a.chunk_steps - 1) / a.chunk_steps;
             if (rest < chunks) break;
             rest -= chunks;
@@ -256,8 +261,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     const int b = bhi / a.heads_kv;
     const int kvh = bhi % a.heads_kv;
-    const int q_begin = kCausal ? kt : 0;
-    const int steps_per_head = n_tiles - q_begin;
+    const int q_begin = first_q_tile(kt, causal_off, kCausal);
+    const int steps_per_head = q_tiles_of_k_tile(kt, n_q_tiles, causal_off, kCausal);
     // this CTA's share of the tile's steps (all of them unless the tile is split)
     const int total_steps = group * steps_per_head;
     const int t_begin = t_begin_split;
@@ -265,6 +270,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int n_steps = t_end - t_begin;
     // "misaligned" also covers a CTA without work: every role is skipped, set-up and teardown still run
     const bool misaligned = (sbase & 1023u) != 0 || n_steps == 0;
+    // (with the diagonal aligned bottom-right the last query sees every key, so an unsplit key tile
+    // always has at least one step; n_steps == 0 only happens for surplus CTAs)
 
     if (threadIdx.x == 0) {
         if ((sbase & 1023u) != 0) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
@@ -309,8 +316,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (kCausal) {
             qt = q_begin + r;
         } else {
-            qt = r + kt;
-            if (qt >= n_tiles) qt -= n_tiles;
+            qt = r + kt % n_q_tiles;
+            if (qt >= n_q_tiles) qt -= n_q_tiles;
         }
     };
 
@@ -323,33 +330,35 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 ptx::prefetch_tensormap(&tm_k);
                 ptx::prefetch_tensormap(&tm_v);
                 ptx::prefetch_tensormap(&tm_do);
-                const int kv_row = (b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile;
+                // tensor maps are [batch][head][row][D]; rows past the end of a sequence read as zero
                 ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
 #pragma unroll
                 for (int bx = 0; bx < C::kBoxes; ++bx) {
-                    ptx::tma_load_2d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64, kv_row);
-                    ptx::tma_load_2d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64, kv_row);
+                    ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
+                                     kt * C::kTile, kvh, b);
+                    ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
+                                     kt * C::kTile, kvh, b);
                 }
 #pragma unroll 1
                 for (int t = 0; t < n_steps; ++t) {
                     int hq, qt;
                     step_coords(t, hq, qt);
-                    const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile;
+                    const int q_row = qt * C::kTile;
                     const int s = t % C::kQStages;
                     if (!bounded_wait<true>(bar(kQEmpty + s), ((t / C::kQStages) & 1) ^ 1, abort_flag)) break;
                     ptx::mbar_arrive_expect_tx(bar(kQFull + s), C::kOperandBytes);
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
-                        ptx::tma_load_2d(sbase + C::kOffQ + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_q,
-                                         bar(kQFull + s), bx * 64, q_row);
+                        ptx::tma_load_4d(sbase + C::kOffQ + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_q,
+                                         bar(kQFull + s), bx * 64, q_row, hq, b);
                     }
                     const int sd = t % C::kDoStages;
                     if (!bounded_wait<true>(bar(kDoEmpty + sd), ((t / C::kDoStages) & 1) ^ 1, abort_flag)) break;
                     ptx::mbar_arrive_expect_tx(bar(kDoFull + sd), C::kOperandBytes);
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
-                        ptx::tma_load_2d(sbase + C::kOffDO + sd * C::kOperandBytes + bx * C::kBoxBytes, &tm_do,
-                                         bar(kDoFull + sd), bx * 64, q_row);
+                        ptx::tma_load_4d(sbase + C::kOffDO + sd * C::kOperandBytes + bx * C::kBoxBytes, &tm_do,
+                                         bar(kDoFull + sd), bx * 64, q_row, hq, b);
                     }
                 }
             }
@@ -486,17 +495,27 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             float* stats = reinterpret_cast<float*>(smem + C::kOffStats);
             uint32_t ppk[32];
             const float* side_base = a.sidecar;
-            float s0 = 0.f, s1 = 1.f, s2 = 0.f;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+            // statistics of query row qi of head hq; rows past the end of the sequence get r = 0, which
+            // makes their P (and with it dS) exactly zero
+            auto load_stats = [&](int hq, int qt) {
+                const int qi = qt * C::kTile + j;
+                const bool valid = qi < a.seqlen_q;
+                const int64_t row = int64_t(b * a.heads_q + hq) * a.seqlen_q + (valid ? qi : 0);
+                const float v0 = side_base[row * 3 + 0];
+                const float v1 = side_base[row * 3 + 1];
+                const float v2 = side_base[row * 3 + 2];
+                s0 = valid ? v0 : 0.f;
+                s1 = valid ? v1 : 0.f;
+                s2 = valid ? v2 : 0.f;
+            };
             // the sidecar comes from the delta kernel, which may still be running (programmatic launch);
             // Q, K, V, dO are inputs of the call, so the TMA and MMA warps did not have to wait
             ptx::grid_dependency_wait();
             if (half == 0) {
                 int hq, qt;
                 step_coords(0, hq, qt);
-                const int64_t row = int64_t(b * a.heads_q + hq) * a.seqlen + qt * C::kTile + j;
-                s0 = side_base[row * 3 + 0];
-                s1 = side_base[row * 3 + 1];
-                s2 = side_base[row * 3 + 2];
+                load_stats(hq, qt);
             }
             bool ok = true;
             DBG_TICK();
@@ -517,10 +536,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     if (t + 1 < n_steps) {
                         int hq1, qt1;
                         step_coords(t + 1, hq1, qt1);
-                        const int64_t row = int64_t(b * a.heads_q + hq1) * a.seqlen + qt1 * C::kTile + j;
-                        s0 = side_base[row * 3 + 0];
-                        s1 = side_base[row * 3 + 1];
-                        s2 = side_base[row * 3 + 2];
+                        load_stats(hq1, qt1);
                     }
                 }
                 if (!(ok = warp_wait(bar(kStatsFull + buf), (t >> 1) & 1, abort_flag))) break;
@@ -528,8 +544,14 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (!(ok = warp_wait(bar(kSFull), t & 1, abort_flag))) break;
                 DBG_STAMP(2);
                 ptx::tc_fence_after();
-                const bool diagonal = kCausal && qt == kt;
-                // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked where query i < key j.
+                // A tile that crosses the diagonal or holds keys past the end of the sequence is masked:
+                // element (key j, query i) survives iff i >= mask_from.
+                const bool diagonal = tile_needs_mask(kt, qt, a.seqlen_k, causal_off, kCausal);
+                const int key = kt * C::kTile + j;
+                const int mask_from = key >= a.seqlen_k ? (1 << 30)
+                                      : kCausal        ? key - causal_off - qt * C::kTile
+                                                       : -(1 << 30);
+                // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked as above.
                                 auto softmax_chunk = [&](int c, const uint32_t* r) {
 #ifdef FA3B200_DEBUG_DUMP
                     if (blockIdx.x == 0 && t == 0)
@@ -549,10 +571,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         float p3 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 3]), a.scale_log2, n4.w));
                         if (diagonal) {
                             const int i = half * 64 + c * 32 + e;
-                            p0 = (i + 0 >= j) ? p0 : 0.0f;
-                            p1 = (i + 1 >= j) ? p1 : 0.0f;
-                            p2 = (i + 2 >= j) ? p2 : 0.0f;
-                            p3 = (i + 3 >= j) ? p3 : 0.0f;
+                            p0 = (i + 0 >= mask_from) ? p0 : 0.0f;
+                            p1 = (i + 1 >= mask_from) ? p1 : 0.0f;
+                            p2 = (i + 2 >= mask_from) ? p2 : 0.0f;
+                            p3 = (i + 3 >= mask_from) ? p3 : 0.0f;
                         }
                         ppk[c * 16 + e / 2 + 0] = ptx::Pack2<T>::pack(p0, p1);
                         ppk[c * 16 + e / 2 + 1] = ptx::Pack2<T>::pack(p2, p3);
@@ -629,9 +651,13 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // ---- epilogue: the first warpgroup writes dK (scaled), the second dV
             if (ok) ok = warp_wait(bar(kDkvFull), 0, abort_flag);
             if (ok && !split) {
+                // (tensor-memory loads are warp-wide: every lane runs them, only the stores of key rows
+                // past the end of the sequence are skipped)
+                const bool key_valid = kt * C::kTile + j < a.seqlen_k;
                 ptx::tc_fence_after();
-                const int64_t row = int64_t(b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile + j;
-                TOut* dst = reinterpret_cast<TOut*>(half == 0 ? a.dk : a.dv) + row * D;
+                const int64_t off = b * a.kv_strides.batch + kvh * a.kv_strides.head +
+                                    int64_t(kt * C::kTile + j) * a.kv_strides.row;
+                TOut* dst = reinterpret_cast<TOut*>(half == 0 ? a.dk : a.dv) + off;
                 const float mul = half == 0 ? a.scale : 1.0f;
                 const uint32_t col0 = tl + (half == 0 ? C::kColDK : C::kColDV);
 #pragma unroll
@@ -639,6 +665,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     uint32_t r[32];
                     ptx::tmem_ld32(col0 + c * 32, r);
                     ptx::tmem_ld_wait();
+                    if (key_valid) {
                     if (sizeof(TOut) == 4) {
                         float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
 #pragma unroll
@@ -657,6 +684,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                             d4[e] = o;
                         }
                     }
+                    }
+                    __syncwarp();  // reconverge before the next warp-wide load
                 }
             }
         }
@@ -679,7 +708,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 for (int t = 0; t < n_steps; ++t) {
                     int hq, qt;
                     step_coords(t, hq, qt);
-                    const int q_row = (b * a.heads_q + hq) * a.seqlen + qt * C::kTile + qd * 32;
+                    const int q_row = qt * C::kTile + qd * 32;  // row inside the head
+                    const int q_head = b * a.heads_q + hq;
                     DBG_STAMP(0);
                     if (!warp_wait(bar(kDqFull), t & 1, abort_flag)) break;
                     DBG_STAMP(1);
@@ -719,9 +749,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
 #ifndef FA3B200_EXPERIMENT_NOREDUCE
-                        if (lane == 0) {
-                            ptx::tma_reduce_add_2d(&tm_dqacc, stage, hf * 64, q_row);
-                            ptx::tma_reduce_add_2d(&tm_dqacc, stage + C::kStageBoxBytes, hf * 64 + 32, q_row);
+                        // accumulator map: [batch*head][row][D]; rows past the sequence end are dropped
+                        if (lane == 0 && q_row < a.seqlen_q) {
+                            ptx::tma_reduce_add_3d(&tm_dqacc, stage, hf * 64, q_row, q_head);
+                            ptx::tma_reduce_add_3d(&tm_dqacc, stage + C::kStageBoxBytes, hf * 64 + 32, q_row, q_head);
                             ptx::bulk_commit_group();
                         }
 #endif
@@ -737,7 +768,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     // with TMA reduce-adds, all in flight together.
                     if (warp_wait(bar(kDkvFull), 0, abort_flag)) {
                         ptx::tc_fence_after();
-                        const int row0 = (b * a.heads_kv + kvh) * a.seqlen + kt * C::kTile + qd * 32;
+                        const int row0 = kt * C::kTile + qd * 32;
                         constexpr int kBoxesPerTensor = D / 32;
                         const uint32_t scratch = sbase + C::kOffQ + qd * (2 * kBoxesPerTensor * C::kStageBoxBytes);
 #pragma unroll
@@ -762,14 +793,15 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         }
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0) {
+                        if (lane == 0 && row0 < a.seqlen_k) {
 #pragma unroll
                             for (int bx = 0; bx < 2 * kBoxesPerTensor; ++bx) {
                                 const int which = bx / kBoxesPerTensor;
                                 const int c = bx % kBoxesPerTensor;
-                                ptx::tma_reduce_add_2d(which == 0 ? static_cast<const void*>(&tm_dkacc)
+                                ptx::tma_reduce_add_3d(which == 0 ? static_cast<const void*>(&tm_dkacc)
                                                                   : static_cast<const void*>(&tm_dvacc),
-                                                       scratch + bx * C::kStageBoxBytes, c * 32, row0);
+                                                       scratch + bx * C::kStageBoxBytes, c * 32, row0,
+                                                       b * a.heads_kv + kvh);
                             }
                             ptx::bulk_commit_group();
                         }

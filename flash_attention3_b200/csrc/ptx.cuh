@@ -56,6 +56,24 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* map, uint3
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+// 4-D tiled load (coordinates innermost first); rows outside the tensor read as zero.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* map, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+// 3-D tiled reduce-add shared -> global; elements outside the tensor are dropped.
+__device__ __forceinline__ void tma_reduce_add_3d(const void* map, uint32_t src, int c0, int c1,
+                                                  int c2) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group"
+        " [%0, {%2, %3, %4}], [%1];"
+        ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
 // 2-D tiled reduce-add shared -> global (element type comes from the map).
 __device__ __forceinline__ void tma_reduce_add_2d(const void* map, uint32_t src, int x, int y) {
     asm volatile(

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "geometry.h"
+
 namespace fa3b200 {
 
 constexpr float kLog2E = 1.44269504088896340736f;
@@ -51,15 +53,36 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
 // accumulator (row pitch D floats), which saves a separate memset pass; a
 // second, unrelated range (zero_extra) can be cleared by the same launch.
 //
+// Rows are numbered in [batch, head, row] order (the order of aux0, delta and
+// the sidecar); RowLayout says where row r of dO and O lives, so that both the
+// [B,H,S,D] and the [B,S,H,D] layout are read in place.  A row whose softmax
+// saw no key at all (aux0 = -inf) gets m = 0, r = 0, which makes P zero.
+//
 // Algorithmic HBM bytes per row: 2*D*2 (dO, O) + 4 (aux0) [+4 aux1] + 4
 // (delta) + 12 (sidecar) [+ 4*D when clearing the accumulator].
+struct RowLayout {
+    TensorStrides strides;  // element strides of the 16-bit tensor
+    int heads;
+    int seqlen;
+    int contiguous;         // 1: row r starts at element r*D ([B,H,S,D] contiguous)
+};
+
+__device__ __forceinline__ int64_t row_offset(const RowLayout& l, int64_t row, int d) {
+    if (l.contiguous) return row * d;
+    const int64_t bh = row / l.seqlen;
+    const int s = int(row - bh * l.seqlen);
+    const int64_t b = bh / l.heads;
+    const int h = int(bh - b * l.heads);
+    return b * l.strides.batch + h * l.strides.head + s * l.strides.row;
+}
+
 template <typename T, int D, bool kLseInput>
 __global__ void __launch_bounds__(256)
 delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
                      const float* __restrict__ aux0, const float* __restrict__ aux1,
                      float* __restrict__ delta, float* __restrict__ sidecar,
                      float* __restrict__ zero_rows, float4* __restrict__ zero_extra,
-                     int64_t zero_extra_vec4, int64_t rows, float scale_log2) {
+                     int64_t zero_extra_vec4, int64_t rows, float scale_log2, RowLayout layout) {
     constexpr int kLanesPerRow = D / 8;
     constexpr int kRowsPerWarp = 32 / kLanesPerRow;
     const int lane = threadIdx.x & 31;
@@ -76,9 +99,17 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
         zero_extra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
 
-    for (int64_t row = warp * kRowsPerWarp + sub; row < rows; row += warps * kRowsPerWarp) {
-        const uint4 a = ld_stream_16B(dout + row * D + col * 8);
-        const uint4 b = ld_stream_16B(out + row * D + col * 8);
+    // the loop bound is the same for every lane of a warp (the shuffles below need all 32 lanes);
+    // lanes whose row lies past the end compute on zeros and write nothing
+    for (int64_t base = warp * kRowsPerWarp; base < rows; base += warps * kRowsPerWarp) {
+        const int64_t row = base + sub;
+        const bool valid = row < rows;
+        uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+        if (valid) {
+            const int64_t src = row_offset(layout, row, D) + col * 8;
+            a = ld_stream_16B(dout + src);
+            b = ld_stream_16B(out + src);
+        }
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
         const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
         float acc = 0.0f;
@@ -93,14 +124,14 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
         for (int off = kLanesPerRow / 2; off > 0; off >>= 1) {
             acc += __shfl_xor_sync(0xffffffffu, acc, off);
         }
-        if (zero_rows != nullptr) {
+        if (valid && zero_rows != nullptr) {
             float4* z = reinterpret_cast<float4*>(zero_rows + row * D);
 #pragma unroll
             for (int i = 0; i < (D / 4) / kLanesPerRow; ++i) {
                 z[col + i * kLanesPerRow] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        if (col == 0) {
+        if (valid && col == 0) {
             delta[row] = acc;
             float m, r;
             if (kLseInput) {
@@ -110,6 +141,10 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
                 m = aux0[row] * scale_log2;
                 const float sum = aux1[row];
                 r = sum != 0.0f ? 1.0f / sum : 0.0f;
+            }
+            if (m == -INFINITY) {  // no visible key
+                m = 0.0f;
+                r = 0.0f;
             }
             float* s = sidecar + row * 3;
             s[0] = m;
@@ -122,11 +157,13 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
 // Up to three (fp32 accumulator -> storage dtype) conversions in one launch:
 // dQ (scaled) always; dK and dV as well when tiles were split.
 struct ConvertSegments {
-    const float* src[3];
+    const float* src[3];   // fp32 [batch, head, row, D] contiguous
     void* dst[3];
     int64_t n_vec8[3];
     float scale[3];
+    RowLayout layout[3];   // where the rows of dst live
     int count;
+    int head_dim;
 };
 
 // dst[i] = T(scale * accum[i]).  8 elements per thread: 32 B in, 16 B out.
@@ -144,6 +181,8 @@ dq_convert_kernel(const ConvertSegments seg) {
     T* __restrict__ dq = static_cast<T*>(seg.dst[sgi]);
     const int64_t n_vec8 = seg.n_vec8[sgi];
     const float scale = seg.scale[sgi];
+    const RowLayout layout = seg.layout[sgi];
+    const int vec_per_row = seg.head_dim / 8;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec8; i += stride) {
         const uint4 lo = ld_stream_16B(accum + i * 8);
         const uint4 hi = ld_stream_16B(accum + i * 8 + 4);
@@ -152,7 +191,13 @@ dq_convert_kernel(const ConvertSegments seg) {
         o.y = pack2<T>(__uint_as_float(lo.z) * scale, __uint_as_float(lo.w) * scale);
         o.z = pack2<T>(__uint_as_float(hi.x) * scale, __uint_as_float(hi.y) * scale);
         o.w = pack2<T>(__uint_as_float(hi.z) * scale, __uint_as_float(hi.w) * scale);
-        reinterpret_cast<uint4*>(dq)[i] = o;
+        if (layout.contiguous) {
+            reinterpret_cast<uint4*>(dq)[i] = o;
+        } else {
+            const int64_t row = i / vec_per_row;
+            const int col = int(i - row * vec_per_row) * 8;
+            *reinterpret_cast<uint4*>(dq + row_offset(layout, row, seg.head_dim) + col) = o;
+        }
     }
     }
 }

@@ -21,10 +21,18 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def make_params(q: torch.Tensor, k: torch.Tensor, causal: bool, softmax_scale=None, **extra) -> capi.Params:
-    b, hq, s, d = q.shape
-    p = capi.new_params(batch=b, seqlen_q=s, seqlen_k=k.shape[2], num_heads_q=hq, num_heads_kv=k.shape[1],
-                        head_dim_qk=d, head_dim_v=d, causal=int(causal), dtype=_DTYPES[q.dtype])
+def make_params(q: torch.Tensor, k: torch.Tensor, causal: bool, softmax_scale=None, layout: str = "bhsd",
+                **extra) -> capi.Params:
+    """layout "bhsd": q [B,Hq,Sq,D], k [B,Hkv,Sk,D]; "bshd": q [B,Sq,Hq,D], k [B,Sk,Hkv,D]."""
+    if layout == "bhsd":
+        (b, hq, s, d), hkv, sk = q.shape, k.shape[1], k.shape[2]
+    elif layout == "bshd":
+        (b, s, hq, d), hkv, sk = q.shape, k.shape[2], k.shape[1]
+    else:
+        raise ValueError(f"unknown layout {layout!r}")
+    p = capi.new_params(batch=b, seqlen_q=s, seqlen_k=sk, num_heads_q=hq, num_heads_kv=hkv,
+                        head_dim_qk=d, head_dim_v=d, causal=int(causal), dtype=_DTYPES[q.dtype],
+                        layout=capi.LAYOUT_BSHD if layout == "bshd" else capi.LAYOUT_BHSD)
     if softmax_scale is not None:
         p.softmax_scale = float(softmax_scale)
         p.softmax_scale_is_set = 1
@@ -38,19 +46,21 @@ def _require_cuda(*tensors):
         if t is not None and not t.is_cuda:
             raise RuntimeError("flash_attention3_b200 has no CPU path: tensors must live on a CUDA device")
         if t is not None and not t.is_contiguous():
-            raise RuntimeError("BHSD-contiguous tensors are required")
+            raise RuntimeError("contiguous tensors are required ([B,H,S,D] or [B,S,H,D])")
 
 
 def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, deterministic=False,
-            workspace=None, return_delta=False, sync=False):
+            workspace=None, return_delta=False, sync=False, layout: str = "bhsd"):
     """dq, dk, dv (and delta) = backward of softmax(q k^T * scale) v.
 
-    q, out, dout: [B,Hq,S,D]; k, v: [B,Hkv,S,D]; fp16 or bf16; softmax_lse:
-    fp32 [B,Hq,S] natural log.  Calls shaobo_fa3_bwd_v2.
+    layout "bhsd": q, out, dout [B,Hq,Sq,D]; k, v [B,Hkv,Sk,D].  layout "bshd": [B,Sq,Hq,D] and
+    [B,Sk,Hkv,D].  fp16 or bf16; softmax_lse: fp32 [B,Hq,Sq] natural log in both layouts.  With
+    causal=True and Sq != Sk the diagonal is aligned bottom-right.  Calls shaobo_fa3_bwd_v2.
     """
     _require_cuda(dout, q, k, v, out, softmax_lse)
     lib = capi.load()
-    p = make_params(q, k, causal, softmax_scale, deterministic=int(deterministic), sync_after_launch=int(sync))
+    p = make_params(q, k, causal, softmax_scale, layout=layout, deterministic=int(deterministic),
+                    sync_after_launch=int(sync))
     need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
     if need == 0:
         raise Fa3Error("shaobo_fa3_bwd_v2_validate", lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(p)))
@@ -59,7 +69,8 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
     p.workspace = workspace.data_ptr()
     p.workspace_bytes = workspace.numel() * workspace.element_size()
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    delta = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if return_delta else None
+    delta = (torch.empty((p.batch, p.num_heads_q, p.seqlen_q), dtype=torch.float32, device=q.device)
+             if return_delta else None)
     with torch.cuda.device(q.device):
         p.reserved_ptr[capi.RESERVED_PTR_STREAM] = torch.cuda.current_stream().cuda_stream or None
         code = lib.shaobo_fa3_bwd_v2(_ptr(dout), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(softmax_lse),

@@ -82,12 +82,13 @@ int main() {
     expect("caps.required bits", (caps.feature_mask & required) == required, 1);
     const ShaoboFa3BwdFeatureMask absent =
         SHAOBO_FA3_BWD_FEATURE_VARLEN | SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW |
-        SHAOBO_FA3_BWD_FEATURE_SOFTCAP | SHAOBO_FA3_BWD_FEATURE_BSHD;
+        SHAOBO_FA3_BWD_FEATURE_SOFTCAP;
+    expect("caps.bshd", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_BSHD) != 0, 1);
     expect("caps.absent bits", (caps.feature_mask & absent) == 0, 1);
     expect("caps.min_head_dim", caps.min_head_dim, 64);
     expect("caps.max_head_dim", caps.max_head_dim, 128);
     expect("caps.head_dim_alignment", caps.head_dim_alignment, 64);
-    expect("caps.sequence_alignment", caps.sequence_alignment, 128);
+    expect("caps.sequence_alignment", caps.sequence_alignment, 1);
 
     // accepted configurations
     ShaoboFa3Params p = good();
@@ -119,8 +120,11 @@ int main() {
     expect("dropout", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
     p = good(); p.dtype = SHAOBO_FA3_DTYPE_FP8;
     expect("fp8", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
+    // wider than the reference: [B,S,H,D], seqlen_q != seqlen_k and ragged lengths are accepted
     p = good(); p.layout = SHAOBO_FA3_LAYOUT_BSHD;
-    expect("bshd", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
+    expect("bshd", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
+    p = good(); p.layout = 2;
+    expect("unknown layout", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
     p = good(); int32_t cu[2] = {0, 1024}; p.cu_seqlens_q = cu;
     expect("varlen", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
     p = good(); p.sm_margin = 1;
@@ -130,9 +134,11 @@ int main() {
     p = good(); p.head_dim_v = 64;
     expect("head_dim_v != head_dim_qk", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
     p = good(); p.seqlen_k = 2048;
-    expect("seqlen_q != seqlen_k", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
+    expect("seqlen_q != seqlen_k", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
     p = good(); p.seqlen_q = p.seqlen_k = 1000;
-    expect("seqlen % 128", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
+    expect("seqlen % 128", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
+    expect("ragged length has a workspace", (long long)shaobo_fa3_bwd_v2_workspace_bytes(&p) > 0, 1);
+    p = good(); p.head_dim_qk = p.head_dim_v = 96;
     expect("unsupported -> zero workspace", (long long)shaobo_fa3_bwd_v2_workspace_bytes(&p), 0);
 
     // malformed input
@@ -161,7 +167,7 @@ int main() {
     expect("v2 no workspace", shaobo_fa3_bwd_v2(x, x, x, x, x, x, x, x, x, nullptr, &p), SHAOBO_FA3_STATUS_INVALID_VALUE);
     p.workspace = x; p.workspace_bytes = shaobo_fa3_bwd_v2_workspace_bytes(&p) - 1;
     expect("v2 short workspace", shaobo_fa3_bwd_v2(x, x, x, x, x, x, x, x, x, nullptr, &p), SHAOBO_FA3_STATUS_INVALID_VALUE);
-    p = good(); p.layout = SHAOBO_FA3_LAYOUT_BSHD;
+    p = good(); p.dtype = SHAOBO_FA3_DTYPE_FP8;
     expect("v2 unsupported", shaobo_fa3_bwd_v2(x, x, x, x, x, x, x, x, x, nullptr, &p), SHAOBO_FA3_STATUS_UNSUPPORTED);
     p = good();
     expect("fused5 null", shaobo_fa3_bwd_fused5(x, x, x, x, nullptr, x, x, x, &p), SHAOBO_FA3_STATUS_INVALID_VALUE);

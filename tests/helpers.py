@@ -32,28 +32,39 @@ def poison(shape, dtype, device="cuda"):
 class Problem:
     """Seeded (or closed-form) inputs plus the oracle's answers."""
 
-    def __init__(self, b, hq, hkv, s, d, dtype, causal, seed=None, scale=None):
+    def __init__(self, b, hq, hkv, s, d, dtype, causal, seed=None, scale=None, sk=None, layout="bhsd"):
+        """s: query length; sk: key length when it differs; layout: how the device tensors are laid
+        out ("bhsd" or "bshd") -- the oracle always works on [B,H,S,D]."""
         self.b, self.hq, self.hkv, self.s, self.d = b, hq, hkv, s, d
+        self.sk = s if sk is None else sk
+        self.layout = layout
         self.dtype, self.causal = dtype, causal
         self.scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
         if seed is None:
-            assert dtype == "fp16"
+            assert dtype == "fp16" and self.sk == s
             self.q, self.k, self.v, self.do = golden.pattern_inputs(b, hq, hkv, s, d)
         else:
-            self.q, self.k, self.v, self.do = golden.seeded_inputs(seed, b, hq, hkv, s, d, dtype)
+            self.q, self.k, self.v, self.do = golden.seeded_inputs(seed, b, hq, hkv, s, d, dtype, sk=self.sk)
         self.ref = golden.backward(self.q, self.k, self.v, self.do, causal, self.scale, dtype)
 
+    def to_layout(self, x: np.ndarray) -> np.ndarray:
+        """[B,H,S,D] -> the device layout of this problem."""
+        return np.ascontiguousarray(x.transpose(0, 2, 1, 3)) if self.layout == "bshd" else x
+
+    def from_layout(self, x: np.ndarray) -> np.ndarray:
+        return np.ascontiguousarray(x.transpose(0, 2, 1, 3)) if self.layout == "bshd" else x
+
     def device_inputs(self):
-        t = self.dtype
-        return dict(q=dev(self.q, t), k=dev(self.k, t), v=dev(self.v, t), dout=dev(self.do, t),
-                    out=dev(self.ref["out"], t), lse=dev(self.ref["lse"]))
+        t, f = self.dtype, self.to_layout
+        return dict(q=dev(f(self.q), t), k=dev(f(self.k), t), v=dev(f(self.v), t), dout=dev(f(self.do), t),
+                    out=dev(f(self.ref["out"]), t), lse=dev(self.ref["lse"]))
 
 
 def run_v2(prob: Problem, deterministic=False, pass_scale=True, poison_ws=True):
     """Call shaobo_fa3_bwd_v2 through ctypes with NaN-poisoned outputs and workspace."""
     lib = capi.load()
     x = prob.device_inputs()
-    p = ops.make_params(x["q"], x["k"], prob.causal, prob.scale if pass_scale else None,
+    p = ops.make_params(x["q"], x["k"], prob.causal, prob.scale if pass_scale else None, layout=prob.layout,
                         deterministic=int(deterministic), sync_after_launch=1)
     need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
     assert need > 0
@@ -68,7 +79,9 @@ def run_v2(prob: Problem, deterministic=False, pass_scale=True, poison_ws=True):
                                  vp(dq), vp(dk), vp(dv), vp(delta), ctypes.byref(p))
     torch.cuda.synchronize()
     dev_err = lib.shaobo_fa3_b200_device_error(1)
-    return dict(code=code, device_error=dev_err, dq=host(dq), dk=host(dk), dv=host(dv), delta=host(delta))
+    back = prob.from_layout
+    return dict(code=code, device_error=dev_err, dq=back(host(dq)), dk=back(host(dk)), dv=back(host(dv)),
+                delta=host(delta))
 
 
 def metrics(result: dict, prob: Problem, out_dtype="storage") -> dict:
