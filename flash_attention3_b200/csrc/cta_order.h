@@ -1,7 +1,8 @@
 // Host-side choice of the CTA launch order for the causal backward.
 //
 // A CTA that owns key tile kt walks the query tiles that see it (n_tiles - kt of
-// them per query head when seqlen_q == seqlen_k), so work per CTA falls with kt.  The B200 block scheduler hands the
+// them per query head when seqlen_q == seqlen_k), so work per CTA falls with kt.
+// The B200 block scheduler hands the
 // next block index to whichever SM frees up first, which is greedy list
 // scheduling; the plan below simulates exactly that for a few candidate orders
 // and keeps the one with the smallest modelled makespan.  This plays the role

@@ -496,18 +496,17 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             uint32_t ppk[32];
             const float* side_base = a.sidecar;
             float s0 = 0.f, s1 = 0.f, s2 = 0.f;
-            // statistics of query row qi of head hq; rows past the end of the sequence get r = 0, which
-            // makes their P (and with it dS) exactly zero
+            bool s_valid = false;
+            // Statistics of query row qi of head hq, fetched one step ahead.  The loaded values are
+            // not touched here (their first use, one step later, is what waits for the loads); rows
+            // past the end of the sequence read row 0 instead and are replaced at that first use.
             auto load_stats = [&](int hq, int qt) {
                 const int qi = qt * C::kTile + j;
-                const bool valid = qi < a.seqlen_q;
-                const int64_t row = int64_t(b * a.heads_q + hq) * a.seqlen_q + (valid ? qi : 0);
-                const float v0 = side_base[row * 3 + 0];
-                const float v1 = side_base[row * 3 + 1];
-                const float v2 = side_base[row * 3 + 2];
-                s0 = valid ? v0 : 0.f;
-                s1 = valid ? v1 : 0.f;
-                s2 = valid ? v2 : 0.f;
+                s_valid = qi < a.seqlen_q;
+                const int64_t row = int64_t(b * a.heads_q + hq) * a.seqlen_q + (s_valid ? qi : 0);
+                s0 = side_base[row * 3 + 0];
+                s1 = side_base[row * 3 + 1];
+                s2 = side_base[row * 3 + 2];
             };
             // the sidecar comes from the delta kernel, which may still be running (programmatic launch);
             // Q, K, V, dO are inputs of the call, so the TMA and MMA warps did not have to wait
@@ -530,8 +529,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 const float* delp = stats + 256 + buf * 128 + half * 64;
                 if (half == 0) {
                     // row statistics of query row j of this tile, for both warpgroups
-                    stats[buf * 128 + j] = __log2f(s1) - s0;  // P = exp2(x - m) * r = exp2(x + (log2 r - m))
-                    stats[256 + buf * 128 + j] = s2;
+                    // P = exp2(x - m) * r = exp2(x + (log2 r - m)); a row past the end of the sequence
+                    // gets -inf, which makes its P (and with it dS) exactly zero
+                    stats[buf * 128 + j] = s_valid ? __log2f(s1) - s0 : -INFINITY;
+                    stats[256 + buf * 128 + j] = s_valid ? s2 : 0.f;
                     ptx::mbar_arrive(bar(kStatsFull + buf));
                     if (t + 1 < n_steps) {
                         int hq1, qt1;
@@ -552,7 +553,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                       : kCausal        ? key - causal_off - qt * C::kTile
                                                        : -(1 << 30);
                 // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked as above.
-                                auto softmax_chunk = [&](int c, const uint32_t* r) {
+                // (two copies of the chunk code, so that unmasked tiles carry no per-element test)
+                auto softmax_chunk = [&](int c, const uint32_t* r, auto masked_tag) {
+                    constexpr bool kMasked = decltype(masked_tag)::value;
 #ifdef FA3B200_DEBUG_DUMP
                     if (blockIdx.x == 0 && t == 0)
                         for (int e = 0; e < 32; ++e)
@@ -569,7 +572,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, n4.y));
                         float p2 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 2]), a.scale_log2, n4.z));
                         float p3 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 3]), a.scale_log2, n4.w));
-                        if (diagonal) {
+                        if (kMasked) {
                             const int i = half * 64 + c * 32 + e;
                             p0 = (i + 0 >= mask_from) ? p0 : 0.0f;
                             p1 = (i + 1 >= mask_from) ? p1 : 0.0f;
@@ -582,12 +585,22 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     // P chunk c -> columns [16c, 16c+16) of this half's S columns (already read)
                     ptx::tmem_st16(s_cols + c * 16, &ppk[c * 16]);
                 };
+                if (diagonal) {
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    ptx::tmem_ld32(s_cols + c * 32, r);
-                    ptx::tmem_ld_wait();
-                    softmax_chunk(c, r);
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(s_cols + c * 32, r);
+                        ptx::tmem_ld_wait();
+                        softmax_chunk(c, r, std::true_type{});
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(s_cols + c * 32, r);
+                        ptx::tmem_ld_wait();
+                        softmax_chunk(c, r, std::false_type{});
+                    }
                 }
                 DBG_STAMP(3);
                 ptx::tmem_st_wait();

@@ -175,9 +175,18 @@ int shaobo_fa3_bwd_v2_validate(const ShaoboFa3Params* params);
 size_t shaobo_fa3_bwd_v2_workspace_bytes(const ShaoboFa3Params* params);
 
 /* Attention backward.  softmax_lse is the natural-log LSE of the forward,
- * fp32 [B,Hq,S]; softmax_d is optional (may be NULL) and receives
- * delta = rowsum(dout * out) in fp32 [B,Hq,S].  dq, dk, dv are written in the
- * input dtype.  Replaces reference src/shaobo_fa3_bwd_api.cpp:206-260. */
+ * fp32 [B,Hq,Sq]; softmax_d is optional (may be NULL) and receives
+ * delta = rowsum(dout * out) in fp32 [B,Hq,Sq].  dq, dk, dv are written in the
+ * input dtype.  Replaces reference src/shaobo_fa3_bwd_api.cpp:206-260.
+ *
+ * Wider than the reference (which returns UNSUPPORTED for all three,
+ * src/shaobo_fa3_bwd_api.cpp:109-118):
+ *  - params->layout = BSHD: q, out, dout, dq are [B,Sq,Hq,D] and k, v, dk, dv
+ *    are [B,Sk,Hkv,D], contiguous; softmax_lse and softmax_d stay [B,Hq,Sq].
+ *  - seqlen_q and seqlen_k need not be multiples of 128.
+ *  - seqlen_q != seqlen_k; with causal = 1 the diagonal is aligned to the
+ *    bottom-right corner: query i sees key j iff j <= i + seqlen_k - seqlen_q.
+ *    A query that sees no key (softmax_lse = -inf) gets a zero gradient. */
 int shaobo_fa3_bwd_v2(const void* dout,
                       const void* q,
                       const void* k,
