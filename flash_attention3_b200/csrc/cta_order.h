@@ -24,11 +24,19 @@ namespace fa3b200 {
 // Tile grid of one head: which query tiles each key tile visits.
 struct TileWork {
     int n_k_tiles = 0;
-    int n_q_tiles = 0;
-    int causal_off = 0;  // seqlen_k - seqlen_q
-    bool causal = false;
-    int steps(int kt) const { return q_tiles_of_k_tile(kt, n_q_tiles, causal_off, causal); }
-    static TileWork square(int n_tiles, bool causal) { return TileWork{n_tiles, n_tiles, 0, causal}; }
+    Band band{};
+    bool causal = false;  // the band is bounded: work differs between key tiles
+    int steps(int kt) const { return q_tiles_of_k_tile(kt, band); }
+    static TileWork of(const Band& band) {
+        TileWork w;
+        w.n_k_tiles = tiles_of(band.seqlen_k);
+        w.band = band;
+        w.causal = !band_is_full(band);
+        return w;
+    }
+    static TileWork square(int n_tiles, bool causal) {
+        return of(make_band(n_tiles * kTileRows, n_tiles * kTileRows, causal, -1, -1));
+    }
 };
 
 enum CtaOrderMode : int {

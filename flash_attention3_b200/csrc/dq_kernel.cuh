@@ -35,8 +35,7 @@ struct DqArgs {
     int batch;
     int heads_q;
     int heads_kv;
-    int seqlen_q;
-    int seqlen_k;
+    Band band;                // sequence lengths and the visible band (geometry.h)
     float scale;
     float scale_log2;
 };
@@ -88,9 +87,7 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kDqbNum);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
-    const int n_q_tiles = tiles_of(a.seqlen_q);
-    const int n_k_tiles = tiles_of(a.seqlen_k);
-    const int causal_off = a.seqlen_k - a.seqlen_q;  // query i sees key j iff j <= i + causal_off
+    const int n_q_tiles = tiles_of(a.band.seqlen_q);
     const int bh_count = a.batch * a.heads_q;
     // heaviest query tiles (most visible keys) are launched first
     const int qt = kCausal ? n_q_tiles - 1 - int(blockIdx.x) / bh_count : int(blockIdx.x) / bh_count;
@@ -98,8 +95,9 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int b = bhi / a.heads_q;
     const int hq = bhi % a.heads_q;
     const int kvh = hq / (a.heads_q / a.heads_kv);
-    // key tiles 0 .. n_steps-1, the diagonal ones last; 0 when no key is visible (causal, Sq > Sk)
-    const int n_steps = k_tiles_of_q_tile(qt, n_k_tiles, causal_off, kCausal);
+    // key tiles k_begin .. k_begin + n_steps - 1 in ascending order; none when no key is visible
+    const int k_begin = first_k_tile(qt, a.band);
+    const int n_steps = k_tiles_of_q_tile(qt, a.band);
     const bool misaligned = (sbase & 1023u) != 0;
 
     if (threadIdx.x == 0) {
@@ -143,7 +141,7 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll 1
                 for (int t = 0; t < n_steps; ++t) {
                     const int s = t & 1;
-                    const int kv_row = t * C::kTile;
+                    const int kv_row = (k_begin + t) * C::kTile;
                     if (!bounded_wait(bar(kDqbKvEmpty + s), ((t >> 1) & 1) ^ 1, abort_flag)) break;
                     ptx::mbar_arrive_expect_tx(bar(kDqbKvFull + s), 2 * C::kOperandBytes);
 #pragma unroll
@@ -220,9 +218,9 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const int i = threadIdx.x - 128;  // query row inside the tile == TMEM lane
             const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
             const int qi = q_row + i;  // query row inside the head
-            const bool q_valid = qi < a.seqlen_q;
+            const bool q_valid = qi < a.band.seqlen_q;
             // rows past the end of the sequence: P = exp2(-inf) = 0
-            const float* side = a.sidecar + (int64_t(b * a.heads_q + hq) * a.seqlen_q + (q_valid ? qi : 0)) * 3;
+            const float* side = a.sidecar + (int64_t(b * a.heads_q + hq) * a.band.seqlen_q + (q_valid ? qi : 0)) * 3;
             const float neg = q_valid ? __log2f(side[1]) - side[0] : -INFINITY;
             const float delta = q_valid ? side[2] : 0.0f;
             uint32_t ppk[64];
@@ -231,11 +229,10 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             for (int t = 0; t < n_steps; ++t) {
                 if (!(ok = warp_wait(bar(kDqbSFull), t & 1, abort_flag))) break;
                 ptx::tc_fence_after();
-                // element (query i, key j) survives iff j <= mask_to (diagonal and end of the key sequence)
-                const bool diagonal = tile_needs_mask(t, qt, a.seqlen_k, causal_off, kCausal);
-                const int last_key = a.seqlen_k - 1 - t * C::kTile;
-                const int diag_key = kCausal ? qi + causal_off - t * C::kTile : (1 << 30);
-                const int mask_to = last_key < diag_key ? last_key : diag_key;
+                // element (query i, key j) survives iff mask_from <= j <= mask_to (band edges, end of keys)
+                const bool diagonal = kCausal && tile_needs_mask(k_begin + t, qt, a.band);
+                int mask_from, mask_to;
+                key_range_of_query(qi, (k_begin + t) * C::kTile, a.band, &mask_from, &mask_to);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t r[32];
@@ -247,8 +244,8 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                         float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, neg));
                         if (diagonal) {
                             const int j = c * 32 + e;
-                            p0 = (j + 0 <= mask_to) ? p0 : 0.0f;
-                            p1 = (j + 1 <= mask_to) ? p1 : 0.0f;
+                            p0 = (j + 0 >= mask_from && j + 0 <= mask_to) ? p0 : 0.0f;
+                            p1 = (j + 1 >= mask_from && j + 1 <= mask_to) ? p1 : 0.0f;
                         }
                         ppk[c * 16 + e / 2] = ptx::Pack2<T>::pack(p0, p1);
                     }

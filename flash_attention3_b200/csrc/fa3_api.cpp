@@ -38,14 +38,11 @@ bool is_flag(int32_t v) { return v == 0 || v == 1; }
 
 bool finite_nonneg(float v) { return std::isfinite(v) && v >= 0.0f; }
 
-// A window that covers every key a causal / full mask would cover counts as
-// "no window" (reference src/shaobo_fa3_bwd_api.cpp:53-68).
-bool window_is_plain(const ShaoboFa3Params* p) {
-    int left = p->window_left >= p->seqlen_k - 1 ? -1 : p->window_left;
-    int right = p->window_right >= p->seqlen_q - 1 ? -1 : p->window_right;
-    if (p->causal != 0) right = 0;
-    if (left >= 0) return false;
-    return p->causal != 0 ? right == 0 : right < 0;
+// The reference only takes windows that cover every key a causal / full mask would cover
+// (src/shaobo_fa3_bwd_api.cpp:53-68); here any window is accepted, negative = unbounded, and
+// make_band() applies the same normalisation (causal forces right = 0).
+bool lengths_in_range(const ShaoboFa3Params* p) {
+    return p->seqlen_q < kUnbounded && p->seqlen_k < kUnbounded;
 }
 
 bool lengths_are_fixed(const ShaoboFa3Params* p) {
@@ -84,11 +81,12 @@ int validate_v2(const ShaoboFa3Params* p) {
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     // ---- well-formed but outside the capability set: UNSUPPORTED ------------
-    // (wider than the reference, which also turns away the [B,S,H,D] layout, seqlen_q != seqlen_k
-    // and sequence lengths that are not multiples of 128: src/shaobo_fa3_bwd_api.cpp:109-118)
+    // (wider than the reference, which also turns away the [B,S,H,D] layout, seqlen_q != seqlen_k,
+    // sequence lengths that are not multiples of 128 and sliding windows:
+    // src/shaobo_fa3_bwd_api.cpp:109-118)
     if (!lengths_are_fixed(p) || !dtype_supported(p->dtype) || !layout_supported(p->layout) ||
         !head_dim_supported(p->head_dim_qk) || p->head_dim_v != p->head_dim_qk ||
-        p->dropout_p != 0.0f || p->softcap != 0.0f || p->sm_margin != 0 || !window_is_plain(p)) {
+        p->dropout_p != 0.0f || p->softcap != 0.0f || p->sm_margin != 0 || !lengths_in_range(p)) {
         return SHAOBO_FA3_STATUS_UNSUPPORTED;
     }
     return SHAOBO_FA3_STATUS_SUCCESS;
@@ -116,16 +114,19 @@ SplitPlan split_plan(const ShaoboFa3Params* p) {
     SplitPlan plan;
     if (!fused_shape_ok(p) || p->deterministic != 0) return plan;
     const int tiles = tiles_of(p->seqlen_k);
-    const int q_tiles = tiles_of(p->seqlen_q);
-    const int causal_off = p->seqlen_k - p->seqlen_q;
+    const Band band = band_of(p);
     const long long heads = (long long)p->batch * p->num_heads_kv;
     if (tiles * heads >= kSplitSmCount) return plan;
     const long long group = p->num_heads_q / p->num_heads_kv;
-    const long long longest = group * q_tiles;  // steps of the heaviest key tile
+    long long longest = 0;  // steps of the heaviest key tile
+    for (int kt = 0; kt < tiles; ++kt) {
+        const long long steps = group * q_tiles_of_k_tile(kt, band);
+        if (steps > longest) longest = steps;
+    }
     for (long long chunk = 1; chunk < longest; ++chunk) {
         long long per_head = 0;
         for (int kt = 0; kt < tiles; ++kt) {
-            const long long steps = group * q_tiles_of_k_tile(kt, q_tiles, causal_off, p->causal != 0);
+            const long long steps = group * q_tiles_of_k_tile(kt, band);
             per_head += (steps + chunk - 1) / chunk;
         }
         if (per_head * heads <= kSplitSmCount) {
@@ -208,12 +209,13 @@ extern "C" int shaobo_fa3_bwd_get_capabilities(ShaoboFa3BwdCapabilities* caps) {
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     caps->api_version = SHAOBO_FA3_API_VERSION;
-    // The reference's set (src/shaobo_fa3_bwd_api.cpp:180-187) plus BF16 and the [B,S,H,D] layout.
+    // The reference's set (src/shaobo_fa3_bwd_api.cpp:180-187) plus BF16, the [B,S,H,D] layout
+    // and sliding windows.
     caps->feature_mask = SHAOBO_FA3_BWD_FEATURE_FIXED_LENGTH | SHAOBO_FA3_BWD_FEATURE_FP16 |
                          SHAOBO_FA3_BWD_FEATURE_BF16 | SHAOBO_FA3_BWD_FEATURE_CAUSAL |
                          SHAOBO_FA3_BWD_FEATURE_GQA | SHAOBO_FA3_BWD_FEATURE_DETERMINISTIC |
                          SHAOBO_FA3_BWD_FEATURE_SOFTMAX_LSE | SHAOBO_FA3_BWD_FEATURE_BHSD |
-                         SHAOBO_FA3_BWD_FEATURE_BSHD |
+                         SHAOBO_FA3_BWD_FEATURE_BSHD | SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW |
                          SHAOBO_FA3_BWD_FEATURE_FULL_ATTENTION;
     caps->min_head_dim = kMinHeadDim;
     caps->max_head_dim = kMaxHeadDim;

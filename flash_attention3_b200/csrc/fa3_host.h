@@ -30,6 +30,12 @@ inline bool dtype_supported(int t) {
     return t == SHAOBO_FA3_DTYPE_FP16 || t == SHAOBO_FA3_DTYPE_BF16;
 }
 
+// The visible band of a parameter block (window_left / window_right: negative = unbounded; causal
+// forces right = 0, as reference src/shaobo_fa3_bwd_api.cpp:53-68 normalises it).
+inline Band band_of(const ShaoboFa3Params* p) {
+    return make_band(p->seqlen_q, p->seqlen_k, p->causal != 0, p->window_left, p->window_right);
+}
+
 // Public validation used by every v2 entry.
 int validate_v2(const ShaoboFa3Params* p);
 

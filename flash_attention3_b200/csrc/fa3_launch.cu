@@ -73,6 +73,12 @@ bool make_map_accum(CUtensorMap* map, const float* base, int64_t batch_heads, in
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The kernels come in two forms: a lean one for full attention over whole 128-row tiles and a general
+// one (causal mask, sliding window, ragged sequence ends).
+bool needs_general_form(const ShaoboFa3Params* p) {
+    return !band_is_full(band_of(p)) || p->seqlen_q % kTileRows != 0 || p->seqlen_k % kTileRows != 0;
+}
+
 bool is_bshd(const ShaoboFa3Params* p) { return p->layout == SHAOBO_FA3_LAYOUT_BSHD; }
 
 RowLayout row_layout(const ShaoboFa3Params* p, int heads, int seqlen) {
@@ -104,9 +110,9 @@ int sm_count() {
 
 CtaOrderPlan cached_plan(const TileWork& work, int bh, int group, int sms, long long dq_bytes) {
     static std::mutex mu;
-    static std::map<std::tuple<int, int, int, bool, int, int, int, long long>, CtaOrderPlan> cache;
-    const auto key = std::make_tuple(work.n_k_tiles, work.n_q_tiles, work.causal_off, work.causal, bh,
-                                     group, sms, dq_bytes);
+    static std::map<std::tuple<int, int, int, int, int, int, int, long long>, CtaOrderPlan> cache;
+    const auto key = std::make_tuple(work.band.seqlen_q, work.band.seqlen_k, work.band.left,
+                                     work.band.right, bh, group, sms, dq_bytes);
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
@@ -286,11 +292,12 @@ int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtens
                    const CUtensorMap& mdk, const CUtensorMap& mdv, const FusedArgs& args, int blocks,
                    bool pdl) {
     cudaStream_t st = stream_of(p);
+    const bool banded = needs_general_form(p);
     if (p->head_dim_qk == 128) {
-        return p->causal ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
+        return banded ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
                          : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
     }
-    return p->causal ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
+    return banded ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
                      : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
 }
 
@@ -334,11 +341,8 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
         mdv = mq;
     }
     const int n_tiles = tiles_of(p->seqlen_k);
-    TileWork work;
-    work.n_k_tiles = n_tiles;
-    work.n_q_tiles = tiles_of(p->seqlen_q);
-    work.causal_off = p->seqlen_k - p->seqlen_q;
-    work.causal = p->causal != 0;
+    const Band band = band_of(p);
+    const TileWork work = TileWork::of(band);
     const int bh = p->batch * p->num_heads_kv;
     const int group = p->num_heads_q / p->num_heads_kv;
     // bytes of dQ accumulator behind one (batch, KV head): only the fused path adds into it
@@ -354,8 +358,7 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     args.batch = p->batch;
     args.heads_q = p->num_heads_q;
     args.heads_kv = p->num_heads_kv;
-    args.seqlen_q = p->seqlen_q;
-    args.seqlen_k = p->seqlen_k;
+    args.band = band;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
     args.order_mode = plan.mode;
@@ -399,11 +402,12 @@ template <typename T, typename TOut>
 int launch_dq_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorMap& mk,
                 const CUtensorMap& mv, const CUtensorMap& mdo, const DqArgs& args, int blocks) {
     cudaStream_t st = stream_of(p);
+    const bool banded = needs_general_form(p);
     if (p->head_dim_qk == 128) {
-        return p->causal ? launch_dq_t<T, 128, true, TOut>(mq, mk, mv, mdo, args, blocks, st)
+        return banded ? launch_dq_t<T, 128, true, TOut>(mq, mk, mv, mdo, args, blocks, st)
                          : launch_dq_t<T, 128, false, TOut>(mq, mk, mv, mdo, args, blocks, st);
     }
-    return p->causal ? launch_dq_t<T, 64, true, TOut>(mq, mk, mv, mdo, args, blocks, st)
+    return banded ? launch_dq_t<T, 64, true, TOut>(mq, mk, mv, mdo, args, blocks, st)
                      : launch_dq_t<T, 64, false, TOut>(mq, mk, mv, mdo, args, blocks, st);
 }
 
@@ -429,8 +433,7 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
     args.batch = p->batch;
     args.heads_q = p->num_heads_q;
     args.heads_kv = p->num_heads_kv;
-    args.seqlen_q = p->seqlen_q;
-    args.seqlen_k = p->seqlen_k;
+    args.band = band_of(p);
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
     const int64_t blocks64 = int64_t(tiles_of(p->seqlen_q)) * p->batch * p->num_heads_q;

@@ -89,8 +89,7 @@ struct FusedArgs {
     int batch;
     int heads_q;
     int heads_kv;
-    int seqlen_q;
-    int seqlen_k;
+    Band band;             // sequence lengths and the visible band (geometry.h)
     float scale;
     float scale_log2;
     int order_mode;        // see cta_order.h
@@ -208,6 +207,11 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity,
     return __all_sync(0xffffffffu, ok);
 }
 
+// kCausal: general form -- the visible band may be bounded (causal mask, sliding window) and the
+// sequence lengths need not be multiples of 128; tiles that need it are masked in registers and the
+// query tiles of a key tile are walked in ascending order from the first one that sees it.
+// false = full attention over whole tiles only: no masking code at all, query sweep rotated per CTA
+// (measured: carrying the unused masking code costs the D=64 full-attention kernel 6 %).
 // T: storage type of Q/K/V/dO (__half or __nv_bfloat16).  TOut: type of the dK
 // and dV outputs (T for the fused path, float for the split path).  kWithDq:
 // false turns the kernel into the four-GEMM dK/dV half of the split path.
@@ -229,9 +233,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     // ---- which tile is ours ------------------------------------------------
-    const int n_tiles = tiles_of(a.seqlen_k);      // key tiles
-    const int n_q_tiles = tiles_of(a.seqlen_q);
-    const int causal_off = a.seqlen_k - a.seqlen_q;  // query i sees key j iff j <= i + causal_off
+    const int n_tiles = tiles_of(a.band.seqlen_k);      // key tiles
+    const int n_q_tiles = tiles_of(a.band.seqlen_q);
     const int bh_count = a.batch * a.heads_kv;
     const bool split = a.chunk_steps > 0;
     const int group = a.heads_q / a.heads_kv;
@@ -251,7 +254,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         int rest = int(blockIdx.x) % a.chunks_per_head;
         kt = 0;
         while (true) {
-            const int steps = group * q_tiles_of_k_tile(kt, n_q_tiles, causal_off, kCausal);
+            const int steps = group * q_tiles_of_k_tile(kt, a.band);
             const int chunks = (steps + a.chunk_steps - 1) / a.chunk_steps;
             if (rest < chunks) break;
             rest -= chunks;
@@ -261,8 +264,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     const int b = bhi / a.heads_kv;
     const int kvh = bhi % a.heads_kv;
-    const int q_begin = first_q_tile(kt, causal_off, kCausal);
-    const int steps_per_head = q_tiles_of_k_tile(kt, n_q_tiles, causal_off, kCausal);
+    const int q_begin = first_q_tile(kt, a.band);
+    const int steps_per_head = q_tiles_of_k_tile(kt, a.band);
     // this CTA's share of the tile's steps (all of them unless the tile is split)
     const int total_steps = group * steps_per_head;
     const int t_begin = t_begin_split;
@@ -270,8 +273,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int n_steps = t_end - t_begin;
     // "misaligned" also covers a CTA without work: every role is skipped, set-up and teardown still run
     const bool misaligned = (sbase & 1023u) != 0 || n_steps == 0;
-    // (with the diagonal aligned bottom-right the last query sees every key, so an unsplit key tile
-    // always has at least one step; n_steps == 0 only happens for surplus CTAs)
+    // an unsplit key tile that no query sees (possible with a left-bounded window) still owes zeros
+    // to dK / dV
+    const bool owes_zeros = !split && n_steps == 0 && (sbase & 1023u) == 0;
 
     if (threadIdx.x == 0) {
         if ((sbase & 1023u) != 0) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
@@ -308,6 +312,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // Query tiles are visited in ascending order starting at the diagonal (causal) or at a
     // per-CTA rotation (non-causal), so that CTAs of one head that run together add into
     // different dQ tiles at any moment.
+    const int rotation = kCausal ? 0 : kt % n_q_tiles;
     auto step_coords = [&](int t_local, int& hq, int& qt) {
         const int t = t_begin + t_local;
         const int g = t / steps_per_head;
@@ -316,7 +321,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (kCausal) {
             qt = q_begin + r;
         } else {
-            qt = r + kt % n_q_tiles;
+            qt = r + rotation;
             if (qt >= n_q_tiles) qt -= n_q_tiles;
         }
     };
@@ -502,8 +507,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // past the end of the sequence read row 0 instead and are replaced at that first use.
             auto load_stats = [&](int hq, int qt) {
                 const int qi = qt * C::kTile + j;
-                s_valid = qi < a.seqlen_q;
-                const int64_t row = int64_t(b * a.heads_q + hq) * a.seqlen_q + (s_valid ? qi : 0);
+                s_valid = qi < a.band.seqlen_q;
+                const int64_t row = int64_t(b * a.heads_q + hq) * a.band.seqlen_q + (s_valid ? qi : 0);
                 s0 = side_base[row * 3 + 0];
                 s1 = side_base[row * 3 + 1];
                 s2 = side_base[row * 3 + 2];
@@ -531,8 +536,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     // row statistics of query row j of this tile, for both warpgroups
                     // P = exp2(x - m) * r = exp2(x + (log2 r - m)); a row past the end of the sequence
                     // gets -inf, which makes its P (and with it dS) exactly zero
-                    stats[buf * 128 + j] = s_valid ? __log2f(s1) - s0 : -INFINITY;
-                    stats[256 + buf * 128 + j] = s_valid ? s2 : 0.f;
+                    stats[buf * 128 + j] = (!kCausal || s_valid) ? __log2f(s1) - s0 : -INFINITY;
+                    stats[256 + buf * 128 + j] = (!kCausal || s_valid) ? s2 : 0.f;
                     ptx::mbar_arrive(bar(kStatsFull + buf));
                     if (t + 1 < n_steps) {
                         int hq1, qt1;
@@ -545,13 +550,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (!(ok = warp_wait(bar(kSFull), t & 1, abort_flag))) break;
                 DBG_STAMP(2);
                 ptx::tc_fence_after();
-                // A tile that crosses the diagonal or holds keys past the end of the sequence is masked:
-                // element (key j, query i) survives iff i >= mask_from.
-                const bool diagonal = tile_needs_mask(kt, qt, a.seqlen_k, causal_off, kCausal);
-                const int key = kt * C::kTile + j;
-                const int mask_from = key >= a.seqlen_k ? (1 << 30)
-                                      : kCausal        ? key - causal_off - qt * C::kTile
-                                                       : -(1 << 30);
+                // A tile that crosses an edge of the band or holds keys past the end of the sequence is
+                // masked: element (key j, query i) survives iff mask_from <= i <= mask_to.
+                const bool diagonal = kCausal && tile_needs_mask(kt, qt, a.band);
+                int mask_from = 0, mask_to = 0;  // set only on masked tiles
                 // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked as above.
                 // (two copies of the chunk code, so that unmasked tiles carry no per-element test)
                 auto softmax_chunk = [&](int c, const uint32_t* r, auto masked_tag) {
@@ -574,10 +576,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         float p3 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 3]), a.scale_log2, n4.w));
                         if (kMasked) {
                             const int i = half * 64 + c * 32 + e;
-                            p0 = (i + 0 >= mask_from) ? p0 : 0.0f;
-                            p1 = (i + 1 >= mask_from) ? p1 : 0.0f;
-                            p2 = (i + 2 >= mask_from) ? p2 : 0.0f;
-                            p3 = (i + 3 >= mask_from) ? p3 : 0.0f;
+                            p0 = (i + 0 >= mask_from && i + 0 <= mask_to) ? p0 : 0.0f;
+                            p1 = (i + 1 >= mask_from && i + 1 <= mask_to) ? p1 : 0.0f;
+                            p2 = (i + 2 >= mask_from && i + 2 <= mask_to) ? p2 : 0.0f;
+                            p3 = (i + 3 >= mask_from && i + 3 <= mask_to) ? p3 : 0.0f;
                         }
                         ppk[c * 16 + e / 2 + 0] = ptx::Pack2<T>::pack(p0, p1);
                         ppk[c * 16 + e / 2 + 1] = ptx::Pack2<T>::pack(p2, p3);
@@ -586,6 +588,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     ptx::tmem_st16(s_cols + c * 16, &ppk[c * 16]);
                 };
                 if (diagonal) {
+                    query_range_of_key(kt * C::kTile + j, qt * C::kTile, a.band, &mask_from, &mask_to);
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
@@ -666,7 +669,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (ok && !split) {
                 // (tensor-memory loads are warp-wide: every lane runs them, only the stores of key rows
                 // past the end of the sequence are skipped)
-                const bool key_valid = kt * C::kTile + j < a.seqlen_k;
+                const bool key_valid = kt * C::kTile + j < a.band.seqlen_k;
                 ptx::tc_fence_after();
                 const int64_t off = b * a.kv_strides.batch + kvh * a.kv_strides.head +
                                     int64_t(kt * C::kTile + j) * a.kv_strides.row;
@@ -700,6 +703,16 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     }
                     __syncwarp();  // reconverge before the next warp-wide load
                 }
+            }
+        } else if (owes_zeros) {
+            // nobody attends to these keys: the first warpgroup clears dK, the second dV
+            const int j = threadIdx.x & 127;
+            if (kt * C::kTile + j < a.band.seqlen_k) {
+                const int64_t off = b * a.kv_strides.batch + kvh * a.kv_strides.head +
+                                    int64_t(kt * C::kTile + j) * a.kv_strides.row;
+                uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<TOut*>(wg == 1 ? a.dk : a.dv) + off);
+#pragma unroll
+                for (int e = 0; e < int(D * sizeof(TOut) / 16); ++e) d4[e] = make_uint4(0u, 0u, 0u, 0u);
             }
         }
     } else {
@@ -763,7 +776,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         __syncwarp();
 #ifndef FA3B200_EXPERIMENT_NOREDUCE
                         // accumulator map: [batch*head][row][D]; rows past the sequence end are dropped
-                        if (lane == 0 && q_row < a.seqlen_q) {
+                        if (lane == 0 && q_row < a.band.seqlen_q) {
                             ptx::tma_reduce_add_3d(&tm_dqacc, stage, hf * 64, q_row, q_head);
                             ptx::tma_reduce_add_3d(&tm_dqacc, stage + C::kStageBoxBytes, hf * 64 + 32, q_row, q_head);
                             ptx::bulk_commit_group();
@@ -806,7 +819,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         }
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0 && row0 < a.seqlen_k) {
+                        if (lane == 0 && row0 < a.band.seqlen_k) {
 #pragma unroll
                             for (int bx = 0; bx < 2 * kBoxesPerTensor; ++bx) {
                                 const int which = bx / kBoxesPerTensor;

@@ -50,17 +50,19 @@ def _require_cuda(*tensors):
 
 
 def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, deterministic=False,
-            workspace=None, return_delta=False, sync=False, layout: str = "bhsd"):
+            workspace=None, return_delta=False, sync=False, layout: str = "bhsd", window=(-1, -1)):
     """dq, dk, dv (and delta) = backward of softmax(q k^T * scale) v.
 
     layout "bhsd": q, out, dout [B,Hq,Sq,D]; k, v [B,Hkv,Sk,D].  layout "bshd": [B,Sq,Hq,D] and
     [B,Sk,Hkv,D].  fp16 or bf16; softmax_lse: fp32 [B,Hq,Sq] natural log in both layouts.  With
-    causal=True and Sq != Sk the diagonal is aligned bottom-right.  Calls shaobo_fa3_bwd_v2.
+    causal=True and Sq != Sk the diagonal is aligned bottom-right.  window = (left, right): query i
+    sees keys i+off-left .. i+off+right (off = Sk - Sq), -1 = unbounded; causal forces right = 0.
+    Calls shaobo_fa3_bwd_v2.
     """
     _require_cuda(dout, q, k, v, out, softmax_lse)
     lib = capi.load()
     p = make_params(q, k, causal, softmax_scale, layout=layout, deterministic=int(deterministic),
-                    sync_after_launch=int(sync))
+                    sync_after_launch=int(sync), window_left=int(window[0]), window_right=int(window[1]))
     need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
     if need == 0:
         raise Fa3Error("shaobo_fa3_bwd_v2_validate", lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(p)))

@@ -179,14 +179,17 @@ size_t shaobo_fa3_bwd_v2_workspace_bytes(const ShaoboFa3Params* params);
  * delta = rowsum(dout * out) in fp32 [B,Hq,Sq].  dq, dk, dv are written in the
  * input dtype.  Replaces reference src/shaobo_fa3_bwd_api.cpp:206-260.
  *
- * Wider than the reference (which returns UNSUPPORTED for all three,
- * src/shaobo_fa3_bwd_api.cpp:109-118):
+ * Wider than the reference (which returns UNSUPPORTED for all of these,
+ * src/shaobo_fa3_bwd_api.cpp:53-68,109-118):
  *  - params->layout = BSHD: q, out, dout, dq are [B,Sq,Hq,D] and k, v, dk, dv
  *    are [B,Sk,Hkv,D], contiguous; softmax_lse and softmax_d stay [B,Hq,Sq].
  *  - seqlen_q and seqlen_k need not be multiples of 128.
  *  - seqlen_q != seqlen_k; with causal = 1 the diagonal is aligned to the
  *    bottom-right corner: query i sees key j iff j <= i + seqlen_k - seqlen_q.
- *    A query that sees no key (softmax_lse = -inf) gets a zero gradient. */
+ *    A query that sees no key (softmax_lse = -inf) gets a zero gradient.
+ *  - window_left / window_right >= 0: sliding window, query i sees keys
+ *    i + off - window_left .. i + off + window_right (off = seqlen_k - seqlen_q);
+ *    a negative side is unbounded and causal = 1 forces window_right = 0. */
 int shaobo_fa3_bwd_v2(const void* dout,
                       const void* q,
                       const void* k,

@@ -81,9 +81,9 @@ int main() {
     expect("caps.api_version", caps.api_version, SHAOBO_FA3_API_VERSION);
     expect("caps.required bits", (caps.feature_mask & required) == required, 1);
     const ShaoboFa3BwdFeatureMask absent =
-        SHAOBO_FA3_BWD_FEATURE_VARLEN | SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW |
-        SHAOBO_FA3_BWD_FEATURE_SOFTCAP;
+        SHAOBO_FA3_BWD_FEATURE_VARLEN | SHAOBO_FA3_BWD_FEATURE_SOFTCAP;
     expect("caps.bshd", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_BSHD) != 0, 1);
+    expect("caps.local window", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW) != 0, 1);
     expect("caps.absent bits", (caps.feature_mask & absent) == 0, 1);
     expect("caps.min_head_dim", caps.min_head_dim, 64);
     expect("caps.max_head_dim", caps.max_head_dim, 128);
@@ -110,10 +110,11 @@ int main() {
     expect("redundant fixed-length fields", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
 
     // unsupported configurations
+    // (sliding windows are accepted here; the reference turns them away)
     p = good(); p.window_left = 128;
-    expect("local window", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
+    expect("local window", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
     p = good(); p.causal = 0; p.window_right = 0;
-    expect("right window without causal", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
+    expect("right window without causal", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
     p = good(); p.softcap = 1.0f;
     expect("softcap", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
     p = good(); p.dropout_p = 0.1f;

@@ -57,3 +57,36 @@ def test_layouts_agree_bitwise_on_the_deterministic_path():
     ra, rb = run_v2(a, deterministic=True), run_v2(b, deterministic=True)
     for name in ("dq", "dk", "dv", "delta"):
         assert np.array_equal(ra[name], rb[name]), name
+
+
+# (b, hq, hkv, sq, sk, d, dtype, causal, window)
+WINDOW_CASES = [
+    (1, 4, 4, 1024, 1024, 128, "fp16", True, (256, -1)),     # causal sliding window
+    (1, 4, 2, 1024, 1024, 64, "bf16", True, (100, -1)),      # window narrower than a tile
+    (2, 2, 2, 640, 640, 128, "bf16", False, (128, 128)),     # two-sided, tile-aligned
+    (1, 2, 2, 777, 1000, 64, "fp16", False, (50, 300)),      # two-sided, ragged, Sq != Sk
+    (1, 2, 1, 900, 400, 128, "fp16", True, (64, -1)),        # Sq > Sk: leading queries see nothing
+    (1, 2, 2, 512, 2048, 128, "bf16", False, (5, 5)),        # a thin band; key tiles without queries
+    (1, 48, 48, 512, 512, 64, "bf16", True, (200, -1)),      # >= 148 key tiles: unsplit path
+    (1, 40, 40, 256, 1024, 128, "fp16", False, (8, 64)),     # unsplit, key tiles that no query sees
+]
+
+
+@pytest.mark.parametrize("b,hq,hkv,sq,sk,d,dtype,causal,window", WINDOW_CASES)
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_sliding_window(b, hq, hkv, sq, sk, d, dtype, causal, window, deterministic):
+    prob = Problem(b, hq, hkv, sq, d, dtype, causal, seed=77 + sq + sk, sk=sk, window=window)
+    res = run_v2(prob, deterministic=deterministic)
+    assert_parity(res, prob, label=f"{(b, hq, hkv, sq, sk, d, dtype, causal, window, deterministic)}")
+    for name in ("dq", "dk", "dv", "delta"):
+        assert np.isfinite(res[name]).all(), name
+
+
+def test_a_window_that_covers_everything_is_the_plain_mask():
+    """A window at least as wide as the sequence gives bit-identical results to no window
+    (the normalisation of reference src/shaobo_fa3_bwd_api.cpp:53-68)."""
+    plain = Problem(1, 2, 2, 384, 128, "fp16", True, seed=3)
+    wide = Problem(1, 2, 2, 384, 128, "fp16", True, seed=3, window=(383, 500))
+    ra, rb = run_v2(plain, deterministic=True), run_v2(wide, deterministic=True)
+    for name in ("dq", "dk", "dv"):
+        assert np.array_equal(ra[name], rb[name]), name
