@@ -35,7 +35,10 @@ struct DqArgs {
     int batch;
     int heads_q;
     int heads_kv;
-    Band band;                // sequence lengths and the visible band (geometry.h)
+    Band band;                // sequence lengths and the visible band (geometry.h); maxima when packed
+    const int* cu_seqlens_q;  // non-null: packed sequences, see FusedArgs
+    const int* cu_seqlens_k;
+    int sidecar_rows;         // rows per head of the sidecar (seqlen_q, or total_q when packed)
     float scale;
     float scale_log2;
 };
@@ -87,7 +90,7 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kDqbNum);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
-    const int n_q_tiles = tiles_of(a.band.seqlen_q);
+    const int n_q_tiles = tiles_of(a.band.seqlen_q);  // of the longest sequence
     const int bh_count = a.batch * a.heads_q;
     // heaviest query tiles (most visible keys) are launched first
     const int qt = kCausal ? n_q_tiles - 1 - int(blockIdx.x) / bh_count : int(blockIdx.x) / bh_count;
@@ -95,9 +98,21 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int b = bhi / a.heads_q;
     const int hq = bhi % a.heads_q;
     const int kvh = hq / (a.heads_q / a.heads_kv);
-    // key tiles k_begin .. k_begin + n_steps - 1 in ascending order; none when no key is visible
-    const int k_begin = first_k_tile(qt, a.band);
-    const int n_steps = k_tiles_of_q_tile(qt, a.band);
+    // packed sequences: this batch entry's own lengths and first rows (see the five-GEMM kernel)
+    Band band = a.band;
+    int q_base = 0, k_base = 0, b_coord = b;
+    if (a.cu_seqlens_q != nullptr) {
+        q_base = a.cu_seqlens_q[b];
+        k_base = a.cu_seqlens_k[b];
+        band.seqlen_q = a.cu_seqlens_q[b + 1] - q_base;
+        band.seqlen_k = a.cu_seqlens_k[b + 1] - k_base;
+        band.off = band.seqlen_k - band.seqlen_q;
+        b_coord = 0;
+    }
+    // key tiles k_begin .. k_begin + n_steps - 1 in ascending order; none when no key is visible or
+    // the query tile lies past the end of this sequence
+    const int k_begin = first_k_tile(qt, band);
+    const int n_steps = qt * C::kTile < band.seqlen_q ? k_tiles_of_q_tile(qt, band) : 0;
     const bool misaligned = (sbase & 1023u) != 0;
 
     if (threadIdx.x == 0) {
@@ -135,21 +150,21 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::mbar_arrive_expect_tx(bar(kDqbQFull), 2 * C::kOperandBytes);
 #pragma unroll
                 for (int bx = 0; bx < C::kBoxes; ++bx) {
-                    ptx::tma_load_4d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kDqbQFull), bx * 64, q_row, hq, b);
-                    ptx::tma_load_4d(sbase + C::kOffDO + bx * C::kBoxBytes, &tm_do, bar(kDqbQFull), bx * 64, q_row, hq, b);
+                    ptx::tma_load_4d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kDqbQFull), bx * 64, q_base + q_row, hq, b_coord);
+                    ptx::tma_load_4d(sbase + C::kOffDO + bx * C::kBoxBytes, &tm_do, bar(kDqbQFull), bx * 64, q_base + q_row, hq, b_coord);
                 }
 #pragma unroll 1
                 for (int t = 0; t < n_steps; ++t) {
                     const int s = t & 1;
-                    const int kv_row = (k_begin + t) * C::kTile;
+                    const int kv_row = k_base + (k_begin + t) * C::kTile;
                     if (!bounded_wait(bar(kDqbKvEmpty + s), ((t >> 1) & 1) ^ 1, abort_flag)) break;
                     ptx::mbar_arrive_expect_tx(bar(kDqbKvFull + s), 2 * C::kOperandBytes);
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
                         ptx::tma_load_4d(sbase + C::kOffK + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_k,
-                                         bar(kDqbKvFull + s), bx * 64, kv_row, kvh, b);
+                                         bar(kDqbKvFull + s), bx * 64, kv_row, kvh, b_coord);
                         ptx::tma_load_4d(sbase + C::kOffV + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_v,
-                                         bar(kDqbKvFull + s), bx * 64, kv_row, kvh, b);
+                                         bar(kDqbKvFull + s), bx * 64, kv_row, kvh, b_coord);
                     }
                 }
             }
@@ -218,9 +233,9 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const int i = threadIdx.x - 128;  // query row inside the tile == TMEM lane
             const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
             const int qi = q_row + i;  // query row inside the head
-            const bool q_valid = qi < a.band.seqlen_q;
+            const bool q_valid = qi < band.seqlen_q;
             // rows past the end of the sequence: P = exp2(-inf) = 0
-            const float* side = a.sidecar + (int64_t(b * a.heads_q + hq) * a.band.seqlen_q + (q_valid ? qi : 0)) * 3;
+            const float* side = a.sidecar + (int64_t(b_coord * a.heads_q + hq) * a.sidecar_rows + q_base + (q_valid ? qi : 0)) * 3;
             const float neg = q_valid ? __log2f(side[1]) - side[0] : -INFINITY;
             const float delta = q_valid ? side[2] : 0.0f;
             uint32_t ppk[64];
@@ -230,9 +245,9 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 if (!(ok = warp_wait(bar(kDqbSFull), t & 1, abort_flag))) break;
                 ptx::tc_fence_after();
                 // element (query i, key j) survives iff mask_from <= j <= mask_to (band edges, end of keys)
-                const bool diagonal = kCausal && tile_needs_mask(k_begin + t, qt, a.band);
+                const bool diagonal = kCausal && tile_needs_mask(k_begin + t, qt, band);
                 int mask_from, mask_to;
-                key_range_of_query(qi, (k_begin + t) * C::kTile, a.band, &mask_from, &mask_to);
+                key_range_of_query(qi, (k_begin + t) * C::kTile, band, &mask_from, &mask_to);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t r[32];
@@ -275,8 +290,8 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::mbar_arrive(bar(kDqbDsReady));
             }
             if (ok && n_steps > 0) ok = warp_wait(bar(kDqbDone), 0, abort_flag);
-            TOut* dst = reinterpret_cast<TOut*>(a.dq) + b * a.q_strides.batch + hq * a.q_strides.head +
-                        int64_t(qi) * a.q_strides.row;
+            TOut* dst = reinterpret_cast<TOut*>(a.dq) + b_coord * a.q_strides.batch + hq * a.q_strides.head +
+                        int64_t(q_base + qi) * a.q_strides.row;
             if (ok && q_valid && n_steps == 0) {
                 // no visible key at all: the gradient of these rows is zero
                 uint4* d4 = reinterpret_cast<uint4*>(dst);

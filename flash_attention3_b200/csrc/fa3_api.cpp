@@ -45,6 +45,17 @@ bool lengths_in_range(const ShaoboFa3Params* p) {
     return p->seqlen_q < kUnbounded && p->seqlen_k < kUnbounded;
 }
 
+// Packed sequences need both offset arrays, the two maxima and the two totals; seqused_* (lengths
+// shorter than the slots) is not supported.
+bool varlen_fields_ok(const ShaoboFa3Params* p) {
+    if (p->seqused_q || p->seqused_k) return false;
+    if (p->cu_seqlens_q == nullptr || p->cu_seqlens_k == nullptr) return false;
+    if (p->max_seqlen_q <= 0 || p->max_seqlen_k <= 0 || p->total_q <= 0 || p->total_k <= 0) return false;
+    if (p->max_seqlen_q >= kUnbounded || p->max_seqlen_k >= kUnbounded) return false;
+    if (p->total_q >= (int64_t(1) << 31) || p->total_k >= (int64_t(1) << 31)) return false;
+    return p->max_seqlen_q <= p->total_q && p->max_seqlen_k <= p->total_k;
+}
+
 bool lengths_are_fixed(const ShaoboFa3Params* p) {
     if (p->cu_seqlens_q || p->cu_seqlens_k || p->seqused_q || p->seqused_k) return false;
     if (p->max_seqlen_q != 0 && p->max_seqlen_q != p->seqlen_q) return false;
@@ -56,9 +67,11 @@ bool lengths_are_fixed(const ShaoboFa3Params* p) {
     return true;
 }
 
+// Query rows over all heads: B*Hq*Sq, or Hq*total_q for packed sequences.
 size_t row_count(const ShaoboFa3Params* p, bool* ok) {
-    size_t rows = size_t(p->batch);
-    *ok = mul_ok(rows, size_t(p->num_heads_q), &rows) && mul_ok(rows, size_t(p->seqlen_q), &rows);
+    size_t rows = is_varlen(p) ? size_t(p->total_q) : size_t(p->batch);
+    *ok = mul_ok(rows, size_t(p->num_heads_q), &rows) &&
+          (is_varlen(p) || mul_ok(rows, size_t(p->seqlen_q), &rows));
     return rows;
 }
 
@@ -84,7 +97,8 @@ int validate_v2(const ShaoboFa3Params* p) {
     // (wider than the reference, which also turns away the [B,S,H,D] layout, seqlen_q != seqlen_k,
     // sequence lengths that are not multiples of 128 and sliding windows:
     // src/shaobo_fa3_bwd_api.cpp:109-118)
-    if (!lengths_are_fixed(p) || !dtype_supported(p->dtype) || !layout_supported(p->layout) ||
+    const bool lengths_ok = is_varlen(p) ? varlen_fields_ok(p) : lengths_are_fixed(p);
+    if (!lengths_ok || !dtype_supported(p->dtype) || !layout_supported(p->layout) ||
         !head_dim_supported(p->head_dim_qk) || p->head_dim_v != p->head_dim_qk ||
         p->dropout_p != 0.0f || p->softcap != 0.0f || p->sm_margin != 0 || !lengths_in_range(p)) {
         return SHAOBO_FA3_STATUS_UNSUPPORTED;
@@ -112,7 +126,8 @@ size_t dq_accum_bytes(const ShaoboFa3Params* p) {
 
 SplitPlan split_plan(const ShaoboFa3Params* p) {
     SplitPlan plan;
-    if (!fused_shape_ok(p) || p->deterministic != 0) return plan;
+    // (per-sequence lengths of packed sequences are not known on the host: no splitting there)
+    if (!fused_shape_ok(p) || p->deterministic != 0 || is_varlen(p)) return plan;
     const int tiles = tiles_of(p->seqlen_k);
     const Band band = band_of(p);
     const long long heads = (long long)p->batch * p->num_heads_kv;
@@ -216,6 +231,7 @@ extern "C" int shaobo_fa3_bwd_get_capabilities(ShaoboFa3BwdCapabilities* caps) {
                          SHAOBO_FA3_BWD_FEATURE_GQA | SHAOBO_FA3_BWD_FEATURE_DETERMINISTIC |
                          SHAOBO_FA3_BWD_FEATURE_SOFTMAX_LSE | SHAOBO_FA3_BWD_FEATURE_BHSD |
                          SHAOBO_FA3_BWD_FEATURE_BSHD | SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW |
+                         SHAOBO_FA3_BWD_FEATURE_VARLEN |
                          SHAOBO_FA3_BWD_FEATURE_FULL_ATTENTION;
     caps->min_head_dim = kMinHeadDim;
     caps->max_head_dim = kMaxHeadDim;

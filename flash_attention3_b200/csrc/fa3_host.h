@@ -30,10 +30,21 @@ inline bool dtype_supported(int t) {
     return t == SHAOBO_FA3_DTYPE_FP16 || t == SHAOBO_FA3_DTYPE_BF16;
 }
 
+// Packed ("varlen") sequences: q, out, dout, dq are [total_q, Hq, D] and k, v, dk, dv are
+// [total_k, Hkv, D]; sequence b owns rows cu_seqlens[b] .. cu_seqlens[b+1]-1 (device arrays of
+// batch+1 int32).  softmax_lse, delta and the sidecar are [Hq, total_q].  max_seqlen_q / max_seqlen_k
+// bound the per-sequence lengths and size the launch.
+inline bool is_varlen(const ShaoboFa3Params* p) {
+    return p->cu_seqlens_q != nullptr || p->cu_seqlens_k != nullptr;
+}
+// Length the launch is planned for: the sequence length, or the longest sequence when packed.
+inline int plan_seqlen_q(const ShaoboFa3Params* p) { return is_varlen(p) ? p->max_seqlen_q : p->seqlen_q; }
+inline int plan_seqlen_k(const ShaoboFa3Params* p) { return is_varlen(p) ? p->max_seqlen_k : p->seqlen_k; }
+
 // The visible band of a parameter block (window_left / window_right: negative = unbounded; causal
 // forces right = 0, as reference src/shaobo_fa3_bwd_api.cpp:53-68 normalises it).
 inline Band band_of(const ShaoboFa3Params* p) {
-    return make_band(p->seqlen_q, p->seqlen_k, p->causal != 0, p->window_left, p->window_right);
+    return make_band(plan_seqlen_q(p), plan_seqlen_k(p), p->causal != 0, p->window_left, p->window_right);
 }
 
 // Public validation used by every v2 entry.

@@ -76,17 +76,29 @@ bool make_map_accum(CUtensorMap* map, const float* base, int64_t batch_heads, in
 // The kernels come in two forms: a lean one for full attention over whole 128-row tiles and a general
 // one (causal mask, sliding window, ragged sequence ends).
 bool needs_general_form(const ShaoboFa3Params* p) {
-    return !band_is_full(band_of(p)) || p->seqlen_q % kTileRows != 0 || p->seqlen_k % kTileRows != 0;
+    return is_varlen(p) || !band_is_full(band_of(p)) || p->seqlen_q % kTileRows != 0 ||
+           p->seqlen_k % kTileRows != 0;
 }
 
-bool is_bshd(const ShaoboFa3Params* p) { return p->layout == SHAOBO_FA3_LAYOUT_BSHD; }
+// How the tensors of a call are addressed.  Packed sequences are one batch entry of `total` rows in
+// the token-major layout ([total, H, D] is [B,S,H,D] with B = 1, S = total).
+struct TensorShape {
+    int batch;     // batch entries of the tensors (1 when packed)
+    int rows_q;    // rows per (batch entry, head) of the query-side tensors
+    int rows_k;
+    bool bshd;
+};
+TensorShape shape_of(const ShaoboFa3Params* p) {
+    if (is_varlen(p)) return TensorShape{1, int(p->total_q), int(p->total_k), true};
+    return TensorShape{p->batch, p->seqlen_q, p->seqlen_k, p->layout == SHAOBO_FA3_LAYOUT_BSHD};
+}
 
-RowLayout row_layout(const ShaoboFa3Params* p, int heads, int seqlen) {
+RowLayout row_layout(const ShaoboFa3Params* p, int heads, int rows, bool bshd) {
     RowLayout l;
-    l.strides = strides_of(is_bshd(p), heads, seqlen, p->head_dim_qk);
+    l.strides = strides_of(bshd, heads, rows, p->head_dim_qk);
     l.heads = heads;
-    l.seqlen = seqlen;
-    l.contiguous = is_bshd(p) ? 0 : 1;
+    l.seqlen = rows;
+    l.contiguous = bshd ? 0 : 1;
     return l;
 }
 
@@ -193,11 +205,12 @@ void launch_delta_t(const void* dout, const void* out, const float* aux0, const 
 void launch_delta(const ShaoboFa3Params* p, const void* dout, const void* out, const float* aux0,
                   const float* aux1, float* delta, float* sidecar, float* zero_rows, bool lse,
                   float* zero_extra = nullptr, int64_t zero_extra_bytes = 0) {
-    const int64_t rows = int64_t(p->batch) * p->num_heads_q * p->seqlen_q;
+    const TensorShape shape = shape_of(p);
+    const int64_t rows = int64_t(shape.batch) * p->num_heads_q * shape.rows_q;
     const float scale_log2 = p->softmax_scale * kLog2E;
     cudaStream_t st = stream_of(p);
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
-    const RowLayout layout = row_layout(p, p->num_heads_q, p->seqlen_q);
+    const RowLayout layout = row_layout(p, p->num_heads_q, shape.rows_q, shape.bshd);
     if (p->head_dim_qk == 128) {
         if (bf) launch_delta_t<__nv_bfloat16, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
         else launch_delta_t<__half, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
@@ -215,21 +228,22 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
     ConvertSegments seg{};
     seg.src[0] = accum;
     seg.dst[0] = dq;
-    seg.n_vec8[0] = int64_t(p->batch) * p->num_heads_q * p->seqlen_q * p->head_dim_qk / 8;
+    const TensorShape shape = shape_of(p);
+    seg.n_vec8[0] = int64_t(shape.batch) * p->num_heads_q * shape.rows_q * p->head_dim_qk / 8;
     seg.scale[0] = p->softmax_scale;
-    seg.layout[0] = row_layout(p, p->num_heads_q, p->seqlen_q);
+    seg.layout[0] = row_layout(p, p->num_heads_q, shape.rows_q, shape.bshd);
     seg.head_dim = p->head_dim_qk;
     seg.count = 1;
     int64_t total = seg.n_vec8[0];
     if (dkv_accum != nullptr) {
-        const int64_t n = int64_t(p->batch) * p->num_heads_kv * p->seqlen_k * p->head_dim_qk;
+        const int64_t n = int64_t(shape.batch) * p->num_heads_kv * shape.rows_k * p->head_dim_qk;
         seg.src[1] = dkv_accum;
         seg.dst[1] = dk;
         seg.src[2] = dkv_accum + n;
         seg.dst[2] = dv;
         seg.n_vec8[1] = seg.n_vec8[2] = n / 8;
         seg.scale[1] = seg.scale[2] = 1.0f;
-        seg.layout[1] = seg.layout[2] = row_layout(p, p->num_heads_kv, p->seqlen_k);
+        seg.layout[1] = seg.layout[2] = row_layout(p, p->num_heads_kv, shape.rows_k, shape.bshd);
         seg.count = 3;
         total += 2 * (n / 8);
     }
@@ -313,17 +327,18 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const int d = p->head_dim_qk;
-    const bool bshd = is_bshd(p);
-    const int64_t kv_heads_total = int64_t(p->batch) * p->num_heads_kv;
+    const TensorShape shape = shape_of(p);
+    const bool bshd = shape.bshd;
+    const int64_t kv_heads_total = int64_t(shape.batch) * p->num_heads_kv;
     CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
-    if (!make_map_16(&mq, type, q, p->batch, p->num_heads_q, p->seqlen_q, d, bshd) ||
-        !make_map_16(&mk, type, k, p->batch, p->num_heads_kv, p->seqlen_k, d, bshd) ||
-        !make_map_16(&mv, type, v, p->batch, p->num_heads_kv, p->seqlen_k, d, bshd) ||
-        !make_map_16(&mdo, type, dout, p->batch, p->num_heads_q, p->seqlen_q, d, bshd)) {
+    if (!make_map_16(&mq, type, q, shape.batch, p->num_heads_q, shape.rows_q, d, bshd) ||
+        !make_map_16(&mk, type, k, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd) ||
+        !make_map_16(&mv, type, v, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd) ||
+        !make_map_16(&mdo, type, dout, shape.batch, p->num_heads_q, shape.rows_q, d, bshd)) {
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
     if (with_dq) {
-        if (!make_map_accum(&mdq, dq_accum, int64_t(p->batch) * p->num_heads_q, p->seqlen_q, d)) {
+        if (!make_map_accum(&mdq, dq_accum, int64_t(shape.batch) * p->num_heads_q, shape.rows_q, d)) {
             return SHAOBO_FA3_STATUS_HIP_ERROR;
         }
     } else {
@@ -331,34 +346,37 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     }
     const SplitPlan split = (with_dq && dkv_accum != nullptr) ? split_plan(p) : SplitPlan{};
     if (split.chunk_steps > 0) {
-        const int64_t kv_elems = kv_heads_total * p->seqlen_k * d;
-        if (!make_map_accum(&mdk, dkv_accum, kv_heads_total, p->seqlen_k, d) ||
-            !make_map_accum(&mdv, dkv_accum + kv_elems, kv_heads_total, p->seqlen_k, d)) {
+        const int64_t kv_elems = kv_heads_total * shape.rows_k * d;
+        if (!make_map_accum(&mdk, dkv_accum, kv_heads_total, shape.rows_k, d) ||
+            !make_map_accum(&mdv, dkv_accum + kv_elems, kv_heads_total, shape.rows_k, d)) {
             return SHAOBO_FA3_STATUS_HIP_ERROR;
         }
     } else {
         mdk = mq;  // unused by the kernel
         mdv = mq;
     }
-    const int n_tiles = tiles_of(p->seqlen_k);
+    const int n_tiles = tiles_of(plan_seqlen_k(p));
     const Band band = band_of(p);
     const TileWork work = TileWork::of(band);
     const int bh = p->batch * p->num_heads_kv;
     const int group = p->num_heads_q / p->num_heads_kv;
     // bytes of dQ accumulator behind one (batch, KV head): only the fused path adds into it
     const long long dq_bytes_per_head =
-        with_dq ? (long long)group * p->seqlen_q * p->head_dim_qk * 4 : 0;
+        with_dq ? (long long)group * plan_seqlen_q(p) * p->head_dim_qk * 4 : 0;
     const CtaOrderPlan plan = cached_plan(work, bh, group, sm_count(), dq_bytes_per_head);
     FusedArgs args;
     args.sidecar = sidecar;
     args.dk = dk;
     args.dv = dv;
     // fp32 dK/dV of the split path are always [B,Hkv,Sk,D]; 16-bit outputs follow the layout of K/V
-    args.kv_strides = strides_of(bshd && !dkv_f32, p->num_heads_kv, p->seqlen_k, d);
+    args.kv_strides = strides_of(bshd && !dkv_f32, p->num_heads_kv, shape.rows_k, d);
     args.batch = p->batch;
     args.heads_q = p->num_heads_q;
     args.heads_kv = p->num_heads_kv;
     args.band = band;
+    args.cu_seqlens_q = p->cu_seqlens_q;
+    args.cu_seqlens_k = p->cu_seqlens_k;
+    args.sidecar_rows = shape.rows_q;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
     args.order_mode = plan.mode;
@@ -417,26 +435,30 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const int d = p->head_dim_qk;
-    const bool bshd = is_bshd(p);
+    const TensorShape shape = shape_of(p);
+    const bool bshd = shape.bshd;
     CUtensorMap mq, mk, mv, mdo;
-    if (!make_map_16(&mq, type, q, p->batch, p->num_heads_q, p->seqlen_q, d, bshd) ||
-        !make_map_16(&mk, type, k, p->batch, p->num_heads_kv, p->seqlen_k, d, bshd) ||
-        !make_map_16(&mv, type, v, p->batch, p->num_heads_kv, p->seqlen_k, d, bshd) ||
-        !make_map_16(&mdo, type, dout, p->batch, p->num_heads_q, p->seqlen_q, d, bshd)) {
+    if (!make_map_16(&mq, type, q, shape.batch, p->num_heads_q, shape.rows_q, d, bshd) ||
+        !make_map_16(&mk, type, k, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd) ||
+        !make_map_16(&mv, type, v, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd) ||
+        !make_map_16(&mdo, type, dout, shape.batch, p->num_heads_q, shape.rows_q, d, bshd)) {
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
     DqArgs args;
     args.sidecar = sidecar;
     args.dq = dq;
     // fp32 dQ of the split path is always [B,Hq,Sq,D]; 16-bit dQ follows the layout of Q
-    args.q_strides = strides_of(bshd && !out_f32, p->num_heads_q, p->seqlen_q, d);
+    args.q_strides = strides_of(bshd && !out_f32, p->num_heads_q, shape.rows_q, d);
     args.batch = p->batch;
     args.heads_q = p->num_heads_q;
     args.heads_kv = p->num_heads_kv;
     args.band = band_of(p);
+    args.cu_seqlens_q = p->cu_seqlens_q;
+    args.cu_seqlens_k = p->cu_seqlens_k;
+    args.sidecar_rows = shape.rows_q;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
-    const int64_t blocks64 = int64_t(tiles_of(p->seqlen_q)) * p->batch * p->num_heads_q;
+    const int64_t blocks64 = int64_t(tiles_of(plan_seqlen_q(p))) * p->batch * p->num_heads_q;
     if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
     const int blocks = int(blocks64);
     if (out_f32) {
@@ -448,7 +470,8 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
 }
 
 bool stage_params_ok(const ShaoboFa3Params* p) {
-    return p != nullptr && dtype_supported(p->dtype) && layout_supported(p->layout) &&
+    // (the component entry points take fixed-length batches only)
+    return p != nullptr && !is_varlen(p) && dtype_supported(p->dtype) && layout_supported(p->layout) &&
            (p->causal == 0 || p->causal == 1) && fused_shape_ok(p);
 }
 

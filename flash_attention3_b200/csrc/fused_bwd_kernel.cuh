@@ -89,7 +89,11 @@ struct FusedArgs {
     int batch;
     int heads_q;
     int heads_kv;
-    Band band;             // sequence lengths and the visible band (geometry.h)
+    Band band;             // sequence lengths and the visible band (geometry.h); with packed
+                           // sequences the lengths are the maxima and each CTA reads its own
+    const int* cu_seqlens_q;  // non-null: sequences are packed ([total, H, D] tensors) and sequence b
+    const int* cu_seqlens_k;  // owns rows cu[b] .. cu[b+1]-1; the tensor maps then have batch = 1
+    int sidecar_rows;      // rows per head of the sidecar / accumulators (seqlen_q, or total_q when packed)
     float scale;
     float scale_log2;
     int order_mode;        // see cta_order.h
@@ -233,8 +237,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     // ---- which tile is ours ------------------------------------------------
-    const int n_tiles = tiles_of(a.band.seqlen_k);      // key tiles
-    const int n_q_tiles = tiles_of(a.band.seqlen_q);
+    const int n_tiles = tiles_of(a.band.seqlen_k);      // key tiles (of the longest sequence)
     const int bh_count = a.batch * a.heads_kv;
     const bool split = a.chunk_steps > 0;
     const int group = a.heads_q / a.heads_kv;
@@ -254,7 +257,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         int rest = int(blockIdx.x) % a.chunks_per_head;
         kt = 0;
         while (true) {
-            const int steps = group * q_tiles_of_k_tile(kt, a.band);
+            const int steps = group * q_tiles_of_k_tile(kt, a.band);  // (never with packed sequences)
             const int chunks = (steps + a.chunk_steps - 1) / a.chunk_steps;
             if (rest < chunks) break;
             rest -= chunks;
@@ -264,8 +267,23 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     const int b = bhi / a.heads_kv;
     const int kvh = bhi % a.heads_kv;
-    const int q_begin = first_q_tile(kt, a.band);
-    const int steps_per_head = q_tiles_of_k_tile(kt, a.band);
+    // Packed sequences: this batch entry's own lengths and first rows; tensors are addressed as one
+    // batch of `total` rows, so rows past the end of a sequence belong to its neighbour (or read as
+    // zero past the end of the tensor) and are masked like any ragged tile end.
+    Band band = a.band;
+    int q_base = 0, k_base = 0, b_coord = b;
+    if (a.cu_seqlens_q != nullptr) {
+        q_base = a.cu_seqlens_q[b];
+        k_base = a.cu_seqlens_k[b];
+        band.seqlen_q = a.cu_seqlens_q[b + 1] - q_base;
+        band.seqlen_k = a.cu_seqlens_k[b + 1] - k_base;
+        band.off = band.seqlen_k - band.seqlen_q;
+        b_coord = 0;
+    }
+    const int n_q_tiles = tiles_of(band.seqlen_q);
+    const bool tile_exists = kt * C::kTile < band.seqlen_k;  // false only with packed sequences
+    const int q_begin = first_q_tile(kt, band);
+    const int steps_per_head = tile_exists ? q_tiles_of_k_tile(kt, band) : 0;
     // this CTA's share of the tile's steps (all of them unless the tile is split)
     const int total_steps = group * steps_per_head;
     const int t_begin = t_begin_split;
@@ -340,22 +358,22 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                 for (int bx = 0; bx < C::kBoxes; ++bx) {
                     ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
-                                     kt * C::kTile, kvh, b);
+                                     k_base + kt * C::kTile, kvh, b_coord);
                     ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
-                                     kt * C::kTile, kvh, b);
+                                     k_base + kt * C::kTile, kvh, b_coord);
                 }
 #pragma unroll 1
                 for (int t = 0; t < n_steps; ++t) {
                     int hq, qt;
                     step_coords(t, hq, qt);
-                    const int q_row = qt * C::kTile;
+                    const int q_row = q_base + qt * C::kTile;
                     const int s = t % C::kQStages;
                     if (!bounded_wait<true>(bar(kQEmpty + s), ((t / C::kQStages) & 1) ^ 1, abort_flag)) break;
                     ptx::mbar_arrive_expect_tx(bar(kQFull + s), C::kOperandBytes);
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
                         ptx::tma_load_4d(sbase + C::kOffQ + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_q,
-                                         bar(kQFull + s), bx * 64, q_row, hq, b);
+                                         bar(kQFull + s), bx * 64, q_row, hq, b_coord);
                     }
                     const int sd = t % C::kDoStages;
                     if (!bounded_wait<true>(bar(kDoEmpty + sd), ((t / C::kDoStages) & 1) ^ 1, abort_flag)) break;
@@ -363,7 +381,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
                         ptx::tma_load_4d(sbase + C::kOffDO + sd * C::kOperandBytes + bx * C::kBoxBytes, &tm_do,
-                                         bar(kDoFull + sd), bx * 64, q_row, hq, b);
+                                         bar(kDoFull + sd), bx * 64, q_row, hq, b_coord);
                     }
                 }
             }
@@ -507,8 +525,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // past the end of the sequence read row 0 instead and are replaced at that first use.
             auto load_stats = [&](int hq, int qt) {
                 const int qi = qt * C::kTile + j;
-                s_valid = qi < a.band.seqlen_q;
-                const int64_t row = int64_t(b * a.heads_q + hq) * a.band.seqlen_q + (s_valid ? qi : 0);
+                s_valid = qi < band.seqlen_q;
+                const int64_t row = int64_t(b_coord * a.heads_q + hq) * a.sidecar_rows + q_base + (s_valid ? qi : 0);
                 s0 = side_base[row * 3 + 0];
                 s1 = side_base[row * 3 + 1];
                 s2 = side_base[row * 3 + 2];
@@ -552,7 +570,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 ptx::tc_fence_after();
                 // A tile that crosses an edge of the band or holds keys past the end of the sequence is
                 // masked: element (key j, query i) survives iff mask_from <= i <= mask_to.
-                const bool diagonal = kCausal && tile_needs_mask(kt, qt, a.band);
+                const bool diagonal = kCausal && tile_needs_mask(kt, qt, band);
                 int mask_from = 0, mask_to = 0;  // set only on masked tiles
                 // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked as above.
                 // (two copies of the chunk code, so that unmasked tiles carry no per-element test)
@@ -588,7 +606,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     ptx::tmem_st16(s_cols + c * 16, &ppk[c * 16]);
                 };
                 if (diagonal) {
-                    query_range_of_key(kt * C::kTile + j, qt * C::kTile, a.band, &mask_from, &mask_to);
+                    query_range_of_key(kt * C::kTile + j, qt * C::kTile, band, &mask_from, &mask_to);
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
@@ -669,10 +687,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (ok && !split) {
                 // (tensor-memory loads are warp-wide: every lane runs them, only the stores of key rows
                 // past the end of the sequence are skipped)
-                const bool key_valid = kt * C::kTile + j < a.band.seqlen_k;
+                const bool key_valid = kt * C::kTile + j < band.seqlen_k;
                 ptx::tc_fence_after();
-                const int64_t off = b * a.kv_strides.batch + kvh * a.kv_strides.head +
-                                    int64_t(kt * C::kTile + j) * a.kv_strides.row;
+                const int64_t off = b_coord * a.kv_strides.batch + kvh * a.kv_strides.head +
+                                    int64_t(k_base + kt * C::kTile + j) * a.kv_strides.row;
                 TOut* dst = reinterpret_cast<TOut*>(half == 0 ? a.dk : a.dv) + off;
                 const float mul = half == 0 ? a.scale : 1.0f;
                 const uint32_t col0 = tl + (half == 0 ? C::kColDK : C::kColDV);
@@ -707,9 +725,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         } else if (owes_zeros) {
             // nobody attends to these keys: the first warpgroup clears dK, the second dV
             const int j = threadIdx.x & 127;
-            if (kt * C::kTile + j < a.band.seqlen_k) {
-                const int64_t off = b * a.kv_strides.batch + kvh * a.kv_strides.head +
-                                    int64_t(kt * C::kTile + j) * a.kv_strides.row;
+            if (kt * C::kTile + j < band.seqlen_k) {
+                const int64_t off = b_coord * a.kv_strides.batch + kvh * a.kv_strides.head +
+                                    int64_t(k_base + kt * C::kTile + j) * a.kv_strides.row;
                 uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<TOut*>(wg == 1 ? a.dk : a.dv) + off);
 #pragma unroll
                 for (int e = 0; e < int(D * sizeof(TOut) / 16); ++e) d4[e] = make_uint4(0u, 0u, 0u, 0u);
@@ -735,7 +753,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     int hq, qt;
                     step_coords(t, hq, qt);
                     const int q_row = qt * C::kTile + qd * 32;  // row inside the head
-                    const int q_head = b * a.heads_q + hq;
+                    const int q_head = b_coord * a.heads_q + hq;
                     DBG_STAMP(0);
                     if (!warp_wait(bar(kDqFull), t & 1, abort_flag)) break;
                     DBG_STAMP(1);
@@ -776,9 +794,9 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         __syncwarp();
 #ifndef FA3B200_EXPERIMENT_NOREDUCE
                         // accumulator map: [batch*head][row][D]; rows past the sequence end are dropped
-                        if (lane == 0 && q_row < a.band.seqlen_q) {
-                            ptx::tma_reduce_add_3d(&tm_dqacc, stage, hf * 64, q_row, q_head);
-                            ptx::tma_reduce_add_3d(&tm_dqacc, stage + C::kStageBoxBytes, hf * 64 + 32, q_row, q_head);
+                        if (lane == 0 && q_row < band.seqlen_q) {
+                            ptx::tma_reduce_add_3d(&tm_dqacc, stage, hf * 64, q_base + q_row, q_head);
+                            ptx::tma_reduce_add_3d(&tm_dqacc, stage + C::kStageBoxBytes, hf * 64 + 32, q_base + q_row, q_head);
                             ptx::bulk_commit_group();
                         }
 #endif
@@ -819,15 +837,15 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         }
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0 && row0 < a.band.seqlen_k) {
+                        if (lane == 0 && row0 < band.seqlen_k) {
 #pragma unroll
                             for (int bx = 0; bx < 2 * kBoxesPerTensor; ++bx) {
                                 const int which = bx / kBoxesPerTensor;
                                 const int c = bx % kBoxesPerTensor;
                                 ptx::tma_reduce_add_3d(which == 0 ? static_cast<const void*>(&tm_dkacc)
                                                                   : static_cast<const void*>(&tm_dvacc),
-                                                       scratch + bx * C::kStageBoxBytes, c * 32, row0,
-                                                       b * a.heads_kv + kvh);
+                                                       scratch + bx * C::kStageBoxBytes, c * 32, k_base + row0,
+                                                       b_coord * a.heads_kv + kvh);
                             }
                             ptx::bulk_commit_group();
                         }

@@ -82,5 +82,44 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
     return (dq, dk, dv, delta) if return_delta else (dq, dk, dv)
 
 
+def fa3_bwd_varlen(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int,
+                   max_seqlen_k: int, causal: bool, softmax_scale=None, deterministic=False, window=(-1, -1),
+                   return_delta=False, sync=False):
+    """Backward over packed sequences.  q, out, dout: [total_q, Hq, D]; k, v: [total_k, Hkv, D];
+    softmax_lse: fp32 [Hq, total_q]; cu_seqlens_*: int32 device tensors of batch+1 row offsets.
+    Returns dq, dk, dv in the shapes of q, k, v (and delta [Hq, total_q]).  Calls shaobo_fa3_bwd_v2."""
+    _require_cuda(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k)
+    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32:
+        raise TypeError("cu_seqlens must be int32")
+    lib = capi.load()
+    total_q, hq, d = q.shape
+    total_k, hkv, _ = k.shape
+    batch = cu_seqlens_q.numel() - 1
+    p = capi.new_params(batch=batch, seqlen_q=int(max_seqlen_q), seqlen_k=int(max_seqlen_k), num_heads_q=hq,
+                        num_heads_kv=hkv, head_dim_qk=d, head_dim_v=d, causal=int(causal), dtype=_DTYPES[q.dtype],
+                        layout=capi.LAYOUT_BSHD, deterministic=int(deterministic), sync_after_launch=int(sync),
+                        window_left=int(window[0]), window_right=int(window[1]),
+                        cu_seqlens_q=cu_seqlens_q.data_ptr(), cu_seqlens_k=cu_seqlens_k.data_ptr(),
+                        max_seqlen_q=int(max_seqlen_q), max_seqlen_k=int(max_seqlen_k),
+                        total_q=int(total_q), total_k=int(total_k))
+    if softmax_scale is not None:
+        p.softmax_scale = float(softmax_scale)
+        p.softmax_scale_is_set = 1
+    need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
+    if need == 0:
+        raise Fa3Error("shaobo_fa3_bwd_v2_validate", lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(p)))
+    workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    p.workspace, p.workspace_bytes = workspace.data_ptr(), need
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty((hq, total_q), dtype=torch.float32, device=q.device) if return_delta else None
+    with torch.cuda.device(q.device):
+        p.reserved_ptr[capi.RESERVED_PTR_STREAM] = torch.cuda.current_stream().cuda_stream or None
+        code = lib.shaobo_fa3_bwd_v2(_ptr(dout), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(softmax_lse),
+                                     _ptr(dq), _ptr(dk), _ptr(dv), _ptr(delta), ctypes.byref(p))
+    if code != capi.STATUS_SUCCESS:
+        raise Fa3Error("shaobo_fa3_bwd_v2", code)
+    return (dq, dk, dv, delta) if return_delta else (dq, dk, dv)
+
+
 def default_scale(d: int) -> float:
     return 1.0 / math.sqrt(d)

@@ -122,7 +122,7 @@ typedef struct ShaoboFa3Params {
     int32_t block_threads;         /*  72  ignored */
     int32_t sync_after_launch;     /*  76  0 or 1 */
 
-    const int32_t* cu_seqlens_q;   /*  80  varlen: unsupported, must be NULL */
+    const int32_t* cu_seqlens_q;   /*  80  packed sequences: device array of batch+1 offsets, or NULL */
     const int32_t* cu_seqlens_k;   /*  88 */
     int32_t max_seqlen_q;          /*  96 */
     int32_t max_seqlen_k;          /* 100 */
@@ -189,7 +189,14 @@ size_t shaobo_fa3_bwd_v2_workspace_bytes(const ShaoboFa3Params* params);
  *    A query that sees no key (softmax_lse = -inf) gets a zero gradient.
  *  - window_left / window_right >= 0: sliding window, query i sees keys
  *    i + off - window_left .. i + off + window_right (off = seqlen_k - seqlen_q);
- *    a negative side is unbounded and causal = 1 forces window_right = 0. */
+ *    a negative side is unbounded and causal = 1 forces window_right = 0.
+ *  - cu_seqlens_q and cu_seqlens_k non-NULL (device arrays of batch+1 int32 row
+ *    offsets): packed sequences.  q, out, dout, dq are [total_q, Hq, D], k, v,
+ *    dk, dv are [total_k, Hkv, D], softmax_lse and softmax_d are [Hq, total_q];
+ *    batch is the number of sequences; max_seqlen_q/k, total_q/k must be set
+ *    and seqlen_q/k hold the maxima; layout is ignored; seqused_q/k must be
+ *    NULL.  Rows of dq/dk/dv outside every sequence are not part of the
+ *    contract. */
 int shaobo_fa3_bwd_v2(const void* dout,
                       const void* q,
                       const void* k,

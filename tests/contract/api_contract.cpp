@@ -81,7 +81,8 @@ int main() {
     expect("caps.api_version", caps.api_version, SHAOBO_FA3_API_VERSION);
     expect("caps.required bits", (caps.feature_mask & required) == required, 1);
     const ShaoboFa3BwdFeatureMask absent =
-        SHAOBO_FA3_BWD_FEATURE_VARLEN | SHAOBO_FA3_BWD_FEATURE_SOFTCAP;
+        SHAOBO_FA3_BWD_FEATURE_SOFTCAP;
+    expect("caps.varlen", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_VARLEN) != 0, 1);
     expect("caps.bshd", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_BSHD) != 0, 1);
     expect("caps.local window", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW) != 0, 1);
     expect("caps.absent bits", (caps.feature_mask & absent) == 0, 1);

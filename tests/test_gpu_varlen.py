@@ -1,0 +1,102 @@
+"""GPU parity on packed ("varlen") sequences: q/out/dout [total_q, Hq, D], k/v [total_k, Hkv, D],
+softmax_lse [Hq, total_q], row offsets in cu_seqlens_*.  Every sequence is checked against the oracle
+run on that sequence alone; rows of neighbouring sequences must not leak into each other."""
+import numpy as np
+import pytest
+import torch
+
+from flash_attention3_b200 import ops
+from oracle import golden
+from tests.helpers import TORCH_DTYPE, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def packed_problem(seqs, hq, hkv, d, dtype, causal, window, seed):
+    """seqs: list of (seqlen_q, seqlen_k).  Returns packed host arrays and per-sequence oracle results."""
+    parts, refs = [], []
+    for i, (sq, sk) in enumerate(seqs):
+        q, k, v, do = golden.seeded_inputs(seed + i, 1, hq, hkv, sq, d, dtype, sk=sk)
+        ref = golden.backward(q, k, v, do, causal, 1.0 / np.sqrt(d), dtype, window)
+        parts.append((q[0], k[0], v[0], do[0]))
+        refs.append(ref)
+    pack = lambda xs: np.ascontiguousarray(np.concatenate([x.transpose(1, 0, 2) for x in xs], axis=0))  # [total,H,D]
+    packed = dict(
+        q=pack([p[0] for p in parts]), k=pack([p[1] for p in parts]), v=pack([p[2] for p in parts]),
+        dout=pack([p[3] for p in parts]), out=pack([r["out"][0] for r in refs]),
+        lse=np.ascontiguousarray(np.concatenate([r["lse"][0] for r in refs], axis=1)),  # [Hq,total_q]
+    )
+    cu_q = np.concatenate([[0], np.cumsum([s[0] for s in seqs])]).astype(np.int32)
+    cu_k = np.concatenate([[0], np.cumsum([s[1] for s in seqs])]).astype(np.int32)
+    return packed, refs, cu_q, cu_k
+
+
+CASES = [
+    # (seqs, hq, hkv, d, dtype, causal, window)
+    ([(128, 128), (256, 256)], 2, 2, 128, "fp16", True, (-1, -1)),
+    ([(100, 100), (300, 300), (77, 77), (513, 513)], 4, 2, 64, "bf16", True, (-1, -1)),
+    ([(200, 333), (64, 1000), (500, 129)], 2, 2, 128, "bf16", False, (-1, -1)),
+    ([(300, 450), (450, 300), (1, 5), (5, 3)], 4, 4, 64, "fp16", True, (-1, -1)),
+    ([(640, 640), (130, 130), (384, 384)], 2, 1, 128, "fp16", True, (100, -1)),
+    ([(256, 256)] * 3 + [(1024, 1024)], 8, 8, 128, "bf16", True, (-1, -1)),
+]
+
+
+@pytest.mark.parametrize("seqs,hq,hkv,d,dtype,causal,window", CASES)
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_packed_sequences(seqs, hq, hkv, d, dtype, causal, window, deterministic):
+    packed, refs, cu_q, cu_k = packed_problem(seqs, hq, hkv, d, dtype, causal, window, seed=4000)
+    t = {n: dev(packed[n], dtype) for n in ("q", "k", "v", "dout", "out")}
+    lse = dev(packed["lse"])
+    # NaN-poisoned outputs would survive an element the kernels forget: ops allocates with empty(), so
+    # poison the caching allocator's next blocks first
+    for n in ("q", "k", "v"):
+        junk = torch.full_like(t[n], float("nan"))
+        del junk
+    dq, dk, dv, delta = ops.fa3_bwd_varlen(
+        t["dout"], t["q"], t["k"], t["v"], t["out"], lse, torch.from_numpy(cu_q).cuda(),
+        torch.from_numpy(cu_k).cuda(), max(s[0] for s in seqs), max(s[1] for s in seqs), causal,
+        deterministic=deterministic, window=window, return_delta=True, sync=True)
+    dq, dk, dv, delta = host(dq), host(dk), host(dv), host(delta)
+    for name, arr in (("dq", dq), ("dk", dk), ("dv", dv), ("delta", delta)):
+        assert np.isfinite(arr).all(), name
+    for i, ref in enumerate(refs):
+        q0, q1, k0, k1 = cu_q[i], cu_q[i + 1], cu_k[i], cu_k[i + 1]
+        got = {"dq": dq[q0:q1].transpose(1, 0, 2)[None], "dk": dk[k0:k1].transpose(1, 0, 2)[None],
+               "dv": dv[k0:k1].transpose(1, 0, 2)[None]}
+        for name in ("dq", "dk", "dv"):
+            m = golden.check_gradient(got[name], ref[name], dtype)
+            assert m["pass"], (i, seqs[i], name, m)
+        assert golden.delta_pass(golden.compare(delta[:, q0:q1][None], ref["delta"])), (i, "delta")
+
+
+def test_packed_equals_batched_bitwise_on_the_deterministic_path():
+    """Equal-length sequences: the packed call and the [B,S,H,D] call are the same computation."""
+    b, s, h, d, dtype = 3, 256, 2, 64, "bf16"
+    packed, refs, cu_q, cu_k = packed_problem([(s, s)] * b, h, h, d, dtype, True, (-1, -1), seed=9)
+    t = {n: dev(packed[n], dtype) for n in ("q", "k", "v", "dout", "out")}
+    lse_packed = dev(packed["lse"])
+    a = ops.fa3_bwd_varlen(t["dout"], t["q"], t["k"], t["v"], t["out"], lse_packed,
+                           torch.from_numpy(cu_q).cuda(), torch.from_numpy(cu_k).cuda(), s, s, True,
+                           deterministic=True, sync=True)
+    tb = {n: t[n].view(b, s, h, d) for n in t}
+    lse_b = lse_packed.view(h, b, s).permute(1, 0, 2).contiguous()
+    bb = ops.fa3_bwd(tb["dout"], tb["q"], tb["k"], tb["v"], tb["out"], lse_b, True, deterministic=True,
+                     sync=True, layout="bshd")
+    for x, y in zip(a, bb):
+        assert torch.equal(x.view(-1), y.reshape(-1))
+
+
+def test_varlen_validation():
+    import ctypes
+    from flash_attention3_b200 import capi
+    lib = capi.load()
+    cu = torch.tensor([0, 128], dtype=torch.int32, device="cuda")
+    base = dict(batch=1, seqlen_q=128, seqlen_k=128, num_heads_q=1, num_heads_kv=1, head_dim_qk=128,
+                head_dim_v=128, cu_seqlens_q=cu.data_ptr(), cu_seqlens_k=cu.data_ptr(), max_seqlen_q=128,
+                max_seqlen_k=128, total_q=128, total_k=128)
+    ok = capi.new_params(**base)
+    assert lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(ok)) == capi.STATUS_SUCCESS
+    for broken in (dict(cu_seqlens_k=None), dict(max_seqlen_q=0), dict(total_k=0), dict(seqused_q=cu.data_ptr())):
+        p = capi.new_params(**{**base, **broken})
+        assert lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(p)) == capi.STATUS_UNSUPPORTED, broken
