@@ -179,7 +179,8 @@ class Workload:
         self.cfg = cfg
         td = torch.float16 if dtype == "fp16" else torch.bfloat16
         self.q, self.k, self.v, self.do = synthetic.make_inputs(seed, b, hq, hkv, s, d, td)
-        self.out, self.lse = synthetic.forward_reference(self.q, self.k, self.v, causal)
+        # O and LSE come from the library's own forward (set-up, outside every timed region)
+        self.out, self.lse = ops.fa3_fwd(self.q, self.k, self.v, causal, sync=True)
         self.lib = capi.load()
         self.p = ops.make_params(self.q, self.k, causal)
         need = self.lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(self.p))
@@ -195,6 +196,27 @@ class Workload:
                                           ctypes.byref(self.p))
         if code != 0:
             raise RuntimeError(f"shaobo_fa3_bwd_v2 returned {code} ({self.capi.status_string(code)})")
+
+
+class ForwardWorkload:
+    """The forward kernel on the same inputs (reported under "also"; not the headline metric)."""
+
+    def __init__(self, cfg, seed, torch, capi, ops, synthetic):
+        b, hq, hkv, s, d, dtype, causal, _ = cfg
+        td = torch.float16 if dtype == "fp16" else torch.bfloat16
+        self.q, self.k, self.v, _ = synthetic.make_inputs(seed, b, hq, hkv, s, d, td)
+        self.lib, self.capi = capi.load(), capi
+        self.p = ops.make_params(self.q, self.k, causal)
+        self.out = torch.empty_like(self.q)
+        self.lse = torch.empty((b, hq, s), dtype=torch.float32, device="cuda")
+        self.flops = 0.4 * bwd_flops(b, hq, s, d, causal)  # 4*B*H*S^2*D, halved when causal
+
+    def step(self):
+        vp = lambda t: ctypes.c_void_p(t.data_ptr())
+        code = self.lib.shaobo_fa3_b200_fwd(vp(self.q), vp(self.k), vp(self.v), vp(self.out), vp(self.lse),
+                                            ctypes.byref(self.p))
+        if code != 0:
+            raise RuntimeError(f"shaobo_fa3_b200_fwd returned {code} ({self.capi.status_string(code)})")
 
 
 class L2Flush:
@@ -380,6 +402,14 @@ def main():
             ms = statistics.median(t2)
             also[name] = {"ms_per_step": ms, "tflops": w2.flops / (ms * 1e-3) / 1e12,
                           "workload": CONFIGS[name][7]}
+            del w2
+            torch.cuda.empty_cache()
+        for name in ("C3d128", "C3d64", "C4"):
+            w2 = ForwardWorkload(CONFIGS[name], 77, torch, capi, ops, synthetic)
+            t2 = time_steps(torch, w2, 10, 3, flush)
+            ms = statistics.median(t2)
+            also["forward_" + name] = {"ms_per_step": ms, "tflops": w2.flops / (ms * 1e-3) / 1e12,
+                                       "workload": "forward kernel, " + CONFIGS[name][7]}
             del w2
             torch.cuda.empty_cache()
         line["also"] = also

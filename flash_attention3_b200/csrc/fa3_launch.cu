@@ -16,6 +16,7 @@
 #include "fa3_host.h"
 #include "fused_bwd_kernel.cuh"
 #include "dq_kernel.cuh"
+#include "fwd_kernel.cuh"
 #include "rowwise_kernels.cuh"
 #include "shaobo_fa3_b200_ext.h"
 #include "shaobo_fa3_components.h"
@@ -469,6 +470,66 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
               : launch_dq_d<__half, __half>(p, mq, mk, mv, mdo, args, blocks);
 }
 
+// ---------------------------------------------------------- forward kernel
+template <typename T, int D, bool kMasked>
+int launch_fwd_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                 const FwdArgs& args, int blocks, cudaStream_t st) {
+    auto kernel = fwd_kernel<T, D, kMasked>;
+    static DeviceOnce configured;
+    if (!configured.done()) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 FwdCfg<D>::kSmemBytes) != cudaSuccess) {
+            return SHAOBO_FA3_STATUS_HIP_ERROR;
+        }
+        configured.mark();
+    }
+    kernel<<<blocks, FwdCfg<D>::kThreads, FwdCfg<D>::kSmemBytes, st>>>(mq, mk, mv, args);
+    return SHAOBO_FA3_STATUS_SUCCESS;
+}
+
+template <typename T>
+int launch_fwd_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorMap& mk,
+                 const CUtensorMap& mv, const FwdArgs& args, int blocks) {
+    cudaStream_t st = stream_of(p);
+    const bool masked = needs_general_form(p);
+    if (p->head_dim_qk == 128) {
+        return masked ? launch_fwd_t<T, 128, true>(mq, mk, mv, args, blocks, st)
+                      : launch_fwd_t<T, 128, false>(mq, mk, mv, args, blocks, st);
+    }
+    return masked ? launch_fwd_t<T, 64, true>(mq, mk, mv, args, blocks, st)
+                  : launch_fwd_t<T, 64, false>(mq, mk, mv, args, blocks, st);
+}
+
+int launch_fwd(const ShaoboFa3Params* p, const void* q, const void* k, const void* v, void* out,
+               float* lse) {
+    const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
+    const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const int d = p->head_dim_qk;
+    const TensorShape shape = shape_of(p);
+    CUtensorMap mq, mk, mv;
+    if (!make_map_16(&mq, type, q, shape.batch, p->num_heads_q, shape.rows_q, d, shape.bshd) ||
+        !make_map_16(&mk, type, k, shape.batch, p->num_heads_kv, shape.rows_k, d, shape.bshd) ||
+        !make_map_16(&mv, type, v, shape.batch, p->num_heads_kv, shape.rows_k, d, shape.bshd)) {
+        return SHAOBO_FA3_STATUS_HIP_ERROR;
+    }
+    FwdArgs args;
+    args.out = out;
+    args.lse = lse;
+    args.o_strides = strides_of(shape.bshd, p->num_heads_q, shape.rows_q, d);
+    args.batch = p->batch;
+    args.heads_q = p->num_heads_q;
+    args.heads_kv = p->num_heads_kv;
+    args.band = band_of(p);
+    args.cu_seqlens_q = p->cu_seqlens_q;
+    args.cu_seqlens_k = p->cu_seqlens_k;
+    args.lse_rows = shape.rows_q;
+    args.scale_log2 = p->softmax_scale * kLog2E;
+    const int64_t blocks64 = int64_t(tiles_of(plan_seqlen_q(p))) * p->batch * p->num_heads_q;
+    if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    return bf ? launch_fwd_d<__nv_bfloat16>(p, mq, mk, mv, args, int(blocks64))
+              : launch_fwd_d<__half>(p, mq, mk, mv, args, int(blocks64));
+}
+
 bool stage_params_ok(const ShaoboFa3Params* p) {
     // (the component entry points take fixed-length batches only)
     return p != nullptr && !is_varlen(p) && dtype_supported(p->dtype) && layout_supported(p->layout) &&
@@ -704,6 +765,26 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
         }
         stage_mark(3, st);
     }
+    if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
+    return finish(&launch, params->sync_after_launch != 0);
+}
+
+// Extension (no counterpart in the reference, which has no forward at all): the attention forward
+// that produces the out and softmax_lse inputs of shaobo_fa3_bwd_v2.  Same parameter block and the
+// same validation as the backward (deterministic is ignored: the forward has no atomics); no
+// workspace.
+extern "C" int shaobo_fa3_b200_fwd(const void* q, const void* k, const void* v, void* out,
+                                   void* softmax_lse, const ShaoboFa3Params* params) {
+    const int validation = validate_v2(params);
+    if (validation != SHAOBO_FA3_STATUS_SUCCESS) return validation;
+    if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || softmax_lse == nullptr) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    ShaoboFa3Params launch = *params;
+    if (launch.softmax_scale_is_set == 0) {
+        launch.softmax_scale = 1.0f / std::sqrt(float(launch.head_dim_qk));
+    }
+    const int status = launch_fwd(&launch, q, k, v, out, static_cast<float*>(softmax_lse));
     if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
     return finish(&launch, params->sync_after_launch != 0);
 }

@@ -1,0 +1,353 @@
+// Attention forward for sm_100a: O = softmax(Q K^T * scale) V and the log-sum-exp of every row, the
+// two tensors the backward needs next to Q, K, V.  Same tile geometry, masks, layouts and packed
+// sequences as the backward kernels (geometry.h).
+//
+// One CTA owns one (batch, query head, 128-row query tile): Q stays in shared memory, K and V tiles
+// stream through a two-stage ring, O is accumulated in tensor memory.  Per key tile:
+//
+//     S  = Q K^T          [query i on TMEM lanes, key j on columns]           SS MMA
+//     m  = max(m, rowmax S),  P = exp2((S - m) * scale*log2e),  l = l*alpha + rowsum P
+//          (thread i owns query row i: no shuffles; P is written over S as 16-bit pairs)
+//     O += P V            A = P from TMEM, B = V (MN-major)                   TS MMA
+//
+// S is double-buffered in tensor memory, so S(t+1) is computed while the softmax of tile t runs.
+// The running maximum is updated lazily: a row keeps its reference maximum until the new maximum
+// exceeds it by more than 2^8, so P stays below 256 and the accumulator only has to be rescaled
+// (tensor memory -> registers -> tensor memory) on the rare steps where some row of a warp moves
+// its reference.  The result is exact: O and l carry the same factor, which cancels in O / l.
+//
+// Tensor-memory ledger: S0 [0,128)  S1 [128,256)  O [256,256+D).
+// Shared-memory ledger: Q resident (D*256), K and V two stages each (4 x D*256), mbarriers 128:
+// 163,968 bytes at D=128, 82,048 at D=64.
+#pragma once
+
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "fused_bwd_kernel.cuh"
+#include "geometry.h"
+#include "ptx.cuh"
+
+namespace fa3b200 {
+
+struct FwdArgs {
+    void* out;                // [B,Hq,Sq,D] or [B,Sq,Hq,D] (or [total_q,Hq,D]), see o_strides
+    float* lse;               // [B,Hq,Sq] natural log ([Hq,total_q] when packed)
+    TensorStrides o_strides;  // element strides of out
+    int batch;
+    int heads_q;
+    int heads_kv;
+    Band band;                // sequence lengths and the visible band; maxima when packed
+    const int* cu_seqlens_q;  // non-null: packed sequences, see FusedArgs
+    const int* cu_seqlens_k;
+    int lse_rows;             // rows per head of lse (seqlen_q, or total_q when packed)
+    float scale_log2;         // softmax scale * log2(e)
+};
+
+template <int D>
+struct FwdCfg {
+    static constexpr int kTile = 128;
+    static constexpr int kThreads = 256;
+    static constexpr int kBoxBytes = 128 * 128;
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kOperandBytes = kBoxes * kBoxBytes;
+    static constexpr int kStages = 2;
+    static constexpr int kOffQ = 0;
+    static constexpr int kOffK = kOperandBytes;
+    static constexpr int kOffV = kOffK + kStages * kOperandBytes;
+    static constexpr int kOffBar = kOffV + kStages * kOperandBytes;
+    static constexpr int kSmemBytes = kOffBar + 128;
+    static constexpr int kTmemCols = 512;
+    static constexpr int kColS = 0;    // two buffers of 128 columns
+    static constexpr int kColO = 256;
+    static constexpr float kRescaleThreshold = 8.0f;  // log2 units
+};
+
+enum FwdBar : int {
+    kFwdQFull = 0,
+    kFwdKvFull = 1,   // 2 stages
+    kFwdKvEmpty = 3,  // 2 stages
+    kFwdSFull = 5,    // 2 buffers
+    kFwdPReady = 7,   // 2 buffers
+    kFwdPvDone = 9,
+    kFwdNum = 10,
+};
+
+template <typename T, int D, bool kMasked>
+__global__ void __launch_bounds__(256, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+           const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
+    using C = FwdCfg<D>;
+    constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = ptx::smem_u32(smem);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    auto bar = [&](int i) -> uint32_t { return sbase + C::kOffBar + 8 * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kFwdNum);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int n_q_tiles = tiles_of(a.band.seqlen_q);  // of the longest sequence
+    const int bh_count = a.batch * a.heads_q;
+    // heaviest query tiles (most visible keys) are launched first
+    const int qt = kMasked ? n_q_tiles - 1 - int(blockIdx.x) / bh_count : int(blockIdx.x) / bh_count;
+    const int bhi = int(blockIdx.x) % bh_count;
+    const int b = bhi / a.heads_q;
+    const int hq = bhi % a.heads_q;
+    const int kvh = hq / (a.heads_q / a.heads_kv);
+    // packed sequences: this batch entry's own lengths and first rows
+    Band band = a.band;
+    int q_base = 0, k_base = 0, b_coord = b;
+    if (a.cu_seqlens_q != nullptr) {
+        q_base = a.cu_seqlens_q[b];
+        k_base = a.cu_seqlens_k[b];
+        band.seqlen_q = a.cu_seqlens_q[b + 1] - q_base;
+        band.seqlen_k = a.cu_seqlens_k[b + 1] - k_base;
+        band.off = band.seqlen_k - band.seqlen_q;
+        b_coord = 0;
+    }
+    // key tiles k_begin .. k_begin + n_steps - 1 in ascending order; none when no key is visible or
+    // the query tile lies past the end of this sequence
+    const int k_begin = first_k_tile(qt, band);
+    const int n_steps = qt * C::kTile < band.seqlen_q ? k_tiles_of_q_tile(qt, band) : 0;
+    const bool misaligned = (sbase & 1023u) != 0;
+
+    if (threadIdx.x == 0) {
+        if (misaligned) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
+        ptx::mbar_init(bar(kFwdQFull), 1);
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(bar(kFwdKvFull + s), 1);
+            ptx::mbar_init(bar(kFwdKvEmpty + s), 1);
+            ptx::mbar_init(bar(kFwdSFull + s), 1);
+            ptx::mbar_init(bar(kFwdPReady + s), 128);
+        }
+        ptx::mbar_init(bar(kFwdPvDone), 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int q_row = qt * C::kTile;  // row inside the head
+
+    if (!misaligned) {
+        if (warp == 0) {
+            if (lane == 0 && n_steps > 0) {  // nothing is loaded for a tile that sees no key
+                ptx::prefetch_tensormap(&tm_q);
+                ptx::prefetch_tensormap(&tm_k);
+                ptx::prefetch_tensormap(&tm_v);
+                ptx::mbar_arrive_expect_tx(bar(kFwdQFull), C::kOperandBytes);
+#pragma unroll
+                for (int bx = 0; bx < C::kBoxes; ++bx) {
+                    ptx::tma_load_4d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kFwdQFull), bx * 64,
+                                     q_base + q_row, hq, b_coord);
+                }
+#pragma unroll 1
+                for (int t = 0; t < n_steps; ++t) {
+                    const int s = t & 1;
+                    const int kv_row = k_base + (k_begin + t) * C::kTile;
+                    if (!bounded_wait(bar(kFwdKvEmpty + s), ((t >> 1) & 1) ^ 1, abort_flag)) break;
+                    ptx::mbar_arrive_expect_tx(bar(kFwdKvFull + s), 2 * C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
+                        ptx::tma_load_4d(sbase + C::kOffK + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_k,
+                                         bar(kFwdKvFull + s), bx * 64, kv_row, kvh, b_coord);
+                        ptx::tma_load_4d(sbase + C::kOffV + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_v,
+                                         bar(kFwdKvFull + s), bx * 64, kv_row, kvh, b_coord);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // MMA issuer: the whole warp runs the role converged; the lean issue forms and the commits
+            // elect their lane inside the asm.
+            constexpr uint32_t kIdS = ptx::instr_desc_f16(kBf16, 128, 128, false, false);
+            constexpr uint32_t kIdO = ptx::instr_desc_f16(kBf16, 128, D, false, true);
+            constexpr uint32_t kHi = ptx::kDescHiSw128;
+            constexpr uint32_t kBoxStep = C::kBoxBytes >> 4;
+            auto k_step = [](int kk) -> uint32_t { return uint32_t(kk >> 2) * kBoxStep + uint32_t(kk & 3) * 2u; };
+            auto mn_step = [](int kk) -> uint32_t { return uint32_t(kk) * 128u; };
+            const uint32_t loQ = ptx::desc_lo_k_major(sbase + C::kOffQ);
+            auto issue_s = [&](int t) {
+                const uint32_t loK = ptx::desc_lo_k_major(sbase + C::kOffK + (t & 1) * C::kOperandBytes);
+                const uint32_t dst = tmem + C::kColS + (t & 1) * 128;
+                ptx::mma_ss_lean<false>(dst, loQ, loK, kHi, kIdS);
+#pragma unroll
+                for (int kk = 1; kk < D / 16; ++kk)
+                    ptx::mma_ss_lean<true>(dst, loQ + k_step(kk), loK + k_step(kk), kHi, kIdS);
+                ptx::tc_commit_elect(bar(kFwdSFull + (t & 1)));
+            };
+            bool ok = n_steps > 0 && warp_wait<false>(bar(kFwdQFull), 0, abort_flag) &&
+                      warp_wait<false>(bar(kFwdKvFull + 0), 0, abort_flag);
+            if (ok) {
+                ptx::tc_fence_after();
+                issue_s(0);
+            }
+#pragma unroll 1
+            for (int t = 0; ok && t < n_steps; ++t) {
+                if (t + 1 < n_steps) {
+                    // S(t+1) goes to the other buffer, whose last reader, P V of step t-1, is already
+                    // in the pipe ahead of it
+                    if (!(ok = warp_wait<false>(bar(kFwdKvFull + ((t + 1) & 1)), ((t + 1) >> 1) & 1, abort_flag))) break;
+                    ptx::tc_fence_after();
+                    issue_s(t + 1);
+                }
+                if (!(ok = warp_wait<false>(bar(kFwdPReady + (t & 1)), (t >> 1) & 1, abort_flag))) break;
+                ptx::tc_fence_after();
+                {
+                    const uint32_t loV = ptx::desc_lo_mn_major(sbase + C::kOffV + (t & 1) * C::kOperandBytes, C::kBoxBytes);
+                    const uint32_t p_cols = tmem + C::kColS + (t & 1) * 128;
+                    ptx::mma_ts_lean_rt(tmem + C::kColO, p_cols, loV, kHi, kIdO, t > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 1; kk < 8; ++kk)
+                        ptx::mma_ts_lean<true>(tmem + C::kColO, p_cols + kk * 8, loV + mn_step(kk), kHi, kIdO);
+                }
+                ptx::tc_commit_elect(bar(kFwdKvEmpty + (t & 1)));
+                ptx::tc_commit_elect(bar(kFwdPvDone));
+            }
+        } else if (warp >= 4) {
+            const int i = threadIdx.x - 128;  // query row inside the tile == TMEM lane
+            const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
+            const int qi = q_row + i;  // query row inside the head
+            const bool q_valid = qi < band.seqlen_q;
+            float m_ref = -INFINITY;  // reference maximum (raw scores) the exponentials are taken against
+            float l = 0.0f;           // sum of the exponentials, in units of exp2(m_ref * scale_log2)
+            bool ok = true;
+#pragma unroll 1
+            for (int t = 0; t < n_steps; ++t) {
+                const uint32_t s_cols = tl + C::kColS + (t & 1) * 128;
+                if (!(ok = warp_wait(bar(kFwdSFull + (t & 1)), (t >> 1) & 1, abort_flag))) break;
+                ptx::tc_fence_after();
+                // key j of this tile survives for query i iff mask_from <= j <= mask_to
+                const bool diagonal = kMasked && tile_needs_mask(k_begin + t, qt, band);
+                int mask_from = 0, mask_to = 0;
+                if (diagonal) key_range_of_query(qi, (k_begin + t) * C::kTile, band, &mask_from, &mask_to);
+                // ---- pass 1: row maximum of this tile
+                float mt = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(s_cols + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    if (diagonal) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const int j = c * 32 + e;
+                            if (j >= mask_from && j <= mask_to) mt = fmaxf(mt, __uint_as_float(r[e]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) mt = fmaxf(mt, __uint_as_float(r[e]));
+                    }
+                }
+                // ---- move the reference maximum only when it is more than 2^8 too small
+                float alpha = 1.0f;
+                const bool move = (mt - m_ref) * a.scale_log2 > C::kRescaleThreshold;  // also -inf -> finite
+                if (move) {
+                    alpha = ptx::ex2_approx((m_ref - mt) * a.scale_log2);  // exp2(-inf) = 0 on the first move
+                    m_ref = mt;
+                    l *= alpha;
+                }
+                if (t > 0 && __any_sync(0xffffffffu, move)) {
+                    // O carries the old reference: wait for P V of step t-1, then rescale these 32 rows
+                    if (!(ok = warp_wait(bar(kFwdPvDone), (t - 1) & 1, abort_flag))) break;
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(tl + C::kColO + c * 32, r);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+                        ptx::tmem_st32(tl + C::kColO + c * 32, r);
+                    }
+                    ptx::tmem_st_wait();
+                }
+                // ---- pass 2: P = exp2((S - m_ref) * scale_log2), written over S as 16-bit pairs
+                const float neg = m_ref == -INFINITY ? 0.0f : -m_ref * a.scale_log2;
+                float sum = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(s_cols + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    uint32_t o[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, neg));
+                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, neg));
+                        if (diagonal) {
+                            const int j = c * 32 + e;
+                            p0 = (j + 0 >= mask_from && j + 0 <= mask_to) ? p0 : 0.0f;
+                            p1 = (j + 1 >= mask_from && j + 1 <= mask_to) ? p1 : 0.0f;
+                        }
+                        sum += p0 + p1;
+                        o[e / 2] = ptx::Pack2<T>::pack(p0, p1);
+                    }
+                    // P chunk c lands on columns [16c, 16c+16) of this S buffer, all of which were read by
+                    // chunk loads <= c
+                    ptx::tmem_st16(s_cols + c * 16, o);
+                }
+                l += sum;
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(bar(kFwdPReady + (t & 1)));
+            }
+            if (ok && n_steps > 0) ok = warp_wait(bar(kFwdPvDone), (n_steps - 1) & 1, abort_flag);
+            T* dst = reinterpret_cast<T*>(a.out) + b_coord * a.o_strides.batch + hq * a.o_strides.head +
+                     int64_t(q_base + qi) * a.o_strides.row;
+            float* lse_dst = a.lse + int64_t(b_coord * a.heads_q + hq) * a.lse_rows + q_base + qi;
+            if (ok && q_valid && n_steps == 0) {
+                // no visible key at all: O = 0, lse = -inf
+                uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                for (int e = 0; e < D / 8; ++e) d4[e] = make_uint4(0u, 0u, 0u, 0u);
+                *lse_dst = -INFINITY;
+            }
+            if (ok && n_steps > 0) {
+                // (tensor-memory loads are warp-wide: every lane runs them, only the stores of query rows
+                // past the end of the sequence are skipped)
+                ptx::tc_fence_after();
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                if (q_valid) {
+                    // ln(sum exp(s*scale)) = (m_ref*scale_log2 + log2 l) * ln 2
+                    *lse_dst = l > 0.0f ? (m_ref * a.scale_log2 + __log2f(l)) * 0.69314718055994531f : -INFINITY;
+                }
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tl + C::kColO + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    if (q_valid) {
+                        uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            uint4 o;
+                            o.x = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 0]) * inv, __uint_as_float(r[8 * e + 1]) * inv);
+                            o.y = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 2]) * inv, __uint_as_float(r[8 * e + 3]) * inv);
+                            o.z = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 4]) * inv, __uint_as_float(r[8 * e + 5]) * inv);
+                            o.w = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 6]) * inv, __uint_as_float(r[8 * e + 7]) * inv);
+                            d4[e] = o;
+                        }
+                    }
+                    __syncwarp();  // reconverge before the next warp-wide load
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem, C::kTmemCols);
+    }
+}
+
+}  // namespace fa3b200

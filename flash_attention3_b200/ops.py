@@ -82,6 +82,60 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
     return (dq, dk, dv, delta) if return_delta else (dq, dk, dv)
 
 
+def fa3_fwd(q, k, v, causal: bool, softmax_scale=None, layout: str = "bhsd", window=(-1, -1), sync=False):
+    """out, softmax_lse = forward of softmax(q k^T * scale) v (shaobo_fa3_b200_fwd).  Shapes, layouts,
+    masks as in fa3_bwd; softmax_lse is fp32 [B,Hq,Sq] natural log."""
+    _require_cuda(q, k, v)
+    lib = capi.load()
+    p = make_params(q, k, causal, softmax_scale, layout=layout, sync_after_launch=int(sync),
+                    window_left=int(window[0]), window_right=int(window[1]))
+    out = torch.empty_like(q)
+    lse = torch.empty((p.batch, p.num_heads_q, p.seqlen_q), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        p.reserved_ptr[capi.RESERVED_PTR_STREAM] = torch.cuda.current_stream().cuda_stream or None
+        code = lib.shaobo_fa3_b200_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), ctypes.byref(p))
+    if code != capi.STATUS_SUCCESS:
+        raise Fa3Error("shaobo_fa3_b200_fwd", code)
+    return out, lse
+
+
+def _varlen_params(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, softmax_scale, window,
+                   **extra) -> capi.Params:
+    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32:
+        raise TypeError("cu_seqlens must be int32")
+    total_q, hq, d = q.shape
+    total_k, hkv, _ = k.shape
+    p = capi.new_params(batch=cu_seqlens_q.numel() - 1, seqlen_q=int(max_seqlen_q), seqlen_k=int(max_seqlen_k),
+                        num_heads_q=hq, num_heads_kv=hkv, head_dim_qk=d, head_dim_v=d, causal=int(causal),
+                        dtype=_DTYPES[q.dtype], layout=capi.LAYOUT_BSHD,
+                        window_left=int(window[0]), window_right=int(window[1]),
+                        cu_seqlens_q=cu_seqlens_q.data_ptr(), cu_seqlens_k=cu_seqlens_k.data_ptr(),
+                        max_seqlen_q=int(max_seqlen_q), max_seqlen_k=int(max_seqlen_k),
+                        total_q=int(total_q), total_k=int(total_k), **extra)
+    if softmax_scale is not None:
+        p.softmax_scale = float(softmax_scale)
+        p.softmax_scale_is_set = 1
+    return p
+
+
+def fa3_fwd_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int, causal: bool,
+                   softmax_scale=None, window=(-1, -1), sync=False):
+    """Forward over packed sequences: q [total_q,Hq,D], k/v [total_k,Hkv,D] -> out [total_q,Hq,D],
+    softmax_lse fp32 [Hq,total_q]."""
+    _require_cuda(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    lib = capi.load()
+    p = _varlen_params(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, softmax_scale,
+                       window, sync_after_launch=int(sync))
+    out = torch.empty_like(q)
+    lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        p.reserved_ptr[capi.RESERVED_PTR_STREAM] = torch.cuda.current_stream().cuda_stream or None
+        code = lib.shaobo_fa3_b200_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), ctypes.byref(p))
+    if code != capi.STATUS_SUCCESS:
+        raise Fa3Error("shaobo_fa3_b200_fwd", code)
+    return out, lse
+
+
 def fa3_bwd_varlen(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int,
                    max_seqlen_k: int, causal: bool, softmax_scale=None, deterministic=False, window=(-1, -1),
                    return_delta=False, sync=False):
@@ -89,22 +143,10 @@ def fa3_bwd_varlen(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, 
     softmax_lse: fp32 [Hq, total_q]; cu_seqlens_*: int32 device tensors of batch+1 row offsets.
     Returns dq, dk, dv in the shapes of q, k, v (and delta [Hq, total_q]).  Calls shaobo_fa3_bwd_v2."""
     _require_cuda(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k)
-    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32:
-        raise TypeError("cu_seqlens must be int32")
     lib = capi.load()
-    total_q, hq, d = q.shape
-    total_k, hkv, _ = k.shape
-    batch = cu_seqlens_q.numel() - 1
-    p = capi.new_params(batch=batch, seqlen_q=int(max_seqlen_q), seqlen_k=int(max_seqlen_k), num_heads_q=hq,
-                        num_heads_kv=hkv, head_dim_qk=d, head_dim_v=d, causal=int(causal), dtype=_DTYPES[q.dtype],
-                        layout=capi.LAYOUT_BSHD, deterministic=int(deterministic), sync_after_launch=int(sync),
-                        window_left=int(window[0]), window_right=int(window[1]),
-                        cu_seqlens_q=cu_seqlens_q.data_ptr(), cu_seqlens_k=cu_seqlens_k.data_ptr(),
-                        max_seqlen_q=int(max_seqlen_q), max_seqlen_k=int(max_seqlen_k),
-                        total_q=int(total_q), total_k=int(total_k))
-    if softmax_scale is not None:
-        p.softmax_scale = float(softmax_scale)
-        p.softmax_scale_is_set = 1
+    total_q, hq = q.shape[0], q.shape[1]
+    p = _varlen_params(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, softmax_scale,
+                       window, deterministic=int(deterministic), sync_after_launch=int(sync))
     need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
     if need == 0:
         raise Fa3Error("shaobo_fa3_bwd_v2_validate", lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(p)))

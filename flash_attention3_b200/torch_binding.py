@@ -3,9 +3,10 @@ reference docs/tridao_fa3_bwd_api.md:48-55, and never shipped).
 
 * ``torch.ops.fa3b200.attention_bwd`` - a ``torch.library`` custom op over the C entry point
   ``shaobo_fa3_bwd_v2`` with a fake (meta) implementation, so it can sit inside traced graphs.
-* ``attention`` - an ``autograd.Function`` whose backward is that op.  Its forward is NOT part of
-  this library: it is a plain fp32 torch softmax (``synthetic.forward_reference``) that exists so
-  that the backward can be driven from ``loss.backward()``; a matching forward kernel is future work.
+* ``torch.ops.fa3b200.attention_fwd`` - the same for the forward kernel (``shaobo_fa3_b200_fwd``),
+  which returns O and the log-sum-exp the backward needs.
+* ``attention`` - an ``autograd.Function`` over the two ops, so that the library can be driven from
+  ``loss.backward()``.
 
 Tensors are BHSD, contiguous, fp16 or bf16, on a CUDA device; there is no CPU path.
 """
@@ -13,7 +14,7 @@ from __future__ import annotations
 
 import torch
 
-from . import ops, synthetic
+from . import ops
 
 
 @torch.library.custom_op("fa3b200::attention_bwd", mutates_args=(), device_types="cuda")
@@ -30,11 +31,23 @@ def _(dout, q, k, v, out, softmax_lse, causal, softmax_scale, deterministic):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
+@torch.library.custom_op("fa3b200::attention_fwd", mutates_args=(), device_types="cuda")
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool,
+                  softmax_scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+    out, lse = ops.fa3_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, softmax_scale)
+    return out, lse
+
+
+@attention_fwd.register_fake
+def _(q, k, v, causal, softmax_scale):
+    return torch.empty_like(q), q.new_empty(q.shape[:3], dtype=torch.float32)
+
+
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, softmax_scale, deterministic):
         scale = softmax_scale if softmax_scale is not None else ops.default_scale(q.shape[-1])
-        out, lse = synthetic.forward_reference(q, k, v, causal, scale)
+        out, lse = torch.ops.fa3b200.attention_fwd(q, k, v, causal, scale)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.causal, ctx.scale, ctx.deterministic = causal, scale, deterministic
         return out

@@ -79,6 +79,25 @@ int shaobo_fa3_b200_bwd_v2_noalloc(const void* dout,
                                    void* softmax_d,
                                    const ShaoboFa3Params* params);
 
+/* Attention forward: out = softmax(q k^T * scale) v and softmax_lse = the
+ * natural-log log-sum-exp of every row, i.e. the two tensors shaobo_fa3_bwd_v2
+ * takes next to q, k, v.  No counterpart in the reference, which is a backward
+ * only and expects them from the caller's forward
+ * (reference docs/tridao_fa3_bwd_api.md:48-55).
+ *
+ * Same parameter block, validation and status codes as shaobo_fa3_bwd_v2 (all
+ * layouts, lengths, windows and packed sequences it accepts); `deterministic`
+ * and the workspace fields are ignored, nothing is allocated.  out has the
+ * shape, dtype and layout of q; softmax_lse is fp32 [B,Hq,Sq] ([Hq,total_q]
+ * for packed sequences).  A query that sees no key gets out = 0 and
+ * softmax_lse = -inf. */
+int shaobo_fa3_b200_fwd(const void* q,
+                        const void* k,
+                        const void* v,
+                        void* out,
+                        void* softmax_lse,
+                        const ShaoboFa3Params* params);
+
 #ifdef __cplusplus
 }
 #endif

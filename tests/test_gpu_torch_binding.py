@@ -15,7 +15,7 @@ def test_autograd_backward_matches_the_oracle():
     x = prob.device_inputs()
     q, k, v = (x[n].clone().requires_grad_(True) for n in ("q", "k", "v"))
     out = torch_binding.attention(q, k, v, causal=True, softmax_scale=prob.scale)
-    # the torch forward agrees with the oracle's forward (same rounding point)
+    # the forward kernel agrees with the oracle forward
     assert golden.compare(helpers.host(out), prob.ref["out"])["rel_l2"] < 3e-3
     out.backward(x["dout"])
     torch.cuda.synchronize()
