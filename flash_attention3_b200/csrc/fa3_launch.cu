@@ -524,7 +524,8 @@ int launch_fwd(const ShaoboFa3Params* p, const void* q, const void* k, const voi
     args.cu_seqlens_k = p->cu_seqlens_k;
     args.lse_rows = shape.rows_q;
     args.scale_log2 = p->softmax_scale * kLog2E;
-    const int64_t blocks64 = int64_t(tiles_of(plan_seqlen_q(p))) * p->batch * p->num_heads_q;
+    // one CTA per pair of query tiles
+    const int64_t blocks64 = int64_t((tiles_of(plan_seqlen_q(p)) + 1) / 2) * p->batch * p->num_heads_q;
     if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
     return bf ? launch_fwd_d<__nv_bfloat16>(p, mq, mk, mv, args, int(blocks64))
               : launch_fwd_d<__half>(p, mq, mk, mv, args, int(blocks64));

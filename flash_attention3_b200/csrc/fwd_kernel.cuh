@@ -2,23 +2,26 @@
 // two tensors the backward needs next to Q, K, V.  Same tile geometry, masks, layouts and packed
 // sequences as the backward kernels (geometry.h).
 //
-// One CTA owns one (batch, query head, 128-row query tile): Q stays in shared memory, K and V tiles
-// stream through a two-stage ring, O is accumulated in tensor memory.  Per key tile:
+// One CTA owns one (batch, query head) and TWO neighbouring 128-row query tiles, A and B.  Both Q tiles
+// stay in shared memory, K and V tiles stream through two-stage rings and are used by both query
+// tiles, and each query tile has its own softmax warpgroup, score buffer and output accumulator in
+// tensor memory.  Per key tile and query tile:
 //
 //     S  = Q K^T          [query i on TMEM lanes, key j on columns]           SS MMA
 //     m  = max(m, rowmax S),  P = exp2((S - m) * scale*log2e),  l = l*alpha + rowsum P
 //          (thread i owns query row i: no shuffles; P is written over S as 16-bit pairs)
 //     O += P V            A = P from TMEM, B = V (MN-major)                   TS MMA
 //
-// S is double-buffered in tensor memory, so S(t+1) is computed while the softmax of tile t runs.
+// The two query tiles alternate on the tensor pipe: while the softmax warpgroup of tile A works on
+// S_A(t), the pipe computes S_B(t) and P_B V, and the other way round.
 // The running maximum is updated lazily: a row keeps its reference maximum until the new maximum
 // exceeds it by more than 2^8, so P stays below 256 and the accumulator only has to be rescaled
 // (tensor memory -> registers -> tensor memory) on the rare steps where some row of a warp moves
 // its reference.  The result is exact: O and l carry the same factor, which cancels in O / l.
 //
-// Tensor-memory ledger: S0 [0,128)  S1 [128,256)  O [256,256+D).
-// Shared-memory ledger: Q resident (D*256), K and V two stages each (4 x D*256), mbarriers 128:
-// 163,968 bytes at D=128, 82,048 at D=64.
+// Tensor-memory ledger: S_A [0,128)  S_B [128,256)  O_A [256,256+D)  O_B [256+D,256+2D).
+// Shared-memory ledger: Q_A, Q_B resident (2 x D*256), K and V two stages each (4 x D*256),
+// mbarriers 256: 196,864 bytes at D=128, 98,560 at D=64.
 #pragma once
 
 #include <cuda.h>
@@ -48,34 +51,38 @@ struct FwdArgs {
 template <int D>
 struct FwdCfg {
     static constexpr int kTile = 128;
-    static constexpr int kThreads = 256;
+    static constexpr int kThreads = 384;
     static constexpr int kBoxBytes = 128 * 128;
     static constexpr int kBoxes = D / 64;
     static constexpr int kOperandBytes = kBoxes * kBoxBytes;
     static constexpr int kStages = 2;
-    static constexpr int kOffQ = 0;
-    static constexpr int kOffK = kOperandBytes;
+    static constexpr int kOffQ = 0;                                  // two query tiles
+    static constexpr int kOffK = 2 * kOperandBytes;
     static constexpr int kOffV = kOffK + kStages * kOperandBytes;
     static constexpr int kOffBar = kOffV + kStages * kOperandBytes;
-    static constexpr int kSmemBytes = kOffBar + 128;
+    static constexpr int kSmemBytes = kOffBar + 256;
+    static_assert(kSmemBytes <= 232448, "shared-memory ledger exceeds 227 KiB");
     static constexpr int kTmemCols = 512;
-    static constexpr int kColS = 0;    // two buffers of 128 columns
-    static constexpr int kColO = 256;
+    static constexpr int kColS = 0;     // + 128 per query tile
+    static constexpr int kColO = 256;   // + D per query tile
+    static_assert(kColO + 2 * D <= kTmemCols, "tensor-memory ledger exceeds 512 columns");
     static constexpr float kRescaleThreshold = 8.0f;  // log2 units
 };
 
 enum FwdBar : int {
-    kFwdQFull = 0,
-    kFwdKvFull = 1,   // 2 stages
-    kFwdKvEmpty = 3,  // 2 stages
-    kFwdSFull = 5,    // 2 buffers
-    kFwdPReady = 7,   // 2 buffers
-    kFwdPvDone = 9,
-    kFwdNum = 10,
+    kFwdQFull = 0,    // per query tile
+    kFwdKFull = 2,    // 2 stages
+    kFwdKEmpty = 4,   // 2 stages
+    kFwdVFull = 6,    // 2 stages
+    kFwdVEmpty = 8,   // 2 stages
+    kFwdSFull = 10,   // per query tile
+    kFwdPReady = 12,  // per query tile
+    kFwdPvDone = 14,  // per query tile
+    kFwdNum = 16,
 };
 
 template <typename T, int D, bool kMasked>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
     using C = FwdCfg<D>;
@@ -88,10 +95,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kFwdNum);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
-    const int n_q_tiles = tiles_of(a.band.seqlen_q);  // of the longest sequence
+    const int n_pairs = (tiles_of(a.band.seqlen_q) + 1) / 2;  // of the longest sequence
     const int bh_count = a.batch * a.heads_q;
     // heaviest query tiles (most visible keys) are launched first
-    const int qt = kMasked ? n_q_tiles - 1 - int(blockIdx.x) / bh_count : int(blockIdx.x) / bh_count;
+    const int pair = kMasked ? n_pairs - 1 - int(blockIdx.x) / bh_count : int(blockIdx.x) / bh_count;
     const int bhi = int(blockIdx.x) % bh_count;
     const int b = bhi / a.heads_q;
     const int hq = bhi % a.heads_q;
@@ -107,22 +114,40 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         band.off = band.seqlen_k - band.seqlen_q;
         b_coord = 0;
     }
-    // key tiles k_begin .. k_begin + n_steps - 1 in ascending order; none when no key is visible or
-    // the query tile lies past the end of this sequence
-    const int k_begin = first_k_tile(qt, band);
-    const int n_steps = qt * C::kTile < band.seqlen_q ? k_tiles_of_q_tile(qt, band) : 0;
+    // Query tile x (0 = A, 1 = B) visits key tiles first[x] .. first[x] + count[x] - 1; count is 0 when
+    // no key is visible or the tile lies past the end of this sequence.  The CTA walks the union.
+    int first[2], count[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int qt = 2 * pair + x;
+        first[x] = first_k_tile(qt, band);
+        count[x] = qt * C::kTile < band.seqlen_q ? k_tiles_of_q_tile(qt, band) : 0;
+    }
+    int t_begin = 0, t_end = -1;  // inclusive range of key tiles
+    if (count[0] > 0 && count[1] > 0) {
+        t_begin = min(first[0], first[1]);
+        t_end = max(first[0] + count[0], first[1] + count[1]) - 1;
+    } else if (count[0] > 0 || count[1] > 0) {
+        const int x = count[0] > 0 ? 0 : 1;
+        t_begin = first[x];
+        t_end = first[x] + count[x] - 1;
+    }
+    const int n_iter = t_end - t_begin + 1;
+    auto active = [&](int x, int t) { return t >= first[x] && t < first[x] + count[x]; };
     const bool misaligned = (sbase & 1023u) != 0;
 
     if (threadIdx.x == 0) {
         if (misaligned) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
-        ptx::mbar_init(bar(kFwdQFull), 1);
         for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(bar(kFwdKvFull + s), 1);
-            ptx::mbar_init(bar(kFwdKvEmpty + s), 1);
+            ptx::mbar_init(bar(kFwdQFull + s), 1);
+            ptx::mbar_init(bar(kFwdKFull + s), 1);
+            ptx::mbar_init(bar(kFwdKEmpty + s), 1);
+            ptx::mbar_init(bar(kFwdVFull + s), 1);
+            ptx::mbar_init(bar(kFwdVEmpty + s), 1);
             ptx::mbar_init(bar(kFwdSFull + s), 1);
             ptx::mbar_init(bar(kFwdPReady + s), 128);
+            ptx::mbar_init(bar(kFwdPvDone + s), 1);
         }
-        ptx::mbar_init(bar(kFwdPvDone), 1);
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -134,32 +159,41 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const int q_row = qt * C::kTile;  // row inside the head
 
     if (!misaligned) {
         if (warp == 0) {
-            if (lane == 0 && n_steps > 0) {  // nothing is loaded for a tile that sees no key
+            if (lane == 0 && n_iter > 0) {
                 ptx::prefetch_tensormap(&tm_q);
                 ptx::prefetch_tensormap(&tm_k);
                 ptx::prefetch_tensormap(&tm_v);
-                ptx::mbar_arrive_expect_tx(bar(kFwdQFull), C::kOperandBytes);
 #pragma unroll
-                for (int bx = 0; bx < C::kBoxes; ++bx) {
-                    ptx::tma_load_4d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kFwdQFull), bx * 64,
-                                     q_base + q_row, hq, b_coord);
+                for (int x = 0; x < 2; ++x) {
+                    if (count[x] == 0) continue;  // nothing is loaded for a tile that sees no key
+                    ptx::mbar_arrive_expect_tx(bar(kFwdQFull + x), C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
+                        ptx::tma_load_4d(sbase + C::kOffQ + x * C::kOperandBytes + bx * C::kBoxBytes, &tm_q,
+                                         bar(kFwdQFull + x), bx * 64, q_base + (2 * pair + x) * C::kTile, hq, b_coord);
+                    }
                 }
 #pragma unroll 1
-                for (int t = 0; t < n_steps; ++t) {
-                    const int s = t & 1;
-                    const int kv_row = k_base + (k_begin + t) * C::kTile;
-                    if (!bounded_wait(bar(kFwdKvEmpty + s), ((t >> 1) & 1) ^ 1, abort_flag)) break;
-                    ptx::mbar_arrive_expect_tx(bar(kFwdKvFull + s), 2 * C::kOperandBytes);
+                for (int it = 0; it < n_iter; ++it) {
+                    const int s = it & 1;
+                    const uint32_t wait_parity = ((it >> 1) & 1) ^ 1;
+                    const int kv_row = k_base + (t_begin + it) * C::kTile;
+                    if (!bounded_wait(bar(kFwdKEmpty + s), wait_parity, abort_flag)) break;
+                    ptx::mbar_arrive_expect_tx(bar(kFwdKFull + s), C::kOperandBytes);
 #pragma unroll
                     for (int bx = 0; bx < C::kBoxes; ++bx) {
                         ptx::tma_load_4d(sbase + C::kOffK + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_k,
-                                         bar(kFwdKvFull + s), bx * 64, kv_row, kvh, b_coord);
+                                         bar(kFwdKFull + s), bx * 64, kv_row, kvh, b_coord);
+                    }
+                    if (!bounded_wait(bar(kFwdVEmpty + s), wait_parity, abort_flag)) break;
+                    ptx::mbar_arrive_expect_tx(bar(kFwdVFull + s), C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
                         ptx::tma_load_4d(sbase + C::kOffV + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_v,
-                                         bar(kFwdKvFull + s), bx * 64, kv_row, kvh, b_coord);
+                                         bar(kFwdVFull + s), bx * 64, kv_row, kvh, b_coord);
                     }
                 }
             }
@@ -172,61 +206,95 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             constexpr uint32_t kBoxStep = C::kBoxBytes >> 4;
             auto k_step = [](int kk) -> uint32_t { return uint32_t(kk >> 2) * kBoxStep + uint32_t(kk & 3) * 2u; };
             auto mn_step = [](int kk) -> uint32_t { return uint32_t(kk) * 128u; };
-            const uint32_t loQ = ptx::desc_lo_k_major(sbase + C::kOffQ);
-            auto issue_s = [&](int t) {
-                const uint32_t loK = ptx::desc_lo_k_major(sbase + C::kOffK + (t & 1) * C::kOperandBytes);
-                const uint32_t dst = tmem + C::kColS + (t & 1) * 128;
+            // S of query tile x against the key tile in ring slot `it`
+            auto issue_s = [&](int x, int it) {
+                const uint32_t loQ = ptx::desc_lo_k_major(sbase + C::kOffQ + x * C::kOperandBytes);
+                const uint32_t loK = ptx::desc_lo_k_major(sbase + C::kOffK + (it & 1) * C::kOperandBytes);
+                const uint32_t dst = tmem + C::kColS + x * 128;
                 ptx::mma_ss_lean<false>(dst, loQ, loK, kHi, kIdS);
 #pragma unroll
                 for (int kk = 1; kk < D / 16; ++kk)
                     ptx::mma_ss_lean<true>(dst, loQ + k_step(kk), loK + k_step(kk), kHi, kIdS);
-                ptx::tc_commit_elect(bar(kFwdSFull + (t & 1)));
+                ptx::tc_commit_elect(bar(kFwdSFull + x));
             };
-            bool ok = n_steps > 0 && warp_wait<false>(bar(kFwdQFull), 0, abort_flag) &&
-                      warp_wait<false>(bar(kFwdKvFull + 0), 0, abort_flag);
+            auto issue_pv = [&](int x, int it, bool accumulate) {
+                const uint32_t loV = ptx::desc_lo_mn_major(sbase + C::kOffV + (it & 1) * C::kOperandBytes, C::kBoxBytes);
+                const uint32_t p_cols = tmem + C::kColS + x * 128;
+                const uint32_t o_cols = tmem + C::kColO + x * D;
+                ptx::mma_ts_lean_rt(o_cols, p_cols, loV, kHi, kIdO, accumulate ? 1u : 0u);
+#pragma unroll
+                for (int kk = 1; kk < 8; ++kk)
+                    ptx::mma_ts_lean<true>(o_cols, p_cols + kk * 8, loV + mn_step(kk), kHi, kIdO);
+                ptx::tc_commit_elect(bar(kFwdPvDone + x));
+            };
+            bool ok = n_iter > 0;
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                if (ok && count[x] > 0) ok = warp_wait<false>(bar(kFwdQFull + x), 0, abort_flag);
+            }
+            if (ok) ok = warp_wait<false>(bar(kFwdKFull + 0), 0, abort_flag);
             if (ok) {
                 ptx::tc_fence_after();
-                issue_s(0);
-            }
-#pragma unroll 1
-            for (int t = 0; ok && t < n_steps; ++t) {
-                if (t + 1 < n_steps) {
-                    // S(t+1) goes to the other buffer, whose last reader, P V of step t-1, is already
-                    // in the pipe ahead of it
-                    if (!(ok = warp_wait<false>(bar(kFwdKvFull + ((t + 1) & 1)), ((t + 1) >> 1) & 1, abort_flag))) break;
-                    ptx::tc_fence_after();
-                    issue_s(t + 1);
-                }
-                if (!(ok = warp_wait<false>(bar(kFwdPReady + (t & 1)), (t >> 1) & 1, abort_flag))) break;
-                ptx::tc_fence_after();
-                {
-                    const uint32_t loV = ptx::desc_lo_mn_major(sbase + C::kOffV + (t & 1) * C::kOperandBytes, C::kBoxBytes);
-                    const uint32_t p_cols = tmem + C::kColS + (t & 1) * 128;
-                    ptx::mma_ts_lean_rt(tmem + C::kColO, p_cols, loV, kHi, kIdO, t > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 1; kk < 8; ++kk)
-                        ptx::mma_ts_lean<true>(tmem + C::kColO, p_cols + kk * 8, loV + mn_step(kk), kHi, kIdO);
+                for (int x = 0; x < 2; ++x) {
+                    if (active(x, t_begin)) issue_s(x, 0);
                 }
-                ptx::tc_commit_elect(bar(kFwdKvEmpty + (t & 1)));
-                ptx::tc_commit_elect(bar(kFwdPvDone));
+                ptx::tc_commit_elect(bar(kFwdKEmpty + 0));
+            }
+            int done[2] = {0, 0};  // local step counters of the two query tiles
+#pragma unroll 1
+            for (int it = 0; ok && it < n_iter; ++it) {
+                const int t = t_begin + it;
+                const bool more = it + 1 < n_iter;
+                bool v_ready = false, k_ready = false;
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    if (active(x, t)) {
+                        if (!(ok = warp_wait<false>(bar(kFwdPReady + x), done[x] & 1, abort_flag))) break;
+                        if (!v_ready) {
+                            if (!(ok = warp_wait<false>(bar(kFwdVFull + (it & 1)), (it >> 1) & 1, abort_flag))) break;
+                            v_ready = true;
+                        }
+                        ptx::tc_fence_after();
+                        issue_pv(x, it, done[x] > 0);
+                        ++done[x];
+                    }
+                    // S of the next key tile goes over P of this one: it follows P V in the pipe
+                    if (more && active(x, t + 1)) {
+                        if (!k_ready) {
+                            if (!(ok = warp_wait<false>(bar(kFwdKFull + ((it + 1) & 1)), ((it + 1) >> 1) & 1, abort_flag))) break;
+                            k_ready = true;
+                        }
+                        ptx::tc_fence_after();
+                        issue_s(x, it + 1);
+                    }
+                }
+                if (!ok) break;
+                if (more) ptx::tc_commit_elect(bar(kFwdKEmpty + ((it + 1) & 1)));
+                ptx::tc_commit_elect(bar(kFwdVEmpty + (it & 1)));
             }
         } else if (warp >= 4) {
-            const int i = threadIdx.x - 128;  // query row inside the tile == TMEM lane
+            const int x = (warp - 4) >> 2;      // which query tile
+            const int i = threadIdx.x & 127;    // query row inside the tile == TMEM lane
+            const int qt = 2 * pair + x;
+            const int n_steps = count[x];
+            const int k_begin = first[x];
             const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
-            const int qi = q_row + i;  // query row inside the head
+            const uint32_t s_cols = tl + C::kColS + x * 128;
+            const uint32_t o_cols = tl + C::kColO + x * D;
+            const int qi = qt * C::kTile + i;  // query row inside the head
             const bool q_valid = qi < band.seqlen_q;
             float m_ref = -INFINITY;  // reference maximum (raw scores) the exponentials are taken against
             float l = 0.0f;           // sum of the exponentials, in units of exp2(m_ref * scale_log2)
             bool ok = true;
 #pragma unroll 1
-            for (int t = 0; t < n_steps; ++t) {
-                const uint32_t s_cols = tl + C::kColS + (t & 1) * 128;
-                if (!(ok = warp_wait(bar(kFwdSFull + (t & 1)), (t >> 1) & 1, abort_flag))) break;
+            for (int u = 0; u < n_steps; ++u) {
+                if (!(ok = warp_wait(bar(kFwdSFull + x), u & 1, abort_flag))) break;
                 ptx::tc_fence_after();
                 // key j of this tile survives for query i iff mask_from <= j <= mask_to
-                const bool diagonal = kMasked && tile_needs_mask(k_begin + t, qt, band);
+                const bool diagonal = kMasked && tile_needs_mask(k_begin + u, qt, band);
                 int mask_from = 0, mask_to = 0;
-                if (diagonal) key_range_of_query(qi, (k_begin + t) * C::kTile, band, &mask_from, &mask_to);
+                if (diagonal) key_range_of_query(qi, (k_begin + u) * C::kTile, band, &mask_from, &mask_to);
                 // ---- pass 1: row maximum of this tile
                 float mt = -INFINITY;
 #pragma unroll
@@ -253,18 +321,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     m_ref = mt;
                     l *= alpha;
                 }
-                if (t > 0 && __any_sync(0xffffffffu, move)) {
-                    // O carries the old reference: wait for P V of step t-1, then rescale these 32 rows
-                    if (!(ok = warp_wait(bar(kFwdPvDone), (t - 1) & 1, abort_flag))) break;
+                if (u > 0 && __any_sync(0xffffffffu, move)) {
+                    // O carries the old reference: wait for P V of step u-1, then rescale these 32 rows
+                    if (!(ok = warp_wait(bar(kFwdPvDone + x), (u - 1) & 1, abort_flag))) break;
                     ptx::tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < D / 32; ++c) {
                         uint32_t r[32];
-                        ptx::tmem_ld32(tl + C::kColO + c * 32, r);
+                        ptx::tmem_ld32(o_cols + c * 32, r);
                         ptx::tmem_ld_wait();
 #pragma unroll
                         for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-                        ptx::tmem_st32(tl + C::kColO + c * 32, r);
+                        ptx::tmem_st32(o_cols + c * 32, r);
                     }
                     ptx::tmem_st_wait();
                 }
@@ -289,16 +357,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                         sum += p0 + p1;
                         o[e / 2] = ptx::Pack2<T>::pack(p0, p1);
                     }
-                    // P chunk c lands on columns [16c, 16c+16) of this S buffer, all of which were read by
+                    // P chunk c lands on columns [16c, 16c+16) of the S region, all of which were read by
                     // chunk loads <= c
                     ptx::tmem_st16(s_cols + c * 16, o);
                 }
                 l += sum;
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(bar(kFwdPReady + (t & 1)));
+                ptx::mbar_arrive(bar(kFwdPReady + x));
             }
-            if (ok && n_steps > 0) ok = warp_wait(bar(kFwdPvDone), (n_steps - 1) & 1, abort_flag);
+            if (ok && n_steps > 0) ok = warp_wait(bar(kFwdPvDone + x), (n_steps - 1) & 1, abort_flag);
             T* dst = reinterpret_cast<T*>(a.out) + b_coord * a.o_strides.batch + hq * a.o_strides.head +
                      int64_t(q_base + qi) * a.o_strides.row;
             float* lse_dst = a.lse + int64_t(b_coord * a.heads_q + hq) * a.lse_rows + q_base + qi;
@@ -321,7 +389,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t r[32];
-                    ptx::tmem_ld32(tl + C::kColO + c * 32, r);
+                    ptx::tmem_ld32(o_cols + c * 32, r);
                     ptx::tmem_ld_wait();
                     if (q_valid) {
                         uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
