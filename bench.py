@@ -307,6 +307,8 @@ def main():
     ap.add_argument("--config", default="C2", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip cpu_baseline, e2e and the 'also' configurations")
+    ap.add_argument("--forward-only", action="store_true",
+                    help="time the forward kernel alone on --config (one GPU; a profiling aid, not the headline metric)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     cfg = CONFIGS[args.config]
@@ -327,6 +329,16 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    if args.forward_only:
+        flush = L2Flush(torch)
+        fw = ForwardWorkload(cfg, 77, torch, capi, ops, synthetic)
+        ms = statistics.median(time_steps(torch, fw, args.steps, args.warmup, flush))
+        print(json.dumps({"metric": "attention forward throughput", "value": fw.flops / (ms * 1e-3) / 1e12,
+                          "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                          "config": {"workload": "forward kernel, " + cfg[7]}, "gpu_launches": args.steps}))
+        return
 
     b, hq, hkv, s, d, dtype, causal, desc = cfg
     strong = args.config == "C5"
