@@ -583,11 +583,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #endif
 #pragma unroll
                     for (int e = 0; e < 32; e += 4) {
-#ifdef FA3B200_EXPERIMENT_NOSTATS
-                        const float4 n4 = make_float4(-8.f, -8.f, -8.f, -8.f);
-#else
                         const float4 n4 = *reinterpret_cast<const float4*>(negp + c * 32 + e);
-#endif
                         float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, n4.x));
                         float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, n4.y));
                         float p2 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 2]), a.scale_log2, n4.z));
@@ -643,12 +639,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #endif
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
-#ifdef FA3B200_EXPERIMENT_NOSTATS
-                        const float4 d0 = make_float4(.1f, .1f, .1f, .1f), d1 = d0;
-#else
                         const float4 d0 = *reinterpret_cast<const float4*>(delp + c * 32 + e);
                         const float4 d1 = *reinterpret_cast<const float4*>(delp + c * 32 + e + 4);
-#endif
                         const float2 pa = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 0]);
                         const float2 pb = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 1]);
                         const float2 pc = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 2]);
@@ -792,14 +784,12 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         }
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
-#ifndef FA3B200_EXPERIMENT_NOREDUCE
                         // accumulator map: [batch*head][row][D]; rows past the sequence end are dropped
                         if (lane == 0 && q_row < band.seqlen_q) {
                             ptx::tma_reduce_add_3d(&tm_dqacc, stage, hf * 64, q_base + q_row, q_head);
                             ptx::tma_reduce_add_3d(&tm_dqacc, stage + C::kStageBoxBytes, hf * 64 + 32, q_base + q_row, q_head);
                             ptx::bulk_commit_group();
                         }
-#endif
                         pending = true;
                     }
                     DBG_STAMP(3);

@@ -127,10 +127,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     if (count[0] > 0 && count[1] > 0) {
         t_begin = min(first[0], first[1]);
         t_end = max(first[0] + count[0], first[1] + count[1]) - 1;
-    } else if (count[0] > 0 || count[1] > 0) {
-        const int x = count[0] > 0 ? 0 : 1;
-        t_begin = first[x];
-        t_end = first[x] + count[x] - 1;
+    } else if (count[0] > 0) {
+        t_begin = first[0];
+        t_end = first[0] + count[0] - 1;
+    } else if (count[1] > 0) {
+        t_begin = first[1];
+        t_end = first[1] + count[1] - 1;
     }
     const int n_iter = t_end - t_begin + 1;
     auto active = [&](int x, int t) { return t >= first[x] && t < first[x] + count[x]; };
@@ -277,8 +279,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const int x = (warp - 4) >> 2;      // which query tile
             const int i = threadIdx.x & 127;    // query row inside the tile == TMEM lane
             const int qt = 2 * pair + x;
-            const int n_steps = count[x];
-            const int k_begin = first[x];
+            const int n_steps = x == 0 ? count[0] : count[1];  // (selects, not indexing: no local array)
+            const int k_begin = x == 0 ? first[0] : first[1];
             const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
             const uint32_t s_cols = tl + C::kColS + x * 128;
             const uint32_t o_cols = tl + C::kColO + x * D;

@@ -340,13 +340,9 @@ __device__ __forceinline__ void setmaxnreg_dec() {
 
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ float ex2_approx(float x) {
-#ifdef FA3B200_EXPERIMENT_NOEX2
-    return x * 0.001f;  // timing experiment only: wrong numerics
-#else
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-#endif
 }
 
 template <typename T>
