@@ -38,6 +38,8 @@ struct DqArgs {
     Band band;                // sequence lengths and the visible band (geometry.h); maxima when packed
     const int* cu_seqlens_q;  // non-null: packed sequences, see FusedArgs
     const int* cu_seqlens_k;
+    const int* seqused_q;     // non-null: used lengths per batch entry, see FusedArgs
+    const int* seqused_k;
     int sidecar_rows;         // rows per head of the sidecar (seqlen_q, or total_q when packed)
     float scale;
     float scale_log2;
@@ -108,6 +110,12 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         band.seqlen_k = a.cu_seqlens_k[b + 1] - k_base;
         band.off = band.seqlen_k - band.seqlen_q;
         b_coord = 0;
+    }
+    const int slot_q = band.seqlen_q;  // rows of dQ this batch entry owns
+    if (a.seqused_q != nullptr || a.seqused_k != nullptr) {
+        if (a.seqused_q != nullptr) band.seqlen_q = max(0, min(band.seqlen_q, a.seqused_q[b]));
+        if (a.seqused_k != nullptr) band.seqlen_k = max(0, min(band.seqlen_k, a.seqused_k[b]));
+        band.off = band.seqlen_k - band.seqlen_q;
     }
     // key tiles k_begin .. k_begin + n_steps - 1 in ascending order; none when no key is visible or
     // the query tile lies past the end of this sequence
@@ -292,12 +300,13 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (ok && n_steps > 0) ok = warp_wait(bar(kDqbDone), 0, abort_flag);
             TOut* dst = reinterpret_cast<TOut*>(a.dq) + b_coord * a.q_strides.batch + hq * a.q_strides.head +
                         int64_t(q_base + qi) * a.q_strides.row;
-            if (ok && q_valid && n_steps == 0) {
-                // no visible key at all: the gradient of these rows is zero
+            if (ok && ((q_valid && n_steps == 0) || (!q_valid && qi < slot_q))) {
+                // no visible key at all, or a row behind the used length: the gradient is zero
                 uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
                 for (int e = 0; e < int(D * sizeof(TOut) / 16); ++e) d4[e] = make_uint4(0u, 0u, 0u, 0u);
             }
+            __syncwarp();
             if (ok && n_steps > 0) {
                 // (tensor-memory loads are warp-wide: every lane runs them, only the stores of query
                 // rows past the end of the sequence are skipped)

@@ -45,10 +45,8 @@ bool lengths_in_range(const ShaoboFa3Params* p) {
     return p->seqlen_q < kUnbounded && p->seqlen_k < kUnbounded;
 }
 
-// Packed sequences need both offset arrays, the two maxima and the two totals; seqused_* (lengths
-// shorter than the slots) is not supported.
+// Packed sequences need both offset arrays, the two maxima and the two totals.
 bool varlen_fields_ok(const ShaoboFa3Params* p) {
-    if (p->seqused_q || p->seqused_k) return false;
     if (p->cu_seqlens_q == nullptr || p->cu_seqlens_k == nullptr) return false;
     if (p->max_seqlen_q <= 0 || p->max_seqlen_k <= 0 || p->total_q <= 0 || p->total_k <= 0) return false;
     if (p->max_seqlen_q >= kUnbounded || p->max_seqlen_k >= kUnbounded) return false;
@@ -57,7 +55,7 @@ bool varlen_fields_ok(const ShaoboFa3Params* p) {
 }
 
 bool lengths_are_fixed(const ShaoboFa3Params* p) {
-    if (p->cu_seqlens_q || p->cu_seqlens_k || p->seqused_q || p->seqused_k) return false;
+    if (p->cu_seqlens_q || p->cu_seqlens_k) return false;
     if (p->max_seqlen_q != 0 && p->max_seqlen_q != p->seqlen_q) return false;
     if (p->max_seqlen_k != 0 && p->max_seqlen_k != p->seqlen_k) return false;
     const int64_t tq = int64_t(p->batch) * p->seqlen_q;
@@ -126,8 +124,9 @@ size_t dq_accum_bytes(const ShaoboFa3Params* p) {
 
 SplitPlan split_plan(const ShaoboFa3Params* p) {
     SplitPlan plan;
-    // (per-sequence lengths of packed sequences are not known on the host: no splitting there)
-    if (!fused_shape_ok(p) || p->deterministic != 0 || is_varlen(p)) return plan;
+    // (per-sequence lengths of packed sequences, and used lengths, are not known on the host: no
+    // splitting there)
+    if (!fused_shape_ok(p) || p->deterministic != 0 || is_varlen(p) || has_seqused(p)) return plan;
     const int tiles = tiles_of(p->seqlen_k);
     const Band band = band_of(p);
     const long long heads = (long long)p->batch * p->num_heads_kv;

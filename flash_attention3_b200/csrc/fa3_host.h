@@ -37,6 +37,11 @@ inline bool dtype_supported(int t) {
 inline bool is_varlen(const ShaoboFa3Params* p) {
     return p->cu_seqlens_q != nullptr || p->cu_seqlens_k != nullptr;
 }
+// seqused_q / seqused_k (device arrays of batch int32): only the first seqused[b] rows of batch entry
+// b take part; works with fixed-length batches and with packed sequences.
+inline bool has_seqused(const ShaoboFa3Params* p) {
+    return p->seqused_q != nullptr || p->seqused_k != nullptr;
+}
 // Length the launch is planned for: the sequence length, or the longest sequence when packed.
 inline int plan_seqlen_q(const ShaoboFa3Params* p) { return is_varlen(p) ? p->max_seqlen_q : p->seqlen_q; }
 inline int plan_seqlen_k(const ShaoboFa3Params* p) { return is_varlen(p) ? p->max_seqlen_k : p->seqlen_k; }

@@ -77,7 +77,7 @@ bool make_map_accum(CUtensorMap* map, const float* base, int64_t batch_heads, in
 // The kernels come in two forms: a lean one for full attention over whole 128-row tiles and a general
 // one (causal mask, sliding window, ragged sequence ends).
 bool needs_general_form(const ShaoboFa3Params* p) {
-    return is_varlen(p) || !band_is_full(band_of(p)) || p->seqlen_q % kTileRows != 0 ||
+    return is_varlen(p) || has_seqused(p) || !band_is_full(band_of(p)) || p->seqlen_q % kTileRows != 0 ||
            p->seqlen_k % kTileRows != 0;
 }
 
@@ -377,6 +377,8 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     args.band = band;
     args.cu_seqlens_q = p->cu_seqlens_q;
     args.cu_seqlens_k = p->cu_seqlens_k;
+    args.seqused_q = p->seqused_q;
+    args.seqused_k = p->seqused_k;
     args.sidecar_rows = shape.rows_q;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
@@ -456,6 +458,8 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
     args.band = band_of(p);
     args.cu_seqlens_q = p->cu_seqlens_q;
     args.cu_seqlens_k = p->cu_seqlens_k;
+    args.seqused_q = p->seqused_q;
+    args.seqused_k = p->seqused_k;
     args.sidecar_rows = shape.rows_q;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
@@ -522,6 +526,8 @@ int launch_fwd(const ShaoboFa3Params* p, const void* q, const void* k, const voi
     args.band = band_of(p);
     args.cu_seqlens_q = p->cu_seqlens_q;
     args.cu_seqlens_k = p->cu_seqlens_k;
+    args.seqused_q = p->seqused_q;
+    args.seqused_k = p->seqused_k;
     args.lse_rows = shape.rows_q;
     args.scale_log2 = p->softmax_scale * kLog2E;
     // one CTA per pair of query tiles
@@ -533,7 +539,7 @@ int launch_fwd(const ShaoboFa3Params* p, const void* q, const void* k, const voi
 
 bool stage_params_ok(const ShaoboFa3Params* p) {
     // (the component entry points take fixed-length batches only)
-    return p != nullptr && !is_varlen(p) && dtype_supported(p->dtype) && layout_supported(p->layout) &&
+    return p != nullptr && !is_varlen(p) && !has_seqused(p) && dtype_supported(p->dtype) && layout_supported(p->layout) &&
            (p->causal == 0 || p->causal == 1) && fused_shape_ok(p);
 }
 

@@ -93,6 +93,8 @@ struct FusedArgs {
                            // sequences the lengths are the maxima and each CTA reads its own
     const int* cu_seqlens_q;  // non-null: sequences are packed ([total, H, D] tensors) and sequence b
     const int* cu_seqlens_k;  // owns rows cu[b] .. cu[b+1]-1; the tensor maps then have batch = 1
+    const int* seqused_q;     // non-null: only the first seqused[b] rows of batch entry b take part; the
+    const int* seqused_k;     // gradient rows behind them, up to the end of the entry's slot, are zero
     int sidecar_rows;      // rows per head of the sidecar / accumulators (seqlen_q, or total_q when packed)
     float scale;
     float scale_log2;
@@ -280,6 +282,12 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         band.off = band.seqlen_k - band.seqlen_q;
         b_coord = 0;
     }
+    const int slot_k = band.seqlen_k;  // rows of dK / dV this batch entry owns
+    if (a.seqused_q != nullptr || a.seqused_k != nullptr) {
+        if (a.seqused_q != nullptr) band.seqlen_q = max(0, min(band.seqlen_q, a.seqused_q[b]));
+        if (a.seqused_k != nullptr) band.seqlen_k = max(0, min(band.seqlen_k, a.seqused_k[b]));
+        band.off = band.seqlen_k - band.seqlen_q;
+    }
     const int n_q_tiles = tiles_of(band.seqlen_q);
     const bool tile_exists = kt * C::kTile < band.seqlen_k;  // false only with packed sequences
     const int q_begin = first_q_tile(kt, band);
@@ -330,7 +338,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // Query tiles are visited in ascending order starting at the diagonal (causal) or at a
     // per-CTA rotation (non-causal), so that CTAs of one head that run together add into
     // different dQ tiles at any moment.
-    const int rotation = kCausal ? 0 : kt % n_q_tiles;
+    const int rotation = (kCausal || n_q_tiles == 0) ? 0 : kt % n_q_tiles;
     auto step_coords = [&](int t_local, int& hq, int& qt) {
         const int t = t_begin + t_local;
         const int g = t / steps_per_head;
@@ -679,7 +687,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (ok && !split) {
                 // (tensor-memory loads are warp-wide: every lane runs them, only the stores of key rows
                 // past the end of the sequence are skipped)
-                const bool key_valid = kt * C::kTile + j < band.seqlen_k;
+                // (rows between the used length and the end of the slot hold exact zeros)
+                const bool key_valid = kt * C::kTile + j < slot_k;
                 ptx::tc_fence_after();
                 const int64_t off = b_coord * a.kv_strides.batch + kvh * a.kv_strides.head +
                                     int64_t(k_base + kt * C::kTile + j) * a.kv_strides.row;
@@ -717,7 +726,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         } else if (owes_zeros) {
             // nobody attends to these keys: the first warpgroup clears dK, the second dV
             const int j = threadIdx.x & 127;
-            if (kt * C::kTile + j < band.seqlen_k) {
+            if (kt * C::kTile + j < slot_k) {
                 const int64_t off = b_coord * a.kv_strides.batch + kvh * a.kv_strides.head +
                                     int64_t(k_base + kt * C::kTile + j) * a.kv_strides.row;
                 uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<TOut*>(wg == 1 ? a.dk : a.dv) + off);

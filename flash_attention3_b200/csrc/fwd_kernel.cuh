@@ -44,6 +44,8 @@ struct FwdArgs {
     Band band;                // sequence lengths and the visible band; maxima when packed
     const int* cu_seqlens_q;  // non-null: packed sequences, see FusedArgs
     const int* cu_seqlens_k;
+    const int* seqused_q;     // non-null: used lengths per batch entry, see FusedArgs; rows behind them
+    const int* seqused_k;     // get out = 0 and lse = -inf
     int lse_rows;             // rows per head of lse (seqlen_q, or total_q when packed)
     float scale_log2;         // softmax scale * log2(e)
 };
@@ -113,6 +115,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         band.seqlen_k = a.cu_seqlens_k[b + 1] - k_base;
         band.off = band.seqlen_k - band.seqlen_q;
         b_coord = 0;
+    }
+    const int slot_q = band.seqlen_q;  // rows of out this batch entry owns
+    if (a.seqused_q != nullptr || a.seqused_k != nullptr) {
+        if (a.seqused_q != nullptr) band.seqlen_q = max(0, min(band.seqlen_q, a.seqused_q[b]));
+        if (a.seqused_k != nullptr) band.seqlen_k = max(0, min(band.seqlen_k, a.seqused_k[b]));
+        band.off = band.seqlen_k - band.seqlen_q;
     }
     // Query tile x (0 = A, 1 = B) visits key tiles first[x] .. first[x] + count[x] - 1; count is 0 when
     // no key is visible or the tile lies past the end of this sequence.  The CTA walks the union.
@@ -372,13 +380,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             T* dst = reinterpret_cast<T*>(a.out) + b_coord * a.o_strides.batch + hq * a.o_strides.head +
                      int64_t(q_base + qi) * a.o_strides.row;
             float* lse_dst = a.lse + int64_t(b_coord * a.heads_q + hq) * a.lse_rows + q_base + qi;
-            if (ok && q_valid && n_steps == 0) {
-                // no visible key at all: O = 0, lse = -inf
+            if (ok && ((q_valid && n_steps == 0) || (!q_valid && qi < slot_q))) {
+                // no visible key at all, or a row behind the used length: O = 0, lse = -inf
                 uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
                 for (int e = 0; e < D / 8; ++e) d4[e] = make_uint4(0u, 0u, 0u, 0u);
                 *lse_dst = -INFINITY;
             }
+            __syncwarp();
             if (ok && n_steps > 0) {
                 // (tensor-memory loads are warp-wide: every lane runs them, only the stores of query rows
                 // past the end of the sequence are skipped)

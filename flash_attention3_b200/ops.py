@@ -21,9 +21,18 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
+def _seqused_ptr(t):
+    if t is None:
+        return None
+    if t.dtype != torch.int32 or not t.is_cuda:
+        raise TypeError("seqused must be an int32 CUDA tensor")
+    return t.data_ptr()
+
+
 def make_params(q: torch.Tensor, k: torch.Tensor, causal: bool, softmax_scale=None, layout: str = "bhsd",
-                **extra) -> capi.Params:
-    """layout "bhsd": q [B,Hq,Sq,D], k [B,Hkv,Sk,D]; "bshd": q [B,Sq,Hq,D], k [B,Sk,Hkv,D]."""
+                seqused_q=None, seqused_k=None, **extra) -> capi.Params:
+    """layout "bhsd": q [B,Hq,Sq,D], k [B,Hkv,Sk,D]; "bshd": q [B,Sq,Hq,D], k [B,Sk,Hkv,D].
+    seqused_q / seqused_k: optional int32 [B] device tensors, the used length of every batch entry."""
     if layout == "bhsd":
         (b, hq, s, d), hkv, sk = q.shape, k.shape[1], k.shape[2]
     elif layout == "bshd":
@@ -36,6 +45,7 @@ def make_params(q: torch.Tensor, k: torch.Tensor, causal: bool, softmax_scale=No
     if softmax_scale is not None:
         p.softmax_scale = float(softmax_scale)
         p.softmax_scale_is_set = 1
+    p.seqused_q, p.seqused_k = _seqused_ptr(seqused_q), _seqused_ptr(seqused_k)
     for key, val in extra.items():
         setattr(p, key, val)
     return p
@@ -50,18 +60,21 @@ def _require_cuda(*tensors):
 
 
 def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, deterministic=False,
-            workspace=None, return_delta=False, sync=False, layout: str = "bhsd", window=(-1, -1)):
+            workspace=None, return_delta=False, sync=False, layout: str = "bhsd", window=(-1, -1),
+            seqused_q=None, seqused_k=None):
     """dq, dk, dv (and delta) = backward of softmax(q k^T * scale) v.
 
     layout "bhsd": q, out, dout [B,Hq,Sq,D]; k, v [B,Hkv,Sk,D].  layout "bshd": [B,Sq,Hq,D] and
     [B,Sk,Hkv,D].  fp16 or bf16; softmax_lse: fp32 [B,Hq,Sq] natural log in both layouts.  With
     causal=True and Sq != Sk the diagonal is aligned bottom-right.  window = (left, right): query i
     sees keys i+off-left .. i+off+right (off = Sk - Sq), -1 = unbounded; causal forces right = 0.
-    Calls shaobo_fa3_bwd_v2.
+    seqused_q / seqused_k (int32 [B]): only the first seqused[b] rows of batch entry b take part; the
+    gradient rows behind them are zero.  Calls shaobo_fa3_bwd_v2.
     """
     _require_cuda(dout, q, k, v, out, softmax_lse)
     lib = capi.load()
-    p = make_params(q, k, causal, softmax_scale, layout=layout, deterministic=int(deterministic),
+    p = make_params(q, k, causal, softmax_scale, layout=layout, seqused_q=seqused_q, seqused_k=seqused_k,
+                    deterministic=int(deterministic),
                     sync_after_launch=int(sync), window_left=int(window[0]), window_right=int(window[1]))
     need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
     if need == 0:
@@ -82,12 +95,14 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
     return (dq, dk, dv, delta) if return_delta else (dq, dk, dv)
 
 
-def fa3_fwd(q, k, v, causal: bool, softmax_scale=None, layout: str = "bhsd", window=(-1, -1), sync=False):
+def fa3_fwd(q, k, v, causal: bool, softmax_scale=None, layout: str = "bhsd", window=(-1, -1), sync=False,
+            seqused_q=None, seqused_k=None):
     """out, softmax_lse = forward of softmax(q k^T * scale) v (shaobo_fa3_b200_fwd).  Shapes, layouts,
     masks as in fa3_bwd; softmax_lse is fp32 [B,Hq,Sq] natural log."""
     _require_cuda(q, k, v)
     lib = capi.load()
-    p = make_params(q, k, causal, softmax_scale, layout=layout, sync_after_launch=int(sync),
+    p = make_params(q, k, causal, softmax_scale, layout=layout, seqused_q=seqused_q, seqused_k=seqused_k,
+                    sync_after_launch=int(sync),
                     window_left=int(window[0]), window_right=int(window[1]))
     out = torch.empty_like(q)
     lse = torch.empty((p.batch, p.num_heads_q, p.seqlen_q), dtype=torch.float32, device=q.device)

@@ -194,9 +194,12 @@ size_t shaobo_fa3_bwd_v2_workspace_bytes(const ShaoboFa3Params* params);
  *    offsets): packed sequences.  q, out, dout, dq are [total_q, Hq, D], k, v,
  *    dk, dv are [total_k, Hkv, D], softmax_lse and softmax_d are [Hq, total_q];
  *    batch is the number of sequences; max_seqlen_q/k, total_q/k must be set
- *    and seqlen_q/k hold the maxima; layout is ignored; seqused_q/k must be
- *    NULL.  Rows of dq/dk/dv outside every sequence are not part of the
- *    contract. */
+ *    and seqlen_q/k hold the maxima; layout is ignored.  Rows of dq/dk/dv
+ *    outside every sequence are not part of the contract.
+ *  - seqused_q / seqused_k non-NULL (device arrays of batch int32): only the
+ *    first seqused[b] rows of batch entry b take part (with fixed-length
+ *    batches and with packed sequences); the rows of dq/dk/dv behind them, up
+ *    to the end of the entry, are written as zero. */
 int shaobo_fa3_bwd_v2(const void* dout,
                       const void* q,
                       const void* k,

@@ -97,6 +97,40 @@ def test_varlen_validation():
                 max_seqlen_k=128, total_q=128, total_k=128)
     ok = capi.new_params(**base)
     assert lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(ok)) == capi.STATUS_SUCCESS
-    for broken in (dict(cu_seqlens_k=None), dict(max_seqlen_q=0), dict(total_k=0), dict(seqused_q=cu.data_ptr())):
+    for broken in (dict(cu_seqlens_k=None), dict(max_seqlen_q=0), dict(total_k=0)):
         p = capi.new_params(**{**base, **broken})
         assert lib.shaobo_fa3_bwd_v2_validate(ctypes.byref(p)) == capi.STATUS_UNSUPPORTED, broken
+
+
+@pytest.mark.parametrize("deterministic", [False, True])
+@pytest.mark.parametrize("layout", ["bhsd", "bshd"])
+def test_seqused_lengths(deterministic, layout):
+    """Fixed-length slots of which only the first seqused[b] rows take part: every batch entry equals
+    the oracle on the truncated sequences, rows behind the used length get zero gradients, and the
+    forward writes out = 0 / lse = -inf there."""
+    b, hq, hkv, s, d, dtype = 3, 4, 2, 384, 64, "bf16"
+    used_q, used_k = [100, 384, 257], [384, 200, 129]
+    q, k, v, do = golden.seeded_inputs(31, b, hq, hkv, s, d, dtype)
+    refs = [golden.backward(q[i:i + 1, :, :used_q[i]], k[i:i + 1, :, :used_k[i]], v[i:i + 1, :, :used_k[i]],
+                            do[i:i + 1, :, :used_q[i]], True, 1.0 / np.sqrt(d), dtype) for i in range(b)]
+    to_dev = lambda x: dev(np.ascontiguousarray(x.transpose(0, 2, 1, 3)) if layout == "bshd" else x, dtype)
+    back = lambda t: host(t).transpose(0, 2, 1, 3) if layout == "bshd" else host(t)
+    sq = torch.tensor(used_q, dtype=torch.int32, device="cuda")
+    sk = torch.tensor(used_k, dtype=torch.int32, device="cuda")
+    tq, tk, tv, tdo = to_dev(q), to_dev(k), to_dev(v), to_dev(do)
+    out, lse = ops.fa3_fwd(tq, tk, tv, True, layout=layout, seqused_q=sq, seqused_k=sk, sync=True)
+    dq, dk, dv = ops.fa3_bwd(tdo, tq, tk, tv, out, lse, True, deterministic=deterministic, layout=layout,
+                             seqused_q=sq, seqused_k=sk, sync=True)
+    out_h, lse_h, dq, dk, dv = back(out), host(lse), back(dq), back(dk), back(dv)
+    for i, ref in enumerate(refs):
+        uq, uk = used_q[i], used_k[i]
+        assert golden.check_gradient(out_h[i:i + 1, :, :uq], ref["out"], dtype)["pass"], (i, "out")
+        got_lse, ref_lse = lse_h[i:i + 1, :, :uq], ref["lse"]
+        assert (np.isneginf(got_lse) == np.isneginf(ref_lse)).all(), (i, "lse -inf pattern")
+        finite = np.isfinite(ref_lse)
+        assert np.abs(got_lse[finite] - ref_lse[finite]).max() <= 2e-3, (i, "lse")
+        assert (out_h[i, :, uq:] == 0).all() and np.isneginf(lse_h[i, :, uq:]).all(), (i, "forward tail")
+        assert golden.check_gradient(dq[i:i + 1, :, :uq], ref["dq"], dtype)["pass"], (i, "dq")
+        assert golden.check_gradient(dk[i:i + 1, :, :uk], ref["dk"], dtype)["pass"], (i, "dk")
+        assert golden.check_gradient(dv[i:i + 1, :, :uk], ref["dv"], dtype)["pass"], (i, "dv")
+        assert (dq[i, :, uq:] == 0).all() and (dk[i, :, uk:] == 0).all() and (dv[i, :, uk:] == 0).all(), (i, "tails")
