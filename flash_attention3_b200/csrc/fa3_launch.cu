@@ -322,25 +322,45 @@ int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtens
 // dkv_accum non-null (fused path only): key tiles are split as split_plan(p) says and their
 // dK/dV partial sums are reduce-added into dkv_accum ([dK | dV], fp32, already zero) instead of
 // being written to dk / dv.
-int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
-                 const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
-                 bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr, bool pdl = false) {
+// Everything the launch of the five-GEMM / dK-dV kernel needs, built on the host ahead of time: the
+// v2 entry prepares it before it launches the delta kernel, so that the GPU does not sit idle
+// between the two launches while the host encodes seven tensor maps.
+struct FusedLaunch {
+    int status = SHAOBO_FA3_STATUS_SUCCESS;
+    CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
+    FusedArgs args;
+    int blocks = 0;
+    bool with_dq = false;
+    bool dkv_f32 = false;
+};
+
+FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
+                          const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
+                          bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr) {
+    FusedLaunch L;
+    L.with_dq = with_dq;
+    L.dkv_f32 = dkv_f32;
+    CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq, &mdk = L.mdk, &mdv = L.mdv;
+    FusedArgs& args = L.args;
+    auto fail = [&](int status) {
+        L.status = status;
+        return L;
+    };
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const int d = p->head_dim_qk;
     const TensorShape shape = shape_of(p);
     const bool bshd = shape.bshd;
     const int64_t kv_heads_total = int64_t(shape.batch) * p->num_heads_kv;
-    CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
     if (!make_map_16(&mq, type, q, shape.batch, p->num_heads_q, shape.rows_q, d, bshd) ||
         !make_map_16(&mk, type, k, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd) ||
         !make_map_16(&mv, type, v, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd) ||
         !make_map_16(&mdo, type, dout, shape.batch, p->num_heads_q, shape.rows_q, d, bshd)) {
-        return SHAOBO_FA3_STATUS_HIP_ERROR;
+        return fail(SHAOBO_FA3_STATUS_HIP_ERROR);
     }
     if (with_dq) {
         if (!make_map_accum(&mdq, dq_accum, int64_t(shape.batch) * p->num_heads_q, shape.rows_q, d)) {
-            return SHAOBO_FA3_STATUS_HIP_ERROR;
+            return fail(SHAOBO_FA3_STATUS_HIP_ERROR);
         }
     } else {
         mdq = mq;  // unused by the kernel
@@ -350,7 +370,7 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
         const int64_t kv_elems = kv_heads_total * shape.rows_k * d;
         if (!make_map_accum(&mdk, dkv_accum, kv_heads_total, shape.rows_k, d) ||
             !make_map_accum(&mdv, dkv_accum + kv_elems, kv_heads_total, shape.rows_k, d)) {
-            return SHAOBO_FA3_STATUS_HIP_ERROR;
+            return fail(SHAOBO_FA3_STATUS_HIP_ERROR);
         }
     } else {
         mdk = mq;  // unused by the kernel
@@ -365,7 +385,6 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     const long long dq_bytes_per_head =
         with_dq ? (long long)group * plan_seqlen_q(p) * p->head_dim_qk * 4 : 0;
     const CtaOrderPlan plan = cached_plan(work, bh, group, sm_count(), dq_bytes_per_head);
-    FusedArgs args;
     args.sidecar = sidecar;
     args.dk = dk;
     args.dv = dv;
@@ -388,18 +407,33 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
     args.chunk_steps = split.chunk_steps;
     args.chunks_per_head = split.chunks_per_head;
     const int64_t blocks64 = split.chunk_steps > 0 ? int64_t(split.chunks_per_head) * bh : int64_t(n_tiles) * bh;
-    if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
-    const int blocks = int(blocks64);
-    if (with_dq) {
+    if (blocks64 > 0x7fffffffLL) return fail(SHAOBO_FA3_STATUS_UNSUPPORTED);
+    L.blocks = int(blocks64);
+    return L;
+}
+
+int run_fused(const ShaoboFa3Params* p, const FusedLaunch& L, bool pdl) {
+    if (L.status != SHAOBO_FA3_STATUS_SUCCESS) return L.status;
+    const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
+    const CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq, &mdk = L.mdk, &mdv = L.mdv;
+    const FusedArgs& args = L.args;
+    const int blocks = L.blocks;
+    if (L.with_dq) {
         return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
                   : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
     }
-    if (dkv_f32) {
+    if (L.dkv_f32) {
         return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
                   : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
     }
     return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
               : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
+}
+
+int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
+                 const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
+                 bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr, bool pdl = false) {
+    return run_fused(p, prepare_fused(p, dout, q, k, v, sidecar, dq_accum, dk, dv, with_dq, dkv_f32, dkv_accum), pdl);
 }
 
 // -------------------------------------------------------------- dQ kernel
@@ -746,14 +780,17 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
     if (launch.deterministic == 0) {
         // delta + sidecar, and the dQ accumulator is cleared in the same pass
         cudaStream_t st = stream_of(&launch);
-        stage_mark(0, st);
         float* dkv_accum = ws.dkv_accum_bytes != 0
                                ? reinterpret_cast<float*>(base + ws.dq_accum_bytes)
                                : nullptr;
+        // host work of the second launch first, then the three launches back to back
+        const FusedLaunch fused = prepare_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true, false, dkv_accum);
+        if (fused.status != SHAOBO_FA3_STATUS_SUCCESS) return fused.status;
+        stage_mark(0, st);
         launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
                      sidecar, accum, true, dkv_accum, int64_t(ws.dkv_accum_bytes));
         stage_mark(1, st);
-        status = launch_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true, false, dkv_accum, true);
+        status = run_fused(&launch, fused, true);
         stage_mark(2, st);
         if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq, dkv_accum, dk, dv);
         stage_mark(3, st);
