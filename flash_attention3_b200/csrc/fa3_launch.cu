@@ -172,6 +172,22 @@ void stage_mark(int i, cudaStream_t st) {
     }
 }
 
+// An entry point that launches calls begin() first.  The runtime keeps one "last error" per host
+// thread, and an error another library left there (a not-ready event query, for one) must not be
+// reported as a failure of this call by finish().
+// The first call on a host thread also makes a runtime call that needs the device context, which
+// binds the primary context to the thread: tensor maps are encoded through the driver API before
+// anything is launched, and the driver API only works on a thread that has a current context (a
+// thread started by another library, an autograd worker for one, may not have made one yet).
+void begin() {
+    thread_local bool context_bound = false;
+    if (!context_bound) {
+        (void)cudaStreamQuery(nullptr);
+        context_bound = true;
+    }
+    (void)cudaGetLastError();
+}
+
 int finish(const ShaoboFa3Params* p, bool sync) {
     if (cudaGetLastError() != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
     if (sync && cudaStreamSynchronize(stream_of(p)) != cudaSuccess) {
@@ -656,6 +672,7 @@ extern "C" int shaobo_fa3_b200_debug_dump(float* host_out) {
 extern "C" int shaobo_fa3_bwd_dot_do_o(const void* dout, const void* out, const void* aux0,
                                        const void* aux1, void* delta, void* packed_sidecar,
                                        const ShaoboFa3Params* params) {
+    begin();
     const bool ok = params != nullptr && params->batch > 0 && params->seqlen_q > 0 &&
                     params->num_heads_q > 0 && head_dim_supported(params->head_dim_qk) &&
                     params->head_dim_v == params->head_dim_qk && dtype_supported(params->dtype) &&
@@ -677,6 +694,7 @@ extern "C" int shaobo_fa3_bwd_dot_do_o(const void* dout, const void* out, const 
 extern "C" int shaobo_fa3_bwd_fused5(const void* dout, const void* q, const void* k,
                                      const void* v, const void* packed_sidecar, void* dq, void* dk,
                                      void* dv, const ShaoboFa3Params* params) {
+    begin();
     if (params == nullptr || dout == nullptr || q == nullptr || k == nullptr || v == nullptr ||
         packed_sidecar == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) {
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
@@ -705,6 +723,7 @@ extern "C" int shaobo_fa3_bwd_fused5(const void* dout, const void* q, const void
 extern "C" int shaobo_fa3_bwd_dkv(const void* dout, const void* q, const void* k, const void* v,
                                   const void* out, const void* aux0, const void* aux1, void* dq,
                                   void* dk, void* dv, const ShaoboFa3Params* params) {
+    begin();
     (void)out; (void)aux0; (void)aux1; (void)dq;
     if (params == nullptr) return SHAOBO_FA3_STATUS_INVALID_VALUE;
     if (params->dkv_path == SHAOBO_FA3_DKV_PATH_REFERENCE) return SHAOBO_FA3_STATUS_NOT_IMPLEMENTED;
@@ -731,6 +750,7 @@ extern "C" int shaobo_fa3_bwd(const void* dout, const void* q, const void* k, co
 extern "C" int shaobo_fa3_bwd_dq(const void* dout, const void* q, const void* k, const void* v,
                                  const void* out, const void* aux0, const void* aux1, void* dq,
                                  void* dk, void* dv, const ShaoboFa3Params* params) {
+    begin();
     (void)out; (void)dk; (void)dv; (void)aux0; (void)aux1;
     if (params == nullptr) return SHAOBO_FA3_STATUS_INVALID_VALUE;
     if (params->dq_path == SHAOBO_FA3_DQ_PATH_REFERENCE) return SHAOBO_FA3_STATUS_NOT_IMPLEMENTED;
@@ -754,6 +774,7 @@ extern "C" int shaobo_fa3_bwd_dq(const void* dout, const void* q, const void* k,
 extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k, const void* v,
                                  const void* out, const void* softmax_lse, void* dq, void* dk,
                                  void* dv, void* softmax_d, const ShaoboFa3Params* params) {
+    begin();
     const int validation = validate_v2(params);
     if (validation != SHAOBO_FA3_STATUS_SUCCESS) return validation;
     if (dout == nullptr || q == nullptr || k == nullptr || v == nullptr || out == nullptr ||
@@ -819,6 +840,7 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
 // workspace.
 extern "C" int shaobo_fa3_b200_fwd(const void* q, const void* k, const void* v, void* out,
                                    void* softmax_lse, const ShaoboFa3Params* params) {
+    begin();
     const int validation = validate_v2(params);
     if (validation != SHAOBO_FA3_STATUS_SUCCESS) return validation;
     if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || softmax_lse == nullptr) {

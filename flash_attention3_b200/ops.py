@@ -61,7 +61,7 @@ def _require_cuda(*tensors):
 
 def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, deterministic=False,
             workspace=None, return_delta=False, sync=False, layout: str = "bhsd", window=(-1, -1),
-            seqused_q=None, seqused_k=None):
+            seqused_q=None, seqused_k=None, outputs=None):
     """dq, dk, dv (and delta) = backward of softmax(q k^T * scale) v.
 
     layout "bhsd": q, out, dout [B,Hq,Sq,D]; k, v [B,Hkv,Sk,D].  layout "bshd": [B,Sq,Hq,D] and
@@ -69,7 +69,8 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
     causal=True and Sq != Sk the diagonal is aligned bottom-right.  window = (left, right): query i
     sees keys i+off-left .. i+off+right (off = Sk - Sq), -1 = unbounded; causal forces right = 0.
     seqused_q / seqused_k (int32 [B]): only the first seqused[b] rows of batch entry b take part; the
-    gradient rows behind them are zero.  Calls shaobo_fa3_bwd_v2.
+    gradient rows behind them are zero.  outputs = (dq, dk, dv): write into these tensors instead of
+    allocating.  Calls shaobo_fa3_bwd_v2.
     """
     _require_cuda(dout, q, k, v, out, softmax_lse)
     lib = capi.load()
@@ -83,7 +84,11 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
         workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
     p.workspace = workspace.data_ptr()
     p.workspace_bytes = workspace.numel() * workspace.element_size()
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if outputs is None:
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    else:
+        dq, dk, dv = outputs
+        _require_cuda(dq, dk, dv)
     delta = (torch.empty((p.batch, p.num_heads_q, p.seqlen_q), dtype=torch.float32, device=q.device)
              if return_delta else None)
     with torch.cuda.device(q.device):
@@ -176,6 +181,91 @@ def fa3_bwd_varlen(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, 
     if code != capi.STATUS_SUCCESS:
         raise Fa3Error("shaobo_fa3_bwd_v2", code)
     return (dq, dk, dv, delta) if return_delta else (dq, dk, dv)
+
+
+class HostBackward:
+    """The backward for callers whose tensors live in host memory ([B,H,S,D], pinned for full speed).
+
+    A call copies the inputs to the GPU, runs shaobo_fa3_bwd_v2 and copies dq, dk, dv back.  Large
+    problems are cut into contiguous (batch, KV head) shards (the backward has no reduction across
+    them) that go round-robin over a few CUDA streams, so that the host-to-device copy of one shard,
+    the kernels of another and the device-to-host copy of a third overlap: over PCIe the copies, not
+    the kernels, bound such a call.  Device staging tensors, workspaces and the parameter blocks of
+    every shard are built once, here; a call itself only issues copies and launches.
+    """
+
+    def __init__(self, batch, heads_q, heads_kv, seqlen, head_dim, dtype, causal, softmax_scale=None,
+                 shards=None, streams=3, device="cuda"):
+        from . import sharding
+        self.group = heads_q // heads_kv
+        units = batch * heads_kv
+        if shards is None:
+            # a shard per ~16 MB of traffic: below that the per-shard host work (copies, launches)
+            # costs more than the overlap gains
+            elem = torch.empty((), dtype=dtype).element_size()
+            total = (5 * batch * heads_q + 4 * batch * heads_kv) * seqlen * head_dim * elem
+            shards = max(1, min(8, total // (16 << 20)))
+        n = max(1, min(int(shards), units))
+        self.shards = [sh for part in sharding.plan(batch, heads_kv, n) for sh in part]
+        self._slice = sharding.slice_tensors
+        mk = lambda *shape, dt=dtype: torch.empty(shape, dtype=dt, device=device)
+        q_shape, kv_shape = (batch, heads_q, seqlen, head_dim), (batch, heads_kv, seqlen, head_dim)
+        self.q, self.dout, self.out, self.dq = mk(*q_shape), mk(*q_shape), mk(*q_shape), mk(*q_shape)
+        self.k, self.v, self.dk, self.dv = mk(*kv_shape), mk(*kv_shape), mk(*kv_shape), mk(*kv_shape)
+        self.lse = mk(batch, heads_q, seqlen, dt=torch.float32)
+        self.streams = [torch.cuda.Stream(device=device) for _ in range(max(1, min(streams, len(self.shards))))]
+        self.lib = capi.load()
+        # per shard: device views, parameter block (workspace and stream filled in), C arguments
+        self.plans = []
+        need = 0
+        for i, sh in enumerate(self.shards):
+            d_q, d_kv, d_row = self._slice(sh, self.group, [self.q, self.dout, self.out, self.dq],
+                                           [self.k, self.v, self.dk, self.dv], [self.lse])
+            p = make_params(d_q[0], d_kv[0], causal, softmax_scale)
+            need = max(need, self.lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p)))
+            self.plans.append((sh, d_q, d_kv, d_row, p))
+        if need == 0:
+            raise Fa3Error("shaobo_fa3_bwd_v2_validate", capi.STATUS_UNSUPPORTED)
+        self.workspaces = [torch.empty(need, dtype=torch.uint8, device=device) for _ in self.streams]
+        self.calls = []
+        for i, (sh, d_q, d_kv, d_row, p) in enumerate(self.plans):
+            lane = i % len(self.streams)
+            p.workspace, p.workspace_bytes = self.workspaces[lane].data_ptr(), need
+            p.reserved_ptr[capi.RESERVED_PTR_STREAM] = self.streams[lane].cuda_stream
+            args = tuple(_ptr(t) for t in (d_q[1], d_q[0], d_kv[0], d_kv[1], d_q[2], d_row[0], d_q[3], d_kv[2], d_kv[3]))
+            self.calls.append(args + (None, ctypes.byref(p)))
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in (self.q, self.k, self.v, self.dout, self.out, self.lse))
+        self.d2h_bytes = sum(t.numel() * t.element_size() for t in (self.dq, self.dk, self.dv))
+
+    def __call__(self, dout, q, k, v, out, softmax_lse, dq, dk, dv):
+        """All nine arguments are host tensors; dq, dk, dv are written.  Returns when the work has been
+        queued: the caller's current stream waits for it (synchronise that stream before reading)."""
+        main = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(main)
+        whole = len(self.plans) == 1
+        for i, (sh, d_q, d_kv, d_row, _) in enumerate(self.plans):
+            st = self.streams[i % len(self.streams)]
+            st.wait_event(start)
+            if whole:
+                h_q, h_kv, h_row = [q, dout, out, dq], [k, v, dk, dv], [softmax_lse]
+            else:
+                h_q, h_kv, h_row = self._slice(sh, self.group, [q, dout, out, dq], [k, v, dk, dv], [softmax_lse])
+            with torch.cuda.stream(st):
+                d_q[0].copy_(h_q[0], non_blocking=True)
+                d_kv[0].copy_(h_kv[0], non_blocking=True)
+                d_kv[1].copy_(h_kv[1], non_blocking=True)
+                d_q[1].copy_(h_q[1], non_blocking=True)
+                d_q[2].copy_(h_q[2], non_blocking=True)
+                d_row[0].copy_(h_row[0], non_blocking=True)
+                code = self.lib.shaobo_fa3_bwd_v2(*self.calls[i])
+                if code != capi.STATUS_SUCCESS:
+                    raise Fa3Error("shaobo_fa3_bwd_v2", code)
+                h_q[3].copy_(d_q[3], non_blocking=True)
+                h_kv[2].copy_(d_kv[2], non_blocking=True)
+                h_kv[3].copy_(d_kv[3], non_blocking=True)
+        for st in self.streams:
+            main.wait_stream(st)
 
 
 def default_scale(d: int) -> float:

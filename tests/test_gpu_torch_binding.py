@@ -38,3 +38,23 @@ def test_custom_op_is_registered_with_a_fake_implementation():
     torch.library.opcheck(torch.ops.fa3b200.attention_bwd,
                           (x["dout"], x["q"], x["k"], x["v"], x["out"], x["lse"], False, prob.scale, True),
                           test_utils=("test_schema", "test_faketensor"))
+
+
+def test_host_tensor_call_matches_the_oracle():
+    """ops.HostBackward: pinned host tensors in and out, shards pipelined over streams."""
+    from flash_attention3_b200 import ops
+    prob = helpers.Problem(2, 4, 2, 384, 64, "bf16", True, seed=303)
+    td = helpers.TORCH_DTYPE["bf16"]
+    pin = lambda x, dt=td: torch.from_numpy(np.ascontiguousarray(x)).to(dt).pin_memory()
+    q, k, v, do, out = (pin(x) for x in (prob.q, prob.k, prob.v, prob.do, prob.ref["out"]))
+    lse = pin(prob.ref["lse"], torch.float32)
+    dq, dk, dv = torch.empty_like(q).pin_memory(), torch.empty_like(k).pin_memory(), torch.empty_like(v).pin_memory()
+    for shards in (1, 3, None):
+        call = ops.HostBackward(2, 4, 2, 384, 64, td, True, softmax_scale=prob.scale, shards=shards)
+        for t in (dq, dk, dv):
+            t.fill_(float("nan"))
+        call(do, q, k, v, out, lse, dq, dk, dv)
+        torch.cuda.synchronize()
+        for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+            m = golden.check_gradient(t.float().numpy(), prob.ref[name], "bf16")
+            assert m["pass"], (shards, name, m)
