@@ -130,3 +130,52 @@ def test_lse_identity():
     p2 = np.exp(s - r.lse[:, None])
     p2[np.triu(np.ones_like(p2, dtype=bool), 1)] = 0
     np.testing.assert_allclose(p2, prob, rtol=2e-5, atol=1e-7)
+
+
+# The reference's golden only covers seqlen_q == seqlen_k with a causal or full mask.  For the shapes
+# and masks accepted beyond that, the oracle is checked against an independent float64 evaluation of
+# the textbook formulas (softmax attention and its gradient), written without the oracle's helpers.
+def _textbook_backward(q, k, v, do, scale, visible):
+    s = (q @ k.T) * scale
+    s = np.where(visible, s, -np.inf)
+    m = np.max(s, axis=1, keepdims=True)
+    m = np.where(np.isfinite(m), m, 0.0)
+    e = np.where(visible, np.exp(s - m), 0.0)
+    z = e.sum(axis=1, keepdims=True)
+    p = np.where(z > 0, e / np.where(z > 0, z, 1.0), 0.0)
+    o = p @ v
+    dp = do @ v.T
+    delta = (do * o).sum(axis=1, keepdims=True)
+    ds = p * (dp - delta) * scale
+    with np.errstate(divide="ignore"):
+        lse = np.where(z[:, 0] > 0, m[:, 0] + np.log(np.where(z[:, 0] > 0, z[:, 0], 1.0)), -np.inf)
+    return o, lse, ds @ k, ds.T @ q, p.T @ do
+
+
+@pytest.mark.parametrize("sq,sk,causal,window", [
+    (9, 9, True, (-1, -1)), (5, 9, True, (-1, -1)), (9, 5, True, (-1, -1)), (7, 11, False, (-1, -1)),
+    (12, 12, True, (3, -1)), (12, 12, False, (2, 4)), (6, 14, False, (0, 5)), (14, 6, True, (4, -1)),
+])
+def test_oracle_matches_textbook_float64_on_widened_masks(sq, sk, causal, window):
+    d, scale = 8, 0.37
+    q, k, v, do = golden.seeded_inputs(99, 1, 1, 1, sq, d, "fp16", sk=sk)
+    got = golden.backward(q, k, v, do, causal, scale, "fp16", window)
+    i = np.arange(sq)[:, None]
+    j = np.arange(sk)[None, :]
+    off = sk - sq
+    left, right = window
+    if causal:
+        right = 0
+    visible = np.ones((sq, sk), bool)
+    if right >= 0:
+        visible &= j <= i + off + right
+    if left >= 0:
+        visible &= j >= i + off - left
+    o, lse, dq, dk, dv = _textbook_backward(*(x[0, 0].astype(np.float64) for x in (q, k, v, do)), scale, visible)
+    # the oracle rounds O to the storage dtype before delta (as the reference does): fp16 spacing
+    assert np.abs(got["out"][0, 0] - o).max() < 2e-3
+    finite = np.isfinite(lse)
+    assert (np.isneginf(got["lse"][0, 0]) == ~finite).all()
+    assert np.abs(got["lse"][0, 0][finite] - lse[finite]).max() < 1e-5
+    for name, ref in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert np.abs(got[name][0, 0] - ref).max() < 2e-3, name
