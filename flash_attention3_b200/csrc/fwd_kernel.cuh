@@ -69,6 +69,12 @@ struct FwdCfg {
     static constexpr int kColO = 256;   // + D per query tile
     static_assert(kColO + 2 * D <= kTmemCols, "tensor-memory ledger exceeds 512 columns");
     static constexpr float kRescaleThreshold = 8.0f;  // log2 units
+    // setmaxnreg split: the kernel starts with 168 registers per thread (384 threads); the producer /
+    // MMA warpgroup gives most of its share to the two softmax warpgroups, which hold a whole score
+    // row (128 values) in registers
+    static constexpr int kRegsControl = 64;
+    static constexpr int kRegsSoftmax = 216;
+    static_assert(kRegsControl + 2 * kRegsSoftmax <= 504, "more registers than the CTA was launched with (168 x 384)");
 };
 
 enum FwdBar : int {
@@ -170,8 +176,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (!misaligned) {
-        if (warp == 0) {
+    // (each role changes its register budget at the top of its own branch, where the compiler can see
+    // which code runs under which budget)
+    if (warp < 4) {
+        ptx::setmaxnreg_dec<C::kRegsControl>();
+        if (misaligned) {
+            // nothing to do
+        } else if (warp == 0) {
             if (lane == 0 && n_iter > 0) {
                 ptx::prefetch_tensormap(&tm_q);
                 ptx::prefetch_tensormap(&tm_k);
@@ -283,7 +294,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 if (more) ptx::tc_commit_elect(bar(kFwdKEmpty + ((it + 1) & 1)));
                 ptx::tc_commit_elect(bar(kFwdVEmpty + (it & 1)));
             }
-        } else if (warp >= 4) {
+        }
+    } else {
+        ptx::setmaxnreg_inc<C::kRegsSoftmax>();
+        if (!misaligned) {
             const int x = (warp - 4) >> 2;      // which query tile
             const int i = threadIdx.x & 127;    // query row inside the tile == TMEM lane
             const int qt = 2 * pair + x;
@@ -305,22 +319,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 const bool diagonal = kMasked && tile_needs_mask(k_begin + u, qt, band);
                 int mask_from = 0, mask_to = 0;
                 if (diagonal) key_range_of_query(qi, (k_begin + u) * C::kTile, band, &mask_from, &mask_to);
-                // ---- pass 1: row maximum of this tile
-                float mt = -INFINITY;
+                // ---- the whole score row of this tile goes to registers in one round trip
+                uint32_t r[4][32];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    ptx::tmem_ld32(s_cols + c * 32, r);
-                    ptx::tmem_ld_wait();
-                    if (diagonal) {
+                for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_cols + c * 32, r[c]);
+                ptx::tmem_ld_wait();
+                float mt = -INFINITY;
+                if (diagonal) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
 #pragma unroll
                         for (int e = 0; e < 32; ++e) {
                             const int j = c * 32 + e;
-                            if (j >= mask_from && j <= mask_to) mt = fmaxf(mt, __uint_as_float(r[e]));
+                            if (j >= mask_from && j <= mask_to) mt = fmaxf(mt, __uint_as_float(r[c][e]));
                         }
-                    } else {
+                    }
+                } else {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) mt = fmaxf(mt, __uint_as_float(r[e]));
+                    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) mt = fmaxf(mt, __uint_as_float(r[c][e]));
                     }
                 }
                 // ---- move the reference maximum only when it is more than 2^8 too small
@@ -335,30 +353,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     // O carries the old reference: wait for P V of step u-1, then rescale these 32 rows
                     if (!(ok = warp_wait(bar(kFwdPvDone + x), (u - 1) & 1, abort_flag))) break;
                     ptx::tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t r[32];
-                        ptx::tmem_ld32(o_cols + c * 32, r);
+                    // (16 columns at a time: the score row is still held in registers)
+#pragma unroll 1
+                    for (int c = 0; c < D / 16; ++c) {
+                        uint32_t acc[16];
+                        ptx::tmem_ld16(o_cols + c * 16, acc);
                         ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-                        ptx::tmem_st32(o_cols + c * 32, r);
+                        for (int e = 0; e < 16; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+                        ptx::tmem_st16(o_cols + c * 16, acc);
                     }
                     ptx::tmem_st_wait();
                 }
-                // ---- pass 2: P = exp2((S - m_ref) * scale_log2), written over S as 16-bit pairs
+                // ---- P = exp2((S - m_ref) * scale_log2), written over S as 16-bit pairs (every column of
+                // S has been read by now)
                 const float neg = m_ref == -INFINITY ? 0.0f : -m_ref * a.scale_log2;
                 float sum = 0.0f;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    ptx::tmem_ld32(s_cols + c * 32, r);
-                    ptx::tmem_ld_wait();
                     uint32_t o[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
-                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, neg));
-                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, neg));
+                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[c][e + 0]), a.scale_log2, neg));
+                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[c][e + 1]), a.scale_log2, neg));
                         if (diagonal) {
                             const int j = c * 32 + e;
                             p0 = (j + 0 >= mask_from && j + 0 <= mask_to) ? p0 : 0.0f;
@@ -367,8 +384,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                         sum += p0 + p1;
                         o[e / 2] = ptx::Pack2<T>::pack(p0, p1);
                     }
-                    // P chunk c lands on columns [16c, 16c+16) of the S region, all of which were read by
-                    // chunk loads <= c
                     ptx::tmem_st16(s_cols + c * 16, o);
                 }
                 l += sum;
