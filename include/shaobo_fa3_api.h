@@ -199,7 +199,12 @@ size_t shaobo_fa3_bwd_v2_workspace_bytes(const ShaoboFa3Params* params);
  *  - seqused_q / seqused_k non-NULL (device arrays of batch int32): only the
  *    first seqused[b] rows of batch entry b take part (with fixed-length
  *    batches and with packed sequences); the rows of dq/dk/dv behind them, up
- *    to the end of the entry, are written as zero. */
+ *    to the end of the entry, are written as zero.
+ *
+ * The call only enqueues work on the stream (params->reserved_ptr[7], NULL =
+ * default stream) unless sync_after_launch is set.  The first call on a host
+ * thread, and the first call that uses a given kernel variant on a device, do
+ * one-time set-up through the runtime: make them outside stream capture. */
 int shaobo_fa3_bwd_v2(const void* dout,
                       const void* q,
                       const void* k,

@@ -58,3 +58,32 @@ def test_host_tensor_call_matches_the_oracle():
         for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
             m = golden.check_gradient(t.float().numpy(), prob.ref[name], "bf16")
             assert m["pass"], (shards, name, m)
+
+
+def test_calls_from_a_fresh_host_thread():
+    """The first CUDA-related thing a new host thread does may be a call into the library (an autograd
+    worker, for one): forward and backward must work there as on the main thread."""
+    import threading
+    from flash_attention3_b200 import ops
+    prob = helpers.Problem(1, 4, 2, 256, 64, "bf16", True, seed=304)
+    x = prob.device_inputs()
+    results = {}
+
+    def work(tag):
+        try:
+            out, lse = ops.fa3_fwd(x["q"], x["k"], x["v"], True, prob.scale, sync=True)
+            dq, _, _ = ops.fa3_bwd(x["dout"], x["q"], x["k"], x["v"], out, lse, True, prob.scale,
+                                   deterministic=True, sync=True)
+            results[tag] = helpers.host(dq)
+        except Exception as exc:  # reported by the assertion below
+            results[tag] = exc
+
+    for tag in ("first", "second"):
+        t = threading.Thread(target=work, args=(tag,))
+        t.start()
+        t.join()
+    work("main")
+    for tag in ("first", "second", "main"):
+        assert isinstance(results[tag], np.ndarray), (tag, results[tag])
+    assert np.array_equal(results["first"], results["main"]) and np.array_equal(results["second"], results["main"])
+    assert golden.check_gradient(results["main"], prob.ref["dq"], "bf16")["pass"]
