@@ -265,7 +265,7 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
         seg.count = 3;
         total += 2 * (n / 8);
     }
-    int64_t blocks = (total / seg.count + 255) / 256;
+    int64_t blocks = (total + 255) / 256;  // one 8-element vector per thread while the grid allows it
     const int64_t cap = int64_t(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;

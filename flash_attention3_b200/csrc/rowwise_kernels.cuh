@@ -173,17 +173,20 @@ __global__ void __launch_bounds__(256)
 dq_convert_kernel(const ConvertSegments seg) {
     // launched programmatically behind the GEMM kernel: wait until all of it has completed
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // The segments form one index space, so that with enough blocks every thread makes a single
+    // load -> store trip whatever the number of segments (small problems are latency-bound here).
+    const int64_t n0 = seg.n_vec8[0];
+    const int64_t n01 = n0 + (seg.count > 1 ? seg.n_vec8[1] : 0);
+    const int64_t total = n01 + (seg.count > 2 ? seg.n_vec8[2] : 0);
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-#pragma unroll
-    for (int sgi = 0; sgi < 3; ++sgi) {
-    if (sgi >= seg.count) break;
-    const float* __restrict__ accum = seg.src[sgi];
-    T* __restrict__ dq = static_cast<T*>(seg.dst[sgi]);
-    const int64_t n_vec8 = seg.n_vec8[sgi];
-    const float scale = seg.scale[sgi];
-    const RowLayout layout = seg.layout[sgi];
     const int vec_per_row = seg.head_dim / 8;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec8; i += stride) {
+    for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += stride) {
+        // (selects instead of indexing: the parameter arrays stay in constant memory)
+        const int sgi = g < n0 ? 0 : (g < n01 ? 1 : 2);
+        const int64_t i = g - (sgi == 0 ? 0 : (sgi == 1 ? n0 : n01));
+        const float* __restrict__ accum = sgi == 0 ? seg.src[0] : (sgi == 1 ? seg.src[1] : seg.src[2]);
+        T* __restrict__ dst = static_cast<T*>(sgi == 0 ? seg.dst[0] : (sgi == 1 ? seg.dst[1] : seg.dst[2]));
+        const float scale = sgi == 0 ? seg.scale[0] : (sgi == 1 ? seg.scale[1] : seg.scale[2]);
         const uint4 lo = ld_stream_16B(accum + i * 8);
         const uint4 hi = ld_stream_16B(accum + i * 8 + 4);
         uint4 o;
@@ -191,14 +194,16 @@ dq_convert_kernel(const ConvertSegments seg) {
         o.y = pack2<T>(__uint_as_float(lo.z) * scale, __uint_as_float(lo.w) * scale);
         o.z = pack2<T>(__uint_as_float(hi.x) * scale, __uint_as_float(hi.y) * scale);
         o.w = pack2<T>(__uint_as_float(hi.z) * scale, __uint_as_float(hi.w) * scale);
-        if (layout.contiguous) {
-            reinterpret_cast<uint4*>(dq)[i] = o;
+        // (the layout of a call is the same for all its segments up to heads and rows)
+        const bool contiguous = seg.layout[0].contiguous != 0;
+        if (contiguous) {
+            reinterpret_cast<uint4*>(dst)[i] = o;
         } else {
+            const RowLayout layout = sgi == 0 ? seg.layout[0] : (sgi == 1 ? seg.layout[1] : seg.layout[2]);
             const int64_t row = i / vec_per_row;
             const int col = int(i - row * vec_per_row) * 8;
-            *reinterpret_cast<uint4*>(dq + row_offset(layout, row, seg.head_dim) + col) = o;
+            *reinterpret_cast<uint4*>(dst + row_offset(layout, row, seg.head_dim) + col) = o;
         }
-    }
     }
 }
 
