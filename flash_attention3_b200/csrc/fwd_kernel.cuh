@@ -84,9 +84,9 @@ enum FwdBar : int {
     kFwdVFull = 6,    // 2 stages
     kFwdVEmpty = 8,   // 2 stages
     kFwdSFull = 10,   // per query tile
-    kFwdPReady = 12,  // per query tile and half of the keys (tile * 2 + half)
-    kFwdPvDone = 16,  // per query tile
-    kFwdNum = 18,
+    kFwdPReady = 12,  // per query tile
+    kFwdPvDone = 14,  // per query tile
+    kFwdNum = 16,
 };
 
 template <typename T, int D, bool kMasked>
@@ -161,8 +161,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             ptx::mbar_init(bar(kFwdVFull + s), 1);
             ptx::mbar_init(bar(kFwdVEmpty + s), 1);
             ptx::mbar_init(bar(kFwdSFull + s), 1);
-            ptx::mbar_init(bar(kFwdPReady + 2 * s), 128);
-            ptx::mbar_init(bar(kFwdPReady + 2 * s + 1), 128);
+            ptx::mbar_init(bar(kFwdPReady + s), 128);
             ptx::mbar_init(bar(kFwdPvDone + s), 1);
         }
         *abort_flag = 0;
@@ -239,23 +238,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     ptx::mma_ss_lean<true>(dst, loQ + k_step(kk), loK + k_step(kk), kHi, kIdS);
                 ptx::tc_commit_elect(bar(kFwdSFull + x));
             };
-            // P V over keys [64*half, 64*half + 64) of the tile: the softmax hands P over in two halves, so
-            // that the first four MMAs run while it still exponentiates the second half
-            auto issue_pv_half = [&](int x, int it, int half, bool accumulate) {
+            auto issue_pv = [&](int x, int it, bool accumulate) {
                 const uint32_t loV = ptx::desc_lo_mn_major(sbase + C::kOffV + (it & 1) * C::kOperandBytes, C::kBoxBytes);
                 const uint32_t p_cols = tmem + C::kColS + x * 128;
                 const uint32_t o_cols = tmem + C::kColO + x * D;
-                if (half == 0) {
-                    ptx::mma_ts_lean_rt(o_cols, p_cols, loV, kHi, kIdO, accumulate ? 1u : 0u);
+                ptx::mma_ts_lean_rt(o_cols, p_cols, loV, kHi, kIdO, accumulate ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 1; kk < 4; ++kk)
-                        ptx::mma_ts_lean<true>(o_cols, p_cols + kk * 8, loV + mn_step(kk), kHi, kIdO);
-                } else {
-#pragma unroll
-                    for (int kk = 4; kk < 8; ++kk)
-                        ptx::mma_ts_lean<true>(o_cols, p_cols + kk * 8, loV + mn_step(kk), kHi, kIdO);
-                    ptx::tc_commit_elect(bar(kFwdPvDone + x));
-                }
+                for (int kk = 1; kk < 8; ++kk)
+                    ptx::mma_ts_lean<true>(o_cols, p_cols + kk * 8, loV + mn_step(kk), kHi, kIdO);
+                ptx::tc_commit_elect(bar(kFwdPvDone + x));
             };
             bool ok = n_iter > 0;
 #pragma unroll
@@ -280,16 +271,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     if (active(x, t)) {
-                        if (!(ok = warp_wait<false>(bar(kFwdPReady + 2 * x), done[x] & 1, abort_flag))) break;
+                        if (!(ok = warp_wait<false>(bar(kFwdPReady + x), done[x] & 1, abort_flag))) break;
                         if (!v_ready) {
                             if (!(ok = warp_wait<false>(bar(kFwdVFull + (it & 1)), (it >> 1) & 1, abort_flag))) break;
                             v_ready = true;
                         }
                         ptx::tc_fence_after();
-                        issue_pv_half(x, it, 0, done[x] > 0);
-                        if (!(ok = warp_wait<false>(bar(kFwdPReady + 2 * x + 1), done[x] & 1, abort_flag))) break;
-                        ptx::tc_fence_after();
-                        issue_pv_half(x, it, 1, true);
+                        issue_pv(x, it, done[x] > 0);
                         ++done[x];
                     }
                     // S of the next key tile goes over P of this one: it follows P V in the pipe
@@ -397,14 +385,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                         o[e / 2] = ptx::Pack2<T>::pack(p0, p1);
                     }
                     ptx::tmem_st16(s_cols + c * 16, o);
-                    if (c == 1 || c == 3) {
-                        // half of P is in place: hand it to the MMA warp
-                        ptx::tmem_st_wait();
-                        ptx::tc_fence_before();
-                        ptx::mbar_arrive(bar(kFwdPReady + 2 * x + (c >> 1)));
-                    }
                 }
                 l += sum;
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(bar(kFwdPReady + x));
             }
             if (ok && n_steps > 0) ok = warp_wait(bar(kFwdPvDone + x), (n_steps - 1) & 1, abort_flag);
             T* dst = reinterpret_cast<T*>(a.out) + b_coord * a.o_strides.batch + hq * a.o_strides.head +
