@@ -173,7 +173,7 @@ def run_reference_arm(args, cfg, rank, world):
 # GPU arm
 # ----------------------------------------------------------------------------
 class Workload:
-    def __init__(self, cfg, seed, torch, capi, ops, synthetic):
+    def __init__(self, cfg, seed, torch, capi, ops, synthetic, deterministic=False):
         self.torch, self.capi = torch, capi
         b, hq, hkv, s, d, dtype, causal, _ = cfg
         self.cfg = cfg
@@ -182,7 +182,7 @@ class Workload:
         # O and LSE come from the library's own forward (set-up, outside every timed region)
         self.out, self.lse = ops.fa3_fwd(self.q, self.k, self.v, causal, sync=True)
         self.lib = capi.load()
-        self.p = ops.make_params(self.q, self.k, causal)
+        self.p = ops.make_params(self.q, self.k, causal, deterministic=int(deterministic))
         need = self.lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(self.p))
         self.ws = torch.empty(need, dtype=torch.uint8, device="cuda")
         self.p.workspace, self.p.workspace_bytes = self.ws.data_ptr(), need
@@ -313,6 +313,8 @@ def main():
     ap.add_argument("--config", default="C2", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip cpu_baseline, e2e and the 'also' configurations")
+    ap.add_argument("--deterministic", action="store_true",
+                    help="time the atomic-free split path (deterministic=1) instead of the fused path")
     ap.add_argument("--forward-only", action="store_true",
                     help="time the forward kernel alone on --config (one GPU; a profiling aid, not the headline metric)")
     args = ap.parse_args()
@@ -354,7 +356,7 @@ def main():
         mine = sharding.plan(b, hkv, world)[rank]
         assert len(mine) == 1 and mine[0].kv_head_count == hkv, "C5 shards are whole batches"
         cfg = (mine[0].batch_count,) + cfg[1:]
-    wl = Workload(cfg, 1234 + rank, torch, capi, ops, synthetic)
+    wl = Workload(cfg, 1234 + rank, torch, capi, ops, synthetic, deterministic=args.deterministic)
     flush = L2Flush(torch)
 
     def barrier():
@@ -378,16 +380,21 @@ def main():
 
     stage_ms = time_stages(torch, wl, min(args.steps, 20), flush)
     peaks = measured_peaks()
-    achieved = wl.flops / (stage_ms[1] * 1e-3) / 1e12
+    # fused path: stage 1 is the five-GEMM kernel (all the FLOPs); deterministic path: stage 1 is the
+    # four-GEMM dK/dV kernel (8 of the 10 units), stage 2 the three-GEMM dQ kernel
+    stage1_flops = wl.flops * (0.8 if args.deterministic else 1.0)
+    achieved = stage1_flops / (stage_ms[1] * 1e-3) / 1e12
     traffic = None
     tpath = ROOT / "profiles" / "dram_traffic.json"
     if tpath.exists():
         traffic = json.loads(tpath.read_text()).get(args.config, {}).get("fused_bwd_kernel")
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["tflops_burst"], "traffic": traffic,
-                "kernel": "fused_bwd_kernel (S, dP, dV, dK, dQ)", "peak_source": peaks["source"] + " (burst bf16 GEMM)",
-                "kernel_ms": stage_ms[1],
-                "other_kernels_ms": {"delta_sidecar_kernel": stage_ms[0], "dq_convert_kernel": stage_ms[2]}}
+                "kernel": ("fused_bwd_kernel without dQ (S, dP, dV, dK)" if args.deterministic
+                           else "fused_bwd_kernel (S, dP, dV, dK, dQ)"),
+                "peak_source": peaks["source"] + " (burst bf16 GEMM)", "kernel_ms": stage_ms[1],
+                "other_kernels_ms": {"delta_sidecar_kernel": stage_ms[0],
+                                     ("dq_bwd_kernel" if args.deterministic else "dq_convert_kernel"): stage_ms[2]}}
 
     e2e_times, h2d, d2h = time_e2e(torch, wl, max(3, min(args.steps, 20)), 3, flush, ops)
     e2e_ms = sum(e2e_times) / len(e2e_times)
@@ -402,6 +409,7 @@ def main():
         "vs_baseline": None, "dtype": dtype, "data": "synthetic",
         "config": {"workload": desc if strong else desc + " per GPU", "global_batch": b if strong else b * world,
                    "sharding": "batch (no collective)",
+                   "path": "deterministic split path" if args.deterministic else "fused path",
                    "l2": f"flushed before every step ({L2_FLUSH_BYTES >> 20} MiB write + {L2_FLUSH_BYTES >> 20} MiB read, untimed)",
                    "frac_of_measured_peak": value / world / peaks["tflops_burst"],
                    "frac_of_nominal_2250": value / world / 2250.0},
