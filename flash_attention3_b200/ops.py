@@ -200,11 +200,12 @@ class HostBackward:
         self.group = heads_q // heads_kv
         units = batch * heads_kv
         if shards is None:
-            # a shard per ~16 MB of traffic: below that the per-shard host work (copies, launches)
-            # costs more than the overlap gains
+            # a shard per ~8 MB of traffic: below that the per-shard host work (copies, launches)
+            # costs more than the overlap gains (measured on B=1,H=4,S=2048,D=128, 16.8 MB: one shard
+            # 389 us, two 370 us, four 419 us)
             elem = torch.empty((), dtype=dtype).element_size()
             total = (5 * batch * heads_q + 4 * batch * heads_kv) * seqlen * head_dim * elem
-            shards = max(1, min(8, total // (16 << 20)))
+            shards = max(1, min(8, total // (8 << 20)))
         n = max(1, min(int(shards), units))
         self.shards = [sh for part in sharding.plan(batch, heads_kv, n) for sh in part]
         self._slice = sharding.slice_tensors
@@ -234,6 +235,7 @@ class HostBackward:
             p.reserved_ptr[capi.RESERVED_PTR_STREAM] = self.streams[lane].cuda_stream
             args = tuple(_ptr(t) for t in (d_q[1], d_q[0], d_kv[0], d_kv[1], d_q[2], d_row[0], d_q[3], d_kv[2], d_kv[3]))
             self.calls.append(args + (None, ctypes.byref(p)))
+        self._host_key, self._host_views = None, None
         self.h2d_bytes = sum(t.numel() * t.element_size() for t in (self.q, self.k, self.v, self.dout, self.out, self.lse))
         self.d2h_bytes = sum(t.numel() * t.element_size() for t in (self.dq, self.dk, self.dv))
 
@@ -243,14 +245,19 @@ class HostBackward:
         main = torch.cuda.current_stream()
         start = torch.cuda.Event()
         start.record(main)
-        whole = len(self.plans) == 1
+        # the per-shard views of the host tensors are kept for the next call with the same tensors
+        key = tuple(t.data_ptr() for t in (dout, q, k, v, out, softmax_lse, dq, dk, dv))
+        if key != self._host_key:
+            if len(self.plans) == 1:
+                self._host_views = [([q, dout, out, dq], [k, v, dk, dv], [softmax_lse])]
+            else:
+                self._host_views = [self._slice(sh, self.group, [q, dout, out, dq], [k, v, dk, dv], [softmax_lse])
+                                    for sh, *_ in self.plans]
+            self._host_key = key
         for i, (sh, d_q, d_kv, d_row, _) in enumerate(self.plans):
             st = self.streams[i % len(self.streams)]
             st.wait_event(start)
-            if whole:
-                h_q, h_kv, h_row = [q, dout, out, dq], [k, v, dk, dv], [softmax_lse]
-            else:
-                h_q, h_kv, h_row = self._slice(sh, self.group, [q, dout, out, dq], [k, v, dk, dv], [softmax_lse])
+            h_q, h_kv, h_row = self._host_views[i]
             with torch.cuda.stream(st):
                 d_q[0].copy_(h_q[0], non_blocking=True)
                 d_kv[0].copy_(h_kv[0], non_blocking=True)
