@@ -269,14 +269,14 @@ def time_stages(torch, wl, steps, flush):
 
 
 def time_e2e(torch, wl, steps, warmup, flush, ops):
-    """Host buffers in, host buffers out, through the library's host-tensor call (ops.HostBackward):
+    """Host buffers in, host buffers out, through the library's host-tensor call (shaobo_fa3_b200_bwd_v2_host):
     pinned H2D of every input, shaobo_fa3_bwd_v2, D2H of dq/dk/dv, pipelined over (batch, KV head)
     shards.  Every byte crosses PCIe inside the timed region, every step."""
     b, hq, hkv, s, d, dtype, causal, _ = wl.cfg
     dev_in = [wl.q, wl.k, wl.v, wl.do, wl.out, wl.lse]
     hq_, hk_, hv_, hdo_, hout_, hlse_ = [t.cpu().pin_memory() for t in dev_in]
     host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (wl.dq, wl.dk, wl.dv)]
-    call = ops.HostBackward(b, hq, hkv, s, d, wl.q.dtype, causal)
+    call = ops.HostBackwardC(b, hq, hkv, s, d, wl.q.dtype, causal)  # shaobo_fa3_b200_bwd_v2_host
     h2d, d2h = call.h2d_bytes, call.d2h_bytes
 
     def one():

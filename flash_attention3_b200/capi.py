@@ -68,6 +68,7 @@ EXPORTS = [
     # include/shaobo_fa3_b200_ext.h
     "shaobo_fa3_b200_device_error", "shaobo_fa3_b200_stage_timing", "shaobo_fa3_b200_last_stage_ms",
     "shaobo_fa3_b200_bwd_v2_noalloc", "shaobo_fa3_b200_fwd",
+    "shaobo_fa3_b200_bwd_v2_host_staging_bytes", "shaobo_fa3_b200_bwd_v2_host",
 ]
 
 _lib = None
@@ -117,6 +118,10 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.shaobo_fa3_b200_device_error.restype = ctypes.c_int
     lib.shaobo_fa3_b200_stage_timing.argtypes = [ctypes.c_int]
     lib.shaobo_fa3_b200_stage_timing.restype = ctypes.c_int
+    lib.shaobo_fa3_b200_bwd_v2_host_staging_bytes.argtypes = [ctypes.POINTER(Params)]
+    lib.shaobo_fa3_b200_bwd_v2_host_staging_bytes.restype = ctypes.c_size_t
+    lib.shaobo_fa3_b200_bwd_v2_host.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_size_t, ctypes.POINTER(Params)]
+    lib.shaobo_fa3_b200_bwd_v2_host.restype = ctypes.c_int
     lib.shaobo_fa3_b200_fwd.argtypes = [ctypes.c_void_p] * 5 + [ctypes.POINTER(Params)]
     lib.shaobo_fa3_b200_fwd.restype = ctypes.c_int
     lib.shaobo_fa3_b200_last_stage_ms.argtypes = [ctypes.POINTER(ctypes.c_float)]

@@ -919,3 +919,230 @@ extern "C" int shaobo_fa3_b200_bwd_v2_noalloc(const void* dout, const void* q, c
     with_scratch.workspace_bytes = size_t(SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES);
     return shaobo_fa3_bwd_v2(dout, q, k, v, out, softmax_lse, dq, dk, dv, softmax_d, &with_scratch);
 }
+
+// ---------------------------------------------------------------------------
+// Backward for callers whose tensors live in host memory.
+//
+// The inputs are copied to the GPU, shaobo_fa3_bwd_v2 runs, dq/dk/dv are copied back.  Over PCIe the
+// copies, not the kernels, bound such a call, so the problem is cut into contiguous (batch, KV head)
+// shards (the backward has no reduction across them) that go round-robin over a few streams: the
+// host-to-device copy of one shard, the kernels of another and the device-to-host copy of a third
+// overlap.  Device memory comes from the caller (one staging buffer); the streams and events the
+// pipeline needs are created once per device and kept.
+namespace {
+
+constexpr int kHostLanes = 3;
+
+struct HostLanes {
+    std::mutex mu;
+    bool ready[128] = {};
+    cudaStream_t stream[128][kHostLanes] = {};
+    cudaEvent_t fork[128] = {};
+    cudaEvent_t join[128][kHostLanes] = {};
+    bool get(int dev) {
+        std::lock_guard<std::mutex> lock(mu);
+        if (ready[dev]) return true;
+        if (cudaEventCreateWithFlags(&fork[dev], cudaEventDisableTiming) != cudaSuccess) return false;
+        for (int i = 0; i < kHostLanes; ++i) {
+            if (cudaStreamCreateWithFlags(&stream[dev][i], cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&join[dev][i], cudaEventDisableTiming) != cudaSuccess) {
+                return false;
+            }
+        }
+        ready[dev] = true;
+        return true;
+    }
+};
+HostLanes g_host_lanes;
+
+// One piece of the (batch x KV head) range: whole batch entries, or a KV-head range inside one.
+struct HostPiece {
+    int batch_begin, batch_count, kv_head_begin, kv_head_count;
+};
+
+// Pieces of shard r of n (contiguous split of the batch*heads_kv units, as evenly as possible).
+int host_pieces(const ShaoboFa3Params* p, int r, int n, HostPiece* out) {
+    const long long units = (long long)p->batch * p->num_heads_kv;
+    long long lo = units * r / n;
+    const long long hi = units * (r + 1) / n;
+    int count = 0;
+    while (lo < hi && count < 3) {
+        const int b = int(lo / p->num_heads_kv), h = int(lo % p->num_heads_kv);
+        if (h == 0 && hi - lo >= p->num_heads_kv) {
+            const int nb = int((hi - lo) / p->num_heads_kv);
+            out[count++] = HostPiece{b, nb, 0, p->num_heads_kv};
+            lo += (long long)nb * p->num_heads_kv;
+        } else {
+            const int nh = int(std::min<long long>(p->num_heads_kv - h, hi - lo));
+            out[count++] = HostPiece{b, 1, h, nh};
+            lo += nh;
+        }
+    }
+    return count;
+}
+
+ShaoboFa3Params piece_params(const ShaoboFa3Params* p, const HostPiece& pc) {
+    ShaoboFa3Params s = *p;
+    const int group = p->num_heads_q / p->num_heads_kv;
+    s.batch = pc.batch_count;
+    s.num_heads_kv = pc.kv_head_count;
+    s.num_heads_q = pc.kv_head_count * group;
+    s.sync_after_launch = 0;
+    return s;
+}
+
+bool host_call_supported(const ShaoboFa3Params* p) {
+    return validate_v2(p) == SHAOBO_FA3_STATUS_SUCCESS && !is_varlen(p) && !has_seqused(p) &&
+           p->layout == SHAOBO_FA3_LAYOUT_BHSD;
+}
+
+int host_shard_count(const ShaoboFa3Params* p) {
+    // about one shard per 8 MB of PCIe traffic, at most 8, at most one per (batch, KV head): every copy
+    // costs about 10 us of set-up, so small problems want few, large copies (measured on 16.8 MB: two
+    // shards 368 us, four 475 us)
+    const size_t elem = 2;
+    const size_t total = (size_t(5) * p->num_heads_q + size_t(4) * p->num_heads_kv) * p->batch *
+                         p->seqlen_q * p->head_dim_qk * elem;
+    long long n = (long long)(total / (size_t(8) << 20));
+    const long long units = (long long)p->batch * p->num_heads_kv;
+    n = std::max<long long>(1, std::min<long long>(8, std::min(n, units)));
+    return int(n);
+}
+
+size_t host_lane_workspace(const ShaoboFa3Params* p) {
+    const int n = host_shard_count(p);
+    size_t need = 0;
+    for (int r = 0; r < n; ++r) {
+        HostPiece pcs[3];
+        const int cnt = host_pieces(p, r, n, pcs);
+        for (int i = 0; i < cnt; ++i) {
+            const ShaoboFa3Params s = piece_params(p, pcs[i]);
+            const V2Workspace w = v2_workspace(&s);
+            if (!w.valid) return 0;
+            need = std::max(need, w.total_bytes);
+        }
+    }
+    size_t out = 0;
+    return round_up_256(need, &out) ? out : 0;
+}
+
+}  // namespace
+
+namespace {
+struct HostStaging {
+    size_t q_bytes = 0, kv_bytes = 0, lse_bytes = 0, lane_ws = 0, total = 0;
+};
+HostStaging host_staging(const ShaoboFa3Params* p) {
+    HostStaging h;
+    if (!host_call_supported(p)) return h;
+    h.q_bytes = size_t(p->batch) * p->num_heads_q * p->seqlen_q * p->head_dim_qk * 2;
+    h.kv_bytes = size_t(p->batch) * p->num_heads_kv * p->seqlen_k * p->head_dim_qk * 2;
+    size_t lse = size_t(p->batch) * p->num_heads_q * p->seqlen_q * sizeof(float);
+    if (!round_up_256(lse, &h.lse_bytes)) return HostStaging{};
+    h.lane_ws = host_lane_workspace(p);
+    if (h.lane_ws == 0) return HostStaging{};
+    h.total = 4 * h.q_bytes + 4 * h.kv_bytes + h.lse_bytes + kHostLanes * h.lane_ws;
+    return h;
+}
+}  // namespace
+
+// Extension (no counterpart in the reference): bytes of device memory shaobo_fa3_b200_bwd_v2_host
+// needs in `staging` for these parameters (device copies of the nine tensors plus one workspace per
+// stream); 0 when the parameters are not accepted.  Host only.
+extern "C" size_t shaobo_fa3_b200_bwd_v2_host_staging_bytes(const ShaoboFa3Params* params) {
+    return host_staging(params).total;
+}
+
+// Extension (no counterpart in the reference): shaobo_fa3_bwd_v2 for tensors in host memory (pinned
+// for full speed), [B,H,S,D], fixed lengths.  Enqueues copies and kernels behind the caller's stream
+// (params->reserved_ptr[7], NULL = default stream) and makes that stream wait for them; the host
+// buffers may be read once that stream has been synchronised (or at once with sync_after_launch).
+extern "C" int shaobo_fa3_b200_bwd_v2_host(const void* dout, const void* q, const void* k,
+                                           const void* v, const void* out, const void* softmax_lse,
+                                           void* dq, void* dk, void* dv, void* staging,
+                                           size_t staging_bytes, const ShaoboFa3Params* params) {
+    begin();
+    const int validation = validate_v2(params);
+    if (validation != SHAOBO_FA3_STATUS_SUCCESS) return validation;
+    if (!host_call_supported(params)) return SHAOBO_FA3_STATUS_UNSUPPORTED;
+    const HostStaging hs = host_staging(params);
+    if (dout == nullptr || q == nullptr || k == nullptr || v == nullptr || out == nullptr ||
+        softmax_lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr ||
+        staging == nullptr || hs.total == 0 || staging_bytes < hs.total) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 128 || !g_host_lanes.get(dev)) {
+        return SHAOBO_FA3_STATUS_HIP_ERROR;
+    }
+    uint8_t* base = static_cast<uint8_t*>(staging);
+    uint8_t* d_q = base;
+    uint8_t* d_do = d_q + hs.q_bytes;
+    uint8_t* d_out = d_do + hs.q_bytes;
+    uint8_t* d_dq = d_out + hs.q_bytes;
+    uint8_t* d_k = d_dq + hs.q_bytes;
+    uint8_t* d_v = d_k + hs.kv_bytes;
+    uint8_t* d_dk = d_v + hs.kv_bytes;
+    uint8_t* d_dv = d_dk + hs.kv_bytes;
+    uint8_t* d_lse = d_dv + hs.kv_bytes;
+    uint8_t* d_ws = d_lse + hs.lse_bytes;
+
+    cudaStream_t caller = stream_of(params);
+    if (cudaEventRecord(g_host_lanes.fork[dev], caller) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
+    const int group = params->num_heads_q / params->num_heads_kv;
+    const size_t q_head = size_t(params->seqlen_q) * params->head_dim_qk * 2;   // bytes of one query head
+    const size_t kv_head = size_t(params->seqlen_k) * params->head_dim_qk * 2;
+    const size_t lse_head = size_t(params->seqlen_q) * sizeof(float);
+    const int n = host_shard_count(params);
+    bool used[kHostLanes] = {};
+    int piece_index = 0;
+    for (int r = 0; r < n; ++r) {
+        HostPiece pcs[3];
+        const int cnt = host_pieces(params, r, n, pcs);
+        for (int i = 0; i < cnt; ++i, ++piece_index) {
+            const int lane = piece_index % kHostLanes;
+            cudaStream_t st = g_host_lanes.stream[dev][lane];
+            if (!used[lane]) {
+                if (cudaStreamWaitEvent(st, g_host_lanes.fork[dev], 0) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
+                used[lane] = true;
+            }
+            const HostPiece& pc = pcs[i];
+            const size_t qh = size_t(pc.batch_begin) * params->num_heads_q + size_t(pc.kv_head_begin) * group;
+            const size_t kh = size_t(pc.batch_begin) * params->num_heads_kv + pc.kv_head_begin;
+            const size_t q_n = size_t(pc.batch_count) * pc.kv_head_count * group;  // query heads in the piece
+            const size_t k_n = size_t(pc.batch_count) * pc.kv_head_count;
+            auto h2d = [&](uint8_t* d, const void* h, size_t off, size_t bytes) {
+                return cudaMemcpyAsync(d + off, static_cast<const uint8_t*>(h) + off, bytes, cudaMemcpyHostToDevice, st) == cudaSuccess;
+            };
+            auto d2h = [&](void* h, const uint8_t* d, size_t off, size_t bytes) {
+                return cudaMemcpyAsync(static_cast<uint8_t*>(h) + off, d + off, bytes, cudaMemcpyDeviceToHost, st) == cudaSuccess;
+            };
+            if (!h2d(d_q, q, qh * q_head, q_n * q_head) || !h2d(d_k, k, kh * kv_head, k_n * kv_head) ||
+                !h2d(d_v, v, kh * kv_head, k_n * kv_head) || !h2d(d_do, dout, qh * q_head, q_n * q_head) ||
+                !h2d(d_out, out, qh * q_head, q_n * q_head) || !h2d(d_lse, softmax_lse, qh * lse_head, q_n * lse_head)) {
+                return SHAOBO_FA3_STATUS_HIP_ERROR;
+            }
+            ShaoboFa3Params s = piece_params(params, pc);
+            s.workspace = d_ws + size_t(lane) * hs.lane_ws;
+            s.workspace_bytes = hs.lane_ws;
+            s.reserved_ptr[SHAOBO_FA3_RESERVED_PTR_STREAM] = st;
+            const int status = shaobo_fa3_bwd_v2(d_do + qh * q_head, d_q + qh * q_head, d_k + kh * kv_head,
+                                                 d_v + kh * kv_head, d_out + qh * q_head, d_lse + qh * lse_head,
+                                                 d_dq + qh * q_head, d_dk + kh * kv_head, d_dv + kh * kv_head,
+                                                 nullptr, &s);
+            if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
+            if (!d2h(dq, d_dq, qh * q_head, q_n * q_head) || !d2h(dk, d_dk, kh * kv_head, k_n * kv_head) ||
+                !d2h(dv, d_dv, kh * kv_head, k_n * kv_head)) {
+                return SHAOBO_FA3_STATUS_HIP_ERROR;
+            }
+        }
+    }
+    for (int lane = 0; lane < kHostLanes; ++lane) {
+        if (!used[lane]) continue;
+        if (cudaEventRecord(g_host_lanes.join[dev][lane], g_host_lanes.stream[dev][lane]) != cudaSuccess ||
+            cudaStreamWaitEvent(caller, g_host_lanes.join[dev][lane], 0) != cudaSuccess) {
+            return SHAOBO_FA3_STATUS_HIP_ERROR;
+        }
+    }
+    return finish(params, params->sync_after_launch != 0);
+}

@@ -275,5 +275,42 @@ class HostBackward:
             main.wait_stream(st)
 
 
+class HostBackwardC:
+    """The same call as HostBackward, with the shard pipeline inside the library
+    (shaobo_fa3_b200_bwd_v2_host): one C call per backward, no per-copy Python overhead.  [B,H,S,D],
+    fixed lengths.  The device staging buffer is allocated once, here."""
+
+    def __init__(self, batch, heads_q, heads_kv, seqlen, head_dim, dtype, causal, softmax_scale=None,
+                 device="cuda", seqlen_k=None):
+        self.lib = capi.load()
+        self.p = capi.new_params(batch=batch, seqlen_q=seqlen, seqlen_k=seqlen if seqlen_k is None else seqlen_k,
+                                 num_heads_q=heads_q, num_heads_kv=heads_kv, head_dim_qk=head_dim,
+                                 head_dim_v=head_dim, causal=int(causal), dtype=_DTYPES[dtype])
+        if softmax_scale is not None:
+            self.p.softmax_scale = float(softmax_scale)
+            self.p.softmax_scale_is_set = 1
+        need = self.lib.shaobo_fa3_b200_bwd_v2_host_staging_bytes(ctypes.byref(self.p))
+        if need == 0:
+            raise Fa3Error("shaobo_fa3_b200_bwd_v2_host_staging_bytes", capi.STATUS_UNSUPPORTED)
+        self.staging = torch.empty(need, dtype=torch.uint8, device=device)
+        elem = torch.empty((), dtype=dtype).element_size()
+        nq, nkv = batch * heads_q * seqlen * head_dim * elem, batch * heads_kv * self.p.seqlen_k * head_dim * elem
+        self.h2d_bytes = 3 * nq + 2 * nkv + batch * heads_q * seqlen * 4
+        self.d2h_bytes = nq + 2 * nkv
+
+    def __call__(self, dout, q, k, v, out, softmax_lse, dq, dk, dv):
+        """Nine host tensors; dq, dk, dv are written once the current stream has been synchronised."""
+        for t in (dout, q, k, v, out, softmax_lse, dq, dk, dv):
+            if t.is_cuda or not t.is_contiguous():
+                raise RuntimeError("contiguous host tensors are required")
+        with torch.cuda.device(self.staging.device):
+            self.p.reserved_ptr[capi.RESERVED_PTR_STREAM] = torch.cuda.current_stream().cuda_stream or None
+            code = self.lib.shaobo_fa3_b200_bwd_v2_host(
+                _ptr(dout), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(softmax_lse), _ptr(dq), _ptr(dk), _ptr(dv),
+                _ptr(self.staging), self.staging.numel(), ctypes.byref(self.p))
+        if code != capi.STATUS_SUCCESS:
+            raise Fa3Error("shaobo_fa3_b200_bwd_v2_host", code)
+
+
 def default_scale(d: int) -> float:
     return 1.0 / math.sqrt(d)

@@ -79,6 +79,36 @@ int shaobo_fa3_b200_bwd_v2_noalloc(const void* dout,
                                    void* softmax_d,
                                    const ShaoboFa3Params* params);
 
+/* shaobo_fa3_bwd_v2 for tensors that live in HOST memory (pinned for full
+ * speed): dout, q, k, v, out, softmax_lse are read from and dq, dk, dv written
+ * to host buffers; [B,H,S,D] layout, fixed lengths (other parameter blocks
+ * return UNSUPPORTED).  No counterpart in the reference.
+ *
+ * The call copies the inputs to the GPU, runs the backward and copies the
+ * gradients back, cut into (batch, KV head) shards that are pipelined over
+ * three internal streams so that copies in both directions and kernels overlap
+ * (over PCIe the copies bound such a call).  `staging` is device memory owned
+ * by the caller, at least shaobo_fa3_b200_bwd_v2_host_staging_bytes(params)
+ * bytes; params->workspace is ignored.  The work is enqueued behind the
+ * caller's stream (params->reserved_ptr[7], NULL = default stream), which is
+ * made to wait for it: the host outputs are valid once that stream has been
+ * synchronised, or on return with sync_after_launch = 1.  The internal streams
+ * and events are created on the first call per device (outside stream
+ * capture) and kept; calls that overlap in time must use different staging. */
+size_t shaobo_fa3_b200_bwd_v2_host_staging_bytes(const ShaoboFa3Params* params);
+int shaobo_fa3_b200_bwd_v2_host(const void* dout,
+                                const void* q,
+                                const void* k,
+                                const void* v,
+                                const void* out,
+                                const void* softmax_lse,
+                                void* dq,
+                                void* dk,
+                                void* dv,
+                                void* staging,
+                                size_t staging_bytes,
+                                const ShaoboFa3Params* params);
+
 /* Attention forward: out = softmax(q k^T * scale) v and softmax_lse = the
  * natural-log log-sum-exp of every row, i.e. the two tensors shaobo_fa3_bwd_v2
  * takes next to q, k, v.  No counterpart in the reference, which is a backward

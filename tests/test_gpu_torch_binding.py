@@ -87,3 +87,23 @@ def test_calls_from_a_fresh_host_thread():
         assert isinstance(results[tag], np.ndarray), (tag, results[tag])
     assert np.array_equal(results["first"], results["main"]) and np.array_equal(results["second"], results["main"])
     assert golden.check_gradient(results["main"], prob.ref["dq"], "bf16")["pass"]
+
+
+def test_host_tensor_entry_point_of_the_library():
+    """shaobo_fa3_b200_bwd_v2_host: the shard pipeline inside the library, host tensors in and out."""
+    from flash_attention3_b200 import ops
+    for shape in ((2, 4, 2, 384, 64), (1, 8, 8, 1024, 128)):   # the second one is cut into several shards
+        b, hq, hkv, s, d = shape
+        prob = helpers.Problem(b, hq, hkv, s, d, "bf16", True, seed=305)
+        td = helpers.TORCH_DTYPE["bf16"]
+        pin = lambda x, dt=td: torch.from_numpy(np.ascontiguousarray(x)).to(dt).pin_memory()
+        q, k, v, do, out = (pin(x) for x in (prob.q, prob.k, prob.v, prob.do, prob.ref["out"]))
+        lse = pin(prob.ref["lse"], torch.float32)
+        dq, dk, dv = (torch.full_like(t, float("nan")).pin_memory() for t in (q, k, v))
+        call = ops.HostBackwardC(b, hq, hkv, s, d, td, True, softmax_scale=prob.scale)
+        for _ in range(2):
+            call(do, q, k, v, out, lse, dq, dk, dv)
+        torch.cuda.synchronize()
+        for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+            m = golden.check_gradient(t.float().numpy(), prob.ref[name], "bf16")
+            assert m["pass"], (shape, name, m)
