@@ -43,6 +43,8 @@ struct DqArgs {
     int sidecar_rows;         // rows per head of the sidecar (seqlen_q, or total_q when packed)
     float scale;
     float scale_log2;
+    float softcap_pre;        // softcap variant, see FusedArgs
+    float softcap_post;
 };
 
 template <int D>
@@ -77,7 +79,7 @@ enum DqBar : int {
     kDqbNum = 10,
 };
 
-template <typename T, int D, bool kCausal, typename TOut>
+template <typename T, int D, bool kCausal, typename TOut, bool kSoftcap = false>
 __global__ void __launch_bounds__(256, 1)
 dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -263,8 +265,14 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     ptx::tmem_ld_wait();
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
-                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, neg));
-                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, neg));
+                        float p0, p1;
+                        if (kSoftcap) {
+                            p0 = ptx::ex2_approx(fmaf(a.softcap_post, ptx::tanh_approx(__uint_as_float(r[e + 0]) * a.softcap_pre), neg));
+                            p1 = ptx::ex2_approx(fmaf(a.softcap_post, ptx::tanh_approx(__uint_as_float(r[e + 1]) * a.softcap_pre), neg));
+                        } else {
+                            p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, neg));
+                            p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, neg));
+                        }
                         if (diagonal) {
                             const int j = c * 32 + e;
                             p0 = (j + 0 >= mask_from && j + 0 <= mask_to) ? p0 : 0.0f;
@@ -286,8 +294,16 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         const float2 p = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2]);
-                        o[e / 2] = ptx::Pack2<T>::pack(p.x * (__uint_as_float(r[e + 0]) - delta),
-                                                       p.y * (__uint_as_float(r[e + 1]) - delta));
+                        float ds0 = p.x * (__uint_as_float(r[e + 0]) - delta);
+                        float ds1 = p.y * (__uint_as_float(r[e + 1]) - delta);
+                        if (kSoftcap) {
+                            // slope 1 - tanh^2 of the cap, with tanh recovered from P and the row's reference
+                            const float inv_post = 1.0f / a.softcap_post;
+                            const float t0 = (__log2f(p.x) - neg) * inv_post, t1 = (__log2f(p.y) - neg) * inv_post;
+                            ds0 = p.x > 0.0f ? ds0 * fmaxf(1.0f - t0 * t0, 0.0f) : 0.0f;
+                            ds1 = p.y > 0.0f ? ds1 * fmaxf(1.0f - t1 * t1, 0.0f) : 0.0f;
+                        }
+                        o[e / 2] = ptx::Pack2<T>::pack(ds0, ds1);
                     }
                     // dS chunk c lands on columns [16c, 16c+16) of the dP region,
                     // all of which were read by chunk loads <= c

@@ -98,7 +98,7 @@ int validate_v2(const ShaoboFa3Params* p) {
     const bool lengths_ok = is_varlen(p) ? varlen_fields_ok(p) : lengths_are_fixed(p);
     if (!lengths_ok || !dtype_supported(p->dtype) || !layout_supported(p->layout) ||
         !head_dim_supported(p->head_dim_qk) || p->head_dim_v != p->head_dim_qk ||
-        p->dropout_p != 0.0f || p->softcap != 0.0f || p->sm_margin != 0 || !lengths_in_range(p)) {
+        p->dropout_p != 0.0f || p->sm_margin != 0 || !lengths_in_range(p)) {
         return SHAOBO_FA3_STATUS_UNSUPPORTED;
     }
     return SHAOBO_FA3_STATUS_SUCCESS;
@@ -230,7 +230,7 @@ extern "C" int shaobo_fa3_bwd_get_capabilities(ShaoboFa3BwdCapabilities* caps) {
                          SHAOBO_FA3_BWD_FEATURE_GQA | SHAOBO_FA3_BWD_FEATURE_DETERMINISTIC |
                          SHAOBO_FA3_BWD_FEATURE_SOFTMAX_LSE | SHAOBO_FA3_BWD_FEATURE_BHSD |
                          SHAOBO_FA3_BWD_FEATURE_BSHD | SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW |
-                         SHAOBO_FA3_BWD_FEATURE_VARLEN |
+                         SHAOBO_FA3_BWD_FEATURE_VARLEN | SHAOBO_FA3_BWD_FEATURE_SOFTCAP |
                          SHAOBO_FA3_BWD_FEATURE_FULL_ATTENTION;
     caps->min_head_dim = kMinHeadDim;
     caps->max_head_dim = kMaxHeadDim;

@@ -77,7 +77,8 @@ bool make_map_accum(CUtensorMap* map, const float* base, int64_t batch_heads, in
 // The kernels come in two forms: a lean one for full attention over whole 128-row tiles and a general
 // one (causal mask, sliding window, ragged sequence ends).
 bool needs_general_form(const ShaoboFa3Params* p) {
-    return is_varlen(p) || has_seqused(p) || !band_is_full(band_of(p)) || p->seqlen_q % kTileRows != 0 ||
+    return is_varlen(p) || has_seqused(p) || p->softcap > 0.0f || !band_is_full(band_of(p)) ||
+           p->seqlen_q % kTileRows != 0 ||
            p->seqlen_k % kTileRows != 0;
 }
 
@@ -286,12 +287,12 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
 }
 
 // ------------------------------------------------------- fused / dKV kernel
-template <typename T, int D, bool kCausal, bool kWithDq, typename TOut>
+template <typename T, int D, bool kCausal, bool kWithDq, typename TOut, bool kSoftcap = false>
 int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                    const CUtensorMap& mdo, const CUtensorMap& mdq, const CUtensorMap& mdk,
                    const CUtensorMap& mdv, const FusedArgs& args, int blocks, cudaStream_t st,
                    bool pdl) {
-    auto kernel = fused_bwd_kernel<T, D, kCausal, kWithDq, TOut>;
+    auto kernel = fused_bwd_kernel<T, D, kCausal, kWithDq, TOut, kSoftcap>;
     static DeviceOnce configured;  // per instantiation and device
     if (!configured.done()) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -325,6 +326,11 @@ int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtens
                    bool pdl) {
     cudaStream_t st = stream_of(p);
     const bool banded = needs_general_form(p);
+    if (p->softcap > 0.0f) {  // softcapped scores: general form only
+        return p->head_dim_qk == 128
+                   ? launch_fused_t<T, 128, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
+                   : launch_fused_t<T, 64, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
+    }
     if (p->head_dim_qk == 128) {
         return banded ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
                          : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
@@ -418,6 +424,8 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
     args.sidecar_rows = shape.rows_q;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
+    args.softcap_pre = p->softcap > 0.0f ? p->softmax_scale / p->softcap : 0.0f;
+    args.softcap_post = p->softcap * kLog2E;
     args.order_mode = plan.mode;
     args.order_width = plan.width;
     args.head_group = plan.head_group;
@@ -454,10 +462,10 @@ int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, cons
 }
 
 // -------------------------------------------------------------- dQ kernel
-template <typename T, int D, bool kCausal, typename TOut>
+template <typename T, int D, bool kCausal, typename TOut, bool kSoftcap = false>
 int launch_dq_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                 const CUtensorMap& mdo, const DqArgs& args, int blocks, cudaStream_t st) {
-    auto kernel = dq_bwd_kernel<T, D, kCausal, TOut>;
+    auto kernel = dq_bwd_kernel<T, D, kCausal, TOut, kSoftcap>;
     static DeviceOnce configured;
     if (!configured.done()) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -475,6 +483,10 @@ int launch_dq_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorM
                 const CUtensorMap& mv, const CUtensorMap& mdo, const DqArgs& args, int blocks) {
     cudaStream_t st = stream_of(p);
     const bool banded = needs_general_form(p);
+    if (p->softcap > 0.0f) {
+        return p->head_dim_qk == 128 ? launch_dq_t<T, 128, true, TOut, true>(mq, mk, mv, mdo, args, blocks, st)
+                                     : launch_dq_t<T, 64, true, TOut, true>(mq, mk, mv, mdo, args, blocks, st);
+    }
     if (p->head_dim_qk == 128) {
         return banded ? launch_dq_t<T, 128, true, TOut>(mq, mk, mv, mdo, args, blocks, st)
                          : launch_dq_t<T, 128, false, TOut>(mq, mk, mv, mdo, args, blocks, st);
@@ -514,6 +526,8 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
     args.sidecar_rows = shape.rows_q;
     args.scale = p->softmax_scale;
     args.scale_log2 = p->softmax_scale * kLog2E;
+    args.softcap_pre = p->softcap > 0.0f ? p->softmax_scale / p->softcap : 0.0f;
+    args.softcap_post = p->softcap * kLog2E;
     const int64_t blocks64 = int64_t(tiles_of(plan_seqlen_q(p))) * p->batch * p->num_heads_q;
     if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
     const int blocks = int(blocks64);
@@ -526,10 +540,10 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
 }
 
 // ---------------------------------------------------------- forward kernel
-template <typename T, int D, bool kMasked>
+template <typename T, int D, bool kMasked, bool kSoftcap = false>
 int launch_fwd_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                  const FwdArgs& args, int blocks, cudaStream_t st) {
-    auto kernel = fwd_kernel<T, D, kMasked>;
+    auto kernel = fwd_kernel<T, D, kMasked, kSoftcap>;
     static DeviceOnce configured;
     if (!configured.done()) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -547,6 +561,10 @@ int launch_fwd_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensor
                  const CUtensorMap& mv, const FwdArgs& args, int blocks) {
     cudaStream_t st = stream_of(p);
     const bool masked = needs_general_form(p);
+    if (p->softcap > 0.0f) {
+        return p->head_dim_qk == 128 ? launch_fwd_t<T, 128, true, true>(mq, mk, mv, args, blocks, st)
+                                     : launch_fwd_t<T, 64, true, true>(mq, mk, mv, args, blocks, st);
+    }
     if (p->head_dim_qk == 128) {
         return masked ? launch_fwd_t<T, 128, true>(mq, mk, mv, args, blocks, st)
                       : launch_fwd_t<T, 128, false>(mq, mk, mv, args, blocks, st);
@@ -581,6 +599,8 @@ int launch_fwd(const ShaoboFa3Params* p, const void* q, const void* k, const voi
     args.seqused_k = p->seqused_k;
     args.lse_rows = shape.rows_q;
     args.scale_log2 = p->softmax_scale * kLog2E;
+    args.softcap_pre = p->softcap > 0.0f ? p->softmax_scale / p->softcap : 0.0f;
+    args.softcap_post = p->softcap * kLog2E;
     // one CTA per pair of query tiles
     const int64_t blocks64 = int64_t((tiles_of(plan_seqlen_q(p)) + 1) / 2) * p->batch * p->num_heads_q;
     if (blocks64 > 0x7fffffffLL) return SHAOBO_FA3_STATUS_UNSUPPORTED;
@@ -590,7 +610,7 @@ int launch_fwd(const ShaoboFa3Params* p, const void* q, const void* k, const voi
 
 bool stage_params_ok(const ShaoboFa3Params* p) {
     // (the component entry points take fixed-length batches only)
-    return p != nullptr && !is_varlen(p) && !has_seqused(p) && dtype_supported(p->dtype) && layout_supported(p->layout) &&
+    return p != nullptr && !is_varlen(p) && !has_seqused(p) && p->softcap == 0.0f && dtype_supported(p->dtype) && layout_supported(p->layout) &&
            (p->causal == 0 || p->causal == 1) && fused_shape_ok(p);
 }
 

@@ -98,6 +98,11 @@ struct FusedArgs {
     int sidecar_rows;      // rows per head of the sidecar / accumulators (seqlen_q, or total_q when packed)
     float scale;
     float scale_log2;
+    // softcap variant: the scaled scores go through softcap * tanh(x / softcap) before the softmax;
+    // in log2 units that is softcap_post * tanh(score * softcap_pre), softcap_pre = scale / softcap,
+    // softcap_post = softcap * log2(e)
+    float softcap_pre;
+    float softcap_post;
     int order_mode;        // see cta_order.h
     int order_width;
     int head_group;        // heads per scheduling group: block = (group * n_tiles + tile slot) * head_group + head
@@ -221,7 +226,10 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity,
 // T: storage type of Q/K/V/dO (__half or __nv_bfloat16).  TOut: type of the dK
 // and dV outputs (T for the fused path, float for the split path).  kWithDq:
 // false turns the kernel into the four-GEMM dK/dV half of the split path.
-template <typename T, int D, bool kCausal, bool kWithDq, typename TOut>
+// kSoftcap: softcapped scores (general form only).  dS then carries the slope 1 - tanh^2 of the cap,
+// which the second softmax phase recovers from P itself (t = (log2 P - (log2 r - m)) / softcap_post)
+// instead of keeping it in registers between the phases.
+template <typename T, int D, bool kCausal, bool kWithDq, typename TOut, bool kSoftcap = false>
 __global__ void __launch_bounds__(512, 1)
 fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -582,6 +590,12 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 int mask_from = 0, mask_to = 0;  // set only on masked tiles
                 // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked as above.
                 // (two copies of the chunk code, so that unmasked tiles carry no per-element test)
+                // score in log2 units, relative to the row's reference: s * scale*log2e + (log2 r - m), or the
+                // capped score + (log2 r - m)
+                auto log2_score = [&](uint32_t raw, float neg) {
+                    return kSoftcap ? fmaf(a.softcap_post, ptx::tanh_approx(__uint_as_float(raw) * a.softcap_pre), neg)
+                                    : fmaf(__uint_as_float(raw), a.scale_log2, neg);
+                };
                 auto softmax_chunk = [&](int c, const uint32_t* r, auto masked_tag) {
                     constexpr bool kMasked = decltype(masked_tag)::value;
 #ifdef FA3B200_DEBUG_DUMP
@@ -592,10 +606,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                     for (int e = 0; e < 32; e += 4) {
                         const float4 n4 = *reinterpret_cast<const float4*>(negp + c * 32 + e);
-                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 0]), a.scale_log2, n4.x));
-                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, n4.y));
-                        float p2 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 2]), a.scale_log2, n4.z));
-                        float p3 = ptx::ex2_approx(fmaf(__uint_as_float(r[e + 3]), a.scale_log2, n4.w));
+                        float p0 = ptx::ex2_approx(log2_score(r[e + 0], n4.x));
+                        float p1 = ptx::ex2_approx(log2_score(r[e + 1], n4.y));
+                        float p2 = ptx::ex2_approx(log2_score(r[e + 2], n4.z));
+                        float p3 = ptx::ex2_approx(log2_score(r[e + 3], n4.w));
                         if (kMasked) {
                             const int i = half * 64 + c * 32 + e;
                             p0 = (i + 0 >= mask_from && i + 0 <= mask_to) ? p0 : 0.0f;
@@ -639,6 +653,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 DBG_STAMP(6);
                 ptx::tc_fence_after();
                 const uint32_t ds_row = sbase + C::kOffDS + half * C::kBoxBytes + j * 128;
+                const float inv_post = kSoftcap ? 1.0f / a.softcap_post : 0.0f;
                 auto ds_chunk = [&](int c, const uint32_t* r) {
 #ifdef FA3B200_DEBUG_DUMP
                     if (blockIdx.x == 0 && t == 0)
@@ -654,6 +669,20 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         const float2 pc = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 2]);
                         const float2 pd = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 3]);
                         uint4 o;
+                        if (kSoftcap) {
+                            // dS = P (dP - delta) (1 - t^2), t recovered from P and the row's reference
+                            const float4 n0 = *reinterpret_cast<const float4*>(negp + c * 32 + e);
+                            const float4 n1 = *reinterpret_cast<const float4*>(negp + c * 32 + e + 4);
+                            auto capped = [&](float p, uint32_t dp, float del, float neg) {
+                                const float t = (__log2f(p) - neg) * inv_post;
+                                const float slope = fmaxf(1.0f - t * t, 0.0f);
+                                return p > 0.0f ? p * (__uint_as_float(dp) - del) * slope : 0.0f;
+                            };
+                            o.x = ptx::Pack2<T>::pack(capped(pa.x, r[e + 0], d0.x, n0.x), capped(pa.y, r[e + 1], d0.y, n0.y));
+                            o.y = ptx::Pack2<T>::pack(capped(pb.x, r[e + 2], d0.z, n0.z), capped(pb.y, r[e + 3], d0.w, n0.w));
+                            o.z = ptx::Pack2<T>::pack(capped(pc.x, r[e + 4], d1.x, n1.x), capped(pc.y, r[e + 5], d1.y, n1.y));
+                            o.w = ptx::Pack2<T>::pack(capped(pd.x, r[e + 6], d1.z, n1.z), capped(pd.y, r[e + 7], d1.w, n1.w));
+                        } else {
                         o.x = ptx::Pack2<T>::pack(pa.x * (__uint_as_float(r[e + 0]) - d0.x),
                                                   pa.y * (__uint_as_float(r[e + 1]) - d0.y));
                         o.y = ptx::Pack2<T>::pack(pb.x * (__uint_as_float(r[e + 2]) - d0.z),
@@ -662,6 +691,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                                   pc.y * (__uint_as_float(r[e + 5]) - d1.y));
                         o.w = ptx::Pack2<T>::pack(pd.x * (__uint_as_float(r[e + 6]) - d1.z),
                                                   pd.y * (__uint_as_float(r[e + 7]) - d1.w));
+                        }
                         const int chunk = c * 4 + e / 8;  // 16-byte chunk inside this half's box
                         const uint32_t addr = ds_row + ((chunk ^ (j & 7)) << 4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.x),

@@ -48,6 +48,8 @@ struct FwdArgs {
     const int* seqused_k;     // get out = 0 and lse = -inf
     int lse_rows;             // rows per head of lse (seqlen_q, or total_q when packed)
     float scale_log2;         // softmax scale * log2(e)
+    float softcap_pre;        // softcap variant: scores become softcap_post * tanh(score * softcap_pre),
+    float softcap_post;       // with softcap_pre = scale / softcap and softcap_post = softcap * log2(e)
 };
 
 template <int D>
@@ -89,7 +91,8 @@ enum FwdBar : int {
     kFwdNum = 16,
 };
 
-template <typename T, int D, bool kMasked>
+// kSoftcap: the scaled scores go through softcap * tanh(x / softcap) before the softmax.
+template <typename T, int D, bool kMasked, bool kSoftcap = false>
 __global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
@@ -310,6 +313,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const bool q_valid = qi < band.seqlen_q;
             float m_ref = -INFINITY;  // reference maximum (raw scores) the exponentials are taken against
             float l = 0.0f;           // sum of the exponentials, in units of exp2(m_ref * scale_log2)
+            const float sl = kSoftcap ? 1.0f : a.scale_log2;  // log2 units per unit of (transformed) score
             bool ok = true;
 #pragma unroll 1
             for (int u = 0; u < n_steps; ++u) {
@@ -324,6 +328,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                 for (int c = 0; c < 4; ++c) ptx::tmem_ld32(s_cols + c * 32, r[c]);
                 ptx::tmem_ld_wait();
+                if (kSoftcap) {
+                    // capped scores, already in log2 units: from here on they are used with a scale of 1
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            r[c][e] = __float_as_uint(a.softcap_post *
+                                                      ptx::tanh_approx(__uint_as_float(r[c][e]) * a.softcap_pre));
+                        }
+                    }
+                }
                 float mt = -INFINITY;
                 if (diagonal) {
 #pragma unroll
@@ -343,9 +358,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 }
                 // ---- move the reference maximum only when it is more than 2^8 too small
                 float alpha = 1.0f;
-                const bool move = (mt - m_ref) * a.scale_log2 > C::kRescaleThreshold;  // also -inf -> finite
+                const bool move = (mt - m_ref) * sl > C::kRescaleThreshold;  // also -inf -> finite
                 if (move) {
-                    alpha = ptx::ex2_approx((m_ref - mt) * a.scale_log2);  // exp2(-inf) = 0 on the first move
+                    alpha = ptx::ex2_approx((m_ref - mt) * sl);  // exp2(-inf) = 0 on the first move
                     m_ref = mt;
                     l *= alpha;
                 }
@@ -367,15 +382,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 }
                 // ---- P = exp2((S - m_ref) * scale_log2), written over S as 16-bit pairs (every column of
                 // S has been read by now)
-                const float neg = m_ref == -INFINITY ? 0.0f : -m_ref * a.scale_log2;
+                const float neg = m_ref == -INFINITY ? 0.0f : -m_ref * sl;
                 float sum = 0.0f;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t o[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
-                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[c][e + 0]), a.scale_log2, neg));
-                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[c][e + 1]), a.scale_log2, neg));
+                        float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[c][e + 0]), sl, neg));
+                        float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[c][e + 1]), sl, neg));
                         if (diagonal) {
                             const int j = c * 32 + e;
                             p0 = (j + 0 >= mask_from && j + 0 <= mask_to) ? p0 : 0.0f;
@@ -410,7 +425,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
                 if (q_valid) {
                     // ln(sum exp(s*scale)) = (m_ref*scale_log2 + log2 l) * ln 2
-                    *lse_dst = l > 0.0f ? (m_ref * a.scale_log2 + __log2f(l)) * 0.69314718055994531f : -INFINITY;
+                    *lse_dst = l > 0.0f ? (m_ref * sl + __log2f(l)) * 0.69314718055994531f : -INFINITY;
                 }
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {

@@ -61,7 +61,7 @@ def _require_cuda(*tensors):
 
 def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, deterministic=False,
             workspace=None, return_delta=False, sync=False, layout: str = "bhsd", window=(-1, -1),
-            seqused_q=None, seqused_k=None, outputs=None):
+            seqused_q=None, seqused_k=None, outputs=None, softcap: float = 0.0):
     """dq, dk, dv (and delta) = backward of softmax(q k^T * scale) v.
 
     layout "bhsd": q, out, dout [B,Hq,Sq,D]; k, v [B,Hkv,Sk,D].  layout "bshd": [B,Sq,Hq,D] and
@@ -75,7 +75,7 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
     _require_cuda(dout, q, k, v, out, softmax_lse)
     lib = capi.load()
     p = make_params(q, k, causal, softmax_scale, layout=layout, seqused_q=seqused_q, seqused_k=seqused_k,
-                    deterministic=int(deterministic),
+                    softcap=float(softcap), deterministic=int(deterministic),
                     sync_after_launch=int(sync), window_left=int(window[0]), window_right=int(window[1]))
     need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
     if need == 0:
@@ -101,13 +101,13 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
 
 
 def fa3_fwd(q, k, v, causal: bool, softmax_scale=None, layout: str = "bhsd", window=(-1, -1), sync=False,
-            seqused_q=None, seqused_k=None):
+            seqused_q=None, seqused_k=None, softcap: float = 0.0):
     """out, softmax_lse = forward of softmax(q k^T * scale) v (shaobo_fa3_b200_fwd).  Shapes, layouts,
     masks as in fa3_bwd; softmax_lse is fp32 [B,Hq,Sq] natural log."""
     _require_cuda(q, k, v)
     lib = capi.load()
     p = make_params(q, k, causal, softmax_scale, layout=layout, seqused_q=seqused_q, seqused_k=seqused_k,
-                    sync_after_launch=int(sync),
+                    softcap=float(softcap), sync_after_launch=int(sync),
                     window_left=int(window[0]), window_right=int(window[1]))
     out = torch.empty_like(q)
     lse = torch.empty((p.batch, p.num_heads_q, p.seqlen_q), dtype=torch.float32, device=q.device)

@@ -200,6 +200,8 @@ size_t shaobo_fa3_bwd_v2_workspace_bytes(const ShaoboFa3Params* params);
  *    first seqused[b] rows of batch entry b take part (with fixed-length
  *    batches and with packed sequences); the rows of dq/dk/dv behind them, up
  *    to the end of the entry, are written as zero.
+ *  - softcap > 0: the scaled scores go through softcap * tanh(x / softcap)
+ *    before the softmax (softmax_lse must come from such a forward).
  *
  * The call only enqueues work on the stream (params->reserved_ptr[7], NULL =
  * default stream) unless sync_after_launch is set.  The first call on a host

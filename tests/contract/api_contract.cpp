@@ -81,7 +81,8 @@ int main() {
     expect("caps.api_version", caps.api_version, SHAOBO_FA3_API_VERSION);
     expect("caps.required bits", (caps.feature_mask & required) == required, 1);
     const ShaoboFa3BwdFeatureMask absent =
-        SHAOBO_FA3_BWD_FEATURE_SOFTCAP;
+        SHAOBO_FA3_BWD_FEATURE_FIXED_LENGTH & 0;  /* every feature of the reference's mask is offered */
+    expect("caps.softcap", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_SOFTCAP) != 0, 1);
     expect("caps.varlen", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_VARLEN) != 0, 1);
     expect("caps.bshd", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_BSHD) != 0, 1);
     expect("caps.local window", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW) != 0, 1);
@@ -117,7 +118,7 @@ int main() {
     p = good(); p.causal = 0; p.window_right = 0;
     expect("right window without causal", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
     p = good(); p.softcap = 1.0f;
-    expect("softcap", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
+    expect("softcap", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
     p = good(); p.dropout_p = 0.1f;
     expect("dropout", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
     p = good(); p.dtype = SHAOBO_FA3_DTYPE_FP8;

@@ -33,13 +33,14 @@ class Problem:
     """Seeded (or closed-form) inputs plus the oracle's answers."""
 
     def __init__(self, b, hq, hkv, s, d, dtype, causal, seed=None, scale=None, sk=None, layout="bhsd",
-                 window=(-1, -1)):
+                 window=(-1, -1), softcap=0.0):
         """s: query length; sk: key length when it differs; layout: how the device tensors are laid
         out ("bhsd" or "bshd") -- the oracle always works on [B,H,S,D]."""
         self.b, self.hq, self.hkv, self.s, self.d = b, hq, hkv, s, d
         self.sk = s if sk is None else sk
         self.layout = layout
         self.window = window
+        self.softcap = float(softcap)
         self.dtype, self.causal = dtype, causal
         self.scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
         if seed is None:
@@ -47,7 +48,7 @@ class Problem:
             self.q, self.k, self.v, self.do = golden.pattern_inputs(b, hq, hkv, s, d)
         else:
             self.q, self.k, self.v, self.do = golden.seeded_inputs(seed, b, hq, hkv, s, d, dtype, sk=self.sk)
-        self.ref = golden.backward(self.q, self.k, self.v, self.do, causal, self.scale, dtype, window)
+        self.ref = golden.backward(self.q, self.k, self.v, self.do, causal, self.scale, dtype, window, self.softcap)
 
     def to_layout(self, x: np.ndarray) -> np.ndarray:
         """[B,H,S,D] -> the device layout of this problem."""
@@ -68,7 +69,7 @@ def run_v2(prob: Problem, deterministic=False, pass_scale=True, poison_ws=True):
     x = prob.device_inputs()
     p = ops.make_params(x["q"], x["k"], prob.causal, prob.scale if pass_scale else None, layout=prob.layout,
                         deterministic=int(deterministic), sync_after_launch=1,
-                        window_left=prob.window[0], window_right=prob.window[1])
+                        window_left=prob.window[0], window_right=prob.window[1], softcap=prob.softcap)
     need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
     assert need > 0
     ws = torch.full((need,), 0xFF if poison_ws else 0, dtype=torch.uint8, device="cuda")

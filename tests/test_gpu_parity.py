@@ -117,9 +117,9 @@ def test_errors_do_not_launch():
     assert call(p) == capi.STATUS_INVALID_VALUE  # short workspace
     p.workspace_bytes = need
     assert call(p, lse=None) == capi.STATUS_INVALID_VALUE
-    p.softcap = 1.0
+    p.dropout_p = 0.5
     assert call(p) == capi.STATUS_UNSUPPORTED
-    p.softcap = 0.0
+    p.dropout_p = 0.0
     p.struct_size = 100
     assert call(p) == capi.STATUS_INVALID_VALUE
     torch.cuda.synchronize()

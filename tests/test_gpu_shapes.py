@@ -5,6 +5,8 @@ shaobo_fa3_bwd_v2 with NaN-poisoned outputs and workspace."""
 import numpy as np
 import pytest
 
+from oracle import golden
+
 from tests.helpers import Problem, assert_parity, run_v2
 
 pytestmark = pytest.mark.gpu
@@ -90,3 +92,31 @@ def test_a_window_that_covers_everything_is_the_plain_mask():
     ra, rb = run_v2(plain, deterministic=True), run_v2(wide, deterministic=True)
     for name in ("dq", "dk", "dv"):
         assert np.array_equal(ra[name], rb[name]), name
+
+
+# (b, hq, hkv, sq, sk, d, dtype, causal, window, softcap)
+SOFTCAP_CASES = [
+    (1, 4, 4, 512, 512, 128, "bf16", True, (-1, -1), 30.0),
+    (2, 4, 2, 384, 384, 64, "fp16", False, (-1, -1), 5.0),
+    (1, 2, 2, 300, 700, 128, "fp16", True, (100, -1), 2.0),
+    (1, 40, 40, 512, 512, 64, "fp16", True, (-1, -1), 50.0),    # >= 148 key tiles: unsplit path
+]
+
+
+@pytest.mark.parametrize("b,hq,hkv,sq,sk,d,dtype,causal,window,softcap", SOFTCAP_CASES)
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_softcap(b, hq, hkv, sq, sk, d, dtype, causal, window, softcap, deterministic):
+    """Scores capped with softcap * tanh(x / softcap): backward against the oracle, and the forward kernel
+    must reproduce the O and LSE the backward was fed."""
+    from flash_attention3_b200 import ops
+    from tests.helpers import host
+    prob = Problem(b, hq, hkv, sq, d, dtype, causal, seed=900 + sq + sk, sk=sk, window=window, softcap=softcap)
+    res = run_v2(prob, deterministic=deterministic)
+    assert_parity(res, prob, label=f"{(b, hq, hkv, sq, sk, d, dtype, causal, window, softcap, deterministic)}")
+    if not deterministic:
+        x = prob.device_inputs()
+        out, lse = ops.fa3_fwd(x["q"], x["k"], x["v"], causal, prob.scale, window=window, softcap=softcap, sync=True)
+        assert golden.check_gradient(host(out), prob.ref["out"], dtype)["pass"]
+        ref_lse = prob.ref["lse"]
+        finite = np.isfinite(ref_lse)
+        assert np.abs(host(lse)[finite] - ref_lse[finite]).max() <= 3e-3
