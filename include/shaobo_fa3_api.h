@@ -137,7 +137,7 @@ typedef struct ShaoboFa3Params {
     const int32_t* seqused_k;      /* 256 */
     int64_t total_q;               /* 264 */
     int64_t total_k;               /* 272 */
-    float softcap;                 /* 280  must be 0 */
+    float softcap;                 /* 280  0 = off; > 0: scores capped with softcap*tanh(x/softcap) */
     int32_t deterministic;         /* 284  0 or 1; 1 selects the atomic-free split path */
     int32_t sm_margin;             /* 288  must be 0 */
     int32_t softmax_scale_is_set;  /* 292  0 -> scale = 1/sqrt(head_dim_qk) */
