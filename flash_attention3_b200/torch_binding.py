@@ -8,7 +8,8 @@ reference docs/tridao_fa3_bwd_api.md:48-55, and never shipped).
 * ``attention`` - an ``autograd.Function`` over the two ops, so that the library can be driven from
   ``loss.backward()``.
 
-Tensors are BHSD, contiguous, fp16 or bf16, on a CUDA device; there is no CPU path.
+Tensors are contiguous [B,H,S,D] (or [B,S,H,D] with layout="bshd"), fp16 or bf16, on a CUDA device;
+there is no CPU path.  Sliding windows and softcap are passed through to the kernels.
 """
 from __future__ import annotations
 
@@ -20,46 +21,55 @@ from . import ops
 @torch.library.custom_op("fa3b200::attention_bwd", mutates_args=(), device_types="cuda")
 def attention_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                   softmax_lse: torch.Tensor, causal: bool, softmax_scale: float,
-                  deterministic: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                  deterministic: bool, window_left: int = -1, window_right: int = -1, softcap: float = 0.0,
+                  layout: str = "bhsd") -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     dq, dk, dv = ops.fa3_bwd(dout.contiguous(), q, k, v, out, softmax_lse, causal, softmax_scale,
-                             deterministic=deterministic)
+                             deterministic=deterministic, window=(window_left, window_right), softcap=softcap,
+                             layout=layout)
     return dq, dk, dv
 
 
 @attention_bwd.register_fake
-def _(dout, q, k, v, out, softmax_lse, causal, softmax_scale, deterministic):
+def _(dout, q, k, v, out, softmax_lse, causal, softmax_scale, deterministic, window_left=-1, window_right=-1,
+      softcap=0.0, layout="bhsd"):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
 @torch.library.custom_op("fa3b200::attention_fwd", mutates_args=(), device_types="cuda")
-def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool,
-                  softmax_scale: float) -> tuple[torch.Tensor, torch.Tensor]:
-    out, lse = ops.fa3_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, softmax_scale)
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, softmax_scale: float,
+                  window_left: int = -1, window_right: int = -1, softcap: float = 0.0,
+                  layout: str = "bhsd") -> tuple[torch.Tensor, torch.Tensor]:
+    out, lse = ops.fa3_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, softmax_scale,
+                           window=(window_left, window_right), softcap=softcap, layout=layout)
     return out, lse
 
 
 @attention_fwd.register_fake
-def _(q, k, v, causal, softmax_scale):
-    return torch.empty_like(q), q.new_empty(q.shape[:3], dtype=torch.float32)
+def _(q, k, v, causal, softmax_scale, window_left=-1, window_right=-1, softcap=0.0, layout="bhsd"):
+    b, h, s = (q.shape[0], q.shape[2], q.shape[1]) if layout == "bshd" else q.shape[:3]
+    return torch.empty_like(q), q.new_empty((b, h, s), dtype=torch.float32)
 
 
 class _Attention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, softmax_scale, deterministic):
+    def forward(ctx, q, k, v, causal, softmax_scale, deterministic, window, softcap, layout):
         scale = softmax_scale if softmax_scale is not None else ops.default_scale(q.shape[-1])
-        out, lse = torch.ops.fa3b200.attention_fwd(q, k, v, causal, scale)
+        out, lse = torch.ops.fa3b200.attention_fwd(q, k, v, causal, scale, window[0], window[1], softcap, layout)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.causal, ctx.scale, ctx.deterministic = causal, scale, deterministic
+        ctx.window, ctx.softcap, ctx.layout = window, softcap, layout
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
         dq, dk, dv = torch.ops.fa3b200.attention_bwd(dout, q, k, v, out, lse, ctx.causal, ctx.scale,
-                                                     ctx.deterministic)
-        return dq, dk, dv, None, None, None
+                                                     ctx.deterministic, ctx.window[0], ctx.window[1],
+                                                     ctx.softcap, ctx.layout)
+        return dq, dk, dv, None, None, None, None, None, None
 
 
-def attention(q, k, v, causal: bool = False, softmax_scale: float | None = None, deterministic: bool = False):
-    """softmax(q k^T * scale) v with this library's backward behind autograd (BHSD tensors)."""
-    return _Attention.apply(q, k, v, causal, softmax_scale, deterministic)
+def attention(q, k, v, causal: bool = False, softmax_scale: float | None = None, deterministic: bool = False,
+              window=(-1, -1), softcap: float = 0.0, layout: str = "bhsd"):
+    """softmax(q k^T * scale) v with this library's forward and backward behind autograd."""
+    return _Attention.apply(q, k, v, causal, softmax_scale, deterministic, tuple(window), float(softcap), layout)

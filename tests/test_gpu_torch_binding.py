@@ -107,3 +107,18 @@ def test_host_tensor_entry_point_of_the_library():
         for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
             m = golden.check_gradient(t.float().numpy(), prob.ref[name], "bf16")
             assert m["pass"], (shape, name, m)
+
+
+def test_autograd_with_window_softcap_and_bshd():
+    from flash_attention3_b200 import torch_binding
+    prob = helpers.Problem(2, 4, 2, 320, 64, "fp16", True, seed=306, window=(96, -1), softcap=8.0, layout="bshd")
+    x = prob.device_inputs()
+    q, k, v = (x[n].clone().requires_grad_(True) for n in ("q", "k", "v"))
+    out = torch_binding.attention(q, k, v, causal=True, softmax_scale=prob.scale, window=(96, -1), softcap=8.0,
+                                  layout="bshd")
+    assert golden.check_gradient(prob.from_layout(helpers.host(out)), prob.ref["out"], "fp16")["pass"]
+    out.backward(x["dout"])
+    torch.cuda.synchronize()
+    for name, grad in (("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
+        m = golden.check_gradient(prob.from_layout(helpers.host(grad)), prob.ref[name], "fp16")
+        assert m["pass"], (name, m)
