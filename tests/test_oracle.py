@@ -179,3 +179,33 @@ def test_oracle_matches_textbook_float64_on_widened_masks(sq, sk, causal, window
     assert np.abs(got["lse"][0, 0][finite] - lse[finite]).max() < 1e-5
     for name, ref in (("dq", dq), ("dk", dk), ("dv", dv)):
         assert np.abs(got[name][0, 0] - ref).max() < 2e-3, name
+
+
+def test_oracle_softcap_gradients_match_finite_differences():
+    """softcap * tanh(x / softcap) is not in the reference: the oracle's gradients for it are checked
+    against central differences of a float64 forward."""
+    sq, sk, d, cap, scale = 6, 7, 8, 2.0, 0.6
+    q, k, v, do = golden.seeded_inputs(3, 1, 1, 1, sq, d, "fp16", sk=sk)
+    got = golden.backward(q, k, v, do, True, scale, "fp16", (-1, -1), cap)
+    Q, K, V, DO = (x[0, 0].astype(np.float64) for x in (q, k, v, do))
+    i = np.arange(sq)[:, None]
+    j = np.arange(sk)[None, :]
+
+    def forward(Q, K, V):
+        z = cap * np.tanh(Q @ K.T * scale / cap)
+        z = np.where(j <= i + sk - sq, z, -np.inf)
+        p = np.exp(z - z.max(axis=1, keepdims=True))
+        return (p / p.sum(axis=1, keepdims=True)) @ V
+
+    def numeric(f, X, eps=1e-6):
+        g = np.zeros_like(X)
+        for idx in np.ndindex(X.shape):
+            hi, lo = X.copy(), X.copy()
+            hi[idx] += eps
+            lo[idx] -= eps
+            g[idx] = ((f(hi) - f(lo)) * DO).sum() / (2 * eps)
+        return g
+
+    assert np.abs(got["dq"][0, 0] - numeric(lambda X: forward(X, K, V), Q)).max() < 2e-3
+    assert np.abs(got["dk"][0, 0] - numeric(lambda X: forward(Q, X, V), K)).max() < 2e-3
+    assert np.abs(got["dv"][0, 0] - numeric(lambda X: forward(Q, K, X), V)).max() < 1e-5
