@@ -29,7 +29,14 @@
 namespace fa3b200 {
 
 struct DqArgs {
-    const float* sidecar;  // [B,Hq,Sq,3]
+    // Row statistics: the packed sidecar [B,Hq,Sq,3] = {m, r, delta}, or, when it is null, the three
+    // arrays of the reference's calling convention (reference src/dq_kernel.cpp:1515-1549): aux0 and
+    // aux1 = row maximum of the unscaled scores and row sum (or aux0 = log-sum-exp and aux1 = null),
+    // and delta, each [B,Hq,Sq].
+    const float* sidecar;
+    const float* aux0;
+    const float* aux1;
+    const float* delta;
     void* dq;              // [B,Hq,Sq,D] or [B,Sq,Hq,D], see q_strides
     TensorStrides q_strides;  // element strides of dq
     int batch;
@@ -245,9 +252,25 @@ dq_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const int qi = q_row + i;  // query row inside the head
             const bool q_valid = qi < band.seqlen_q;
             // rows past the end of the sequence: P = exp2(-inf) = 0
-            const float* side = a.sidecar + (int64_t(b_coord * a.heads_q + hq) * a.sidecar_rows + q_base + (q_valid ? qi : 0)) * 3;
-            const float neg = q_valid ? __log2f(side[1]) - side[0] : -INFINITY;
-            const float delta = q_valid ? side[2] : 0.0f;
+            // P = exp2(x - m) * r = exp2(x + (log2 r - m)); a row that saw no key (m = -inf or r = 0) gets -inf
+            const int64_t stat_row = int64_t(b_coord * a.heads_q + hq) * a.sidecar_rows + q_base + (q_valid ? qi : 0);
+            float neg = -INFINITY, delta = 0.0f;
+            if (q_valid) {
+                if (a.sidecar != nullptr) {
+                    const float* side = a.sidecar + stat_row * 3;
+                    neg = __log2f(side[1]) - side[0];
+                    delta = side[2];
+                } else {
+                    const float x = a.aux0[stat_row];
+                    if (a.aux1 == nullptr) {
+                        neg = x == -INFINITY ? -INFINITY : -x * 1.44269504088896340736f;
+                    } else {
+                        const float sum = a.aux1[stat_row];
+                        neg = (x == -INFINITY || sum == 0.0f) ? -INFINITY : -__log2f(sum) - x * a.scale_log2;
+                    }
+                    delta = a.delta[stat_row];
+                }
+            }
             uint32_t ppk[64];
             bool ok = true;
 #pragma unroll 1

@@ -153,11 +153,13 @@ SplitPlan split_plan(const ShaoboFa3Params* p) {
 }
 
 size_t dkv_accum_bytes(const ShaoboFa3Params* p) {
-    if (split_plan(p).chunk_steps == 0) return 0;
+    const SplitPlan plan = split_plan(p);
+    if (plan.chunk_steps == 0) return 0;
+    // one dK slab and one dV slab of [128 rows][D] fp32 per CTA
     size_t n = size_t(p->batch), out = 0;
-    if (!mul_ok(n, size_t(p->num_heads_kv), &n) || !mul_ok(n, size_t(p->seqlen_k), &n) ||
-        !mul_ok(n, size_t(p->head_dim_qk), &n) || !mul_ok(n, 2 * sizeof(float), &n) ||
-        !round_up_256(n, &out)) {
+    if (!mul_ok(n, size_t(p->num_heads_kv), &n) || !mul_ok(n, size_t(plan.chunks_per_head), &n) ||
+        !mul_ok(n, size_t(kSequenceAlignment), &n) || !mul_ok(n, size_t(p->head_dim_qk), &n) ||
+        !mul_ok(n, 2 * sizeof(float), &n) || !round_up_256(n, &out)) {
         return 0;
     }
     return out;

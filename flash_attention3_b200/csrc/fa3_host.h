@@ -65,8 +65,8 @@ size_t dq_accum_bytes(const ShaoboFa3Params* p);
 
 // Splitting of key tiles on small problems.  Shapes with fewer (batch x KV head x key tile) units
 // than a B200 has SMs would leave most of the chip idle, so the query steps of every key tile are
-// cut into chunks of `chunk_steps` steps, one CTA per chunk, whose dK/dV partial sums meet in fp32
-// accumulators.  The chunk size is the smallest one whose CTA count still fits one wave of 148
+// cut into chunks of `chunk_steps` steps, one CTA per chunk; every CTA writes its dK/dV partial sums
+// to its own fp32 slab and the convert kernel adds the slabs of a tile in chunk order.  The chunk size is the smallest one whose CTA count still fits one wave of 148
 // SMs.  The decision depends on the parameters only, so the workspace formula and the launch
 // always agree.  The deterministic path never splits.
 constexpr int kSplitSmCount = 148;
@@ -76,13 +76,13 @@ struct SplitPlan {
 };
 SplitPlan split_plan(const ShaoboFa3Params* p);
 
-// Bytes of the two fp32 accumulators [B,Hkv,S,D] (dK then dV) that split tiles add into; 0 when
-// tiles are not split.
+// Bytes of the per-CTA partial-sum slabs of split tiles (one dK and one dV slab of [128][D] fp32
+// per CTA); 0 when tiles are not split.
 size_t dkv_accum_bytes(const ShaoboFa3Params* p);
 
 // Carving of the caller's workspace by shaobo_fa3_bwd_v2:
 //   [0, dq_accum)                fp32 dQ accumulator
-//   [dq_accum, +dkv_accum)       fp32 dK and dV accumulators (only when tiles are split)
+//   [dq_accum, +dkv_accum)       fp32 dK / dV partial-sum slabs (only when tiles are split)
 //   [delta_offset, +rows*4)      delta, used when softmax_d is NULL
 //   [sidecar_offset, +rows*12)   packed sidecar
 // Each region starts on a 256-byte boundary.

@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <map>
@@ -159,15 +160,21 @@ struct DeviceOnce {
 
 // Optional per-stage timing of shaobo_fa3_bwd_v2 (off by default): when
 // enabled, four events bracket the three launches of a call on its stream.
+// A benchmarking aid for one timed call at a time: the events are shared, so calls from several
+// host threads while timing is on record over each other (the mutex only keeps the bookkeeping
+// itself consistent).  Off, it costs every call one relaxed atomic load per launch.
 struct StageTimer {
-    bool enabled = false;
+    std::atomic<bool> enabled{false};
+    std::mutex mu;  // guards valid and ev
     bool valid = false;
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
 };
 StageTimer g_stage_timer;
 
 void stage_mark(int i, cudaStream_t st) {
-    if (g_stage_timer.enabled && g_stage_timer.ev[i] != nullptr) {
+    if (!g_stage_timer.enabled.load(std::memory_order_relaxed)) return;
+    std::lock_guard<std::mutex> lock(g_stage_timer.mu);
+    if (g_stage_timer.enabled.load(std::memory_order_relaxed) && g_stage_timer.ev[i] != nullptr) {
         cudaEventRecord(g_stage_timer.ev[i], st);
         if (i == 3) g_stage_timer.valid = true;
     }
@@ -201,29 +208,27 @@ int finish(const ShaoboFa3Params* p, bool sync) {
 // ------------------------------------------------------------------ delta
 template <typename T, int D>
 void launch_delta_t(const void* dout, const void* out, const float* aux0, const float* aux1,
-                    float* delta, float* sidecar, float* zero_rows, float* zero_extra,
-                    int64_t zero_extra_bytes, int64_t rows, bool lse, float scale_log2,
-                    const RowLayout& layout, cudaStream_t st) {
+                    float* delta, float* sidecar, float* zero_rows, int64_t rows, bool lse,
+                    float scale_log2, const RowLayout& layout, cudaStream_t st) {
     constexpr int kRowsPerBlock = 8 * (32 / (D / 8));
     int64_t blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
     const int64_t cap = int64_t(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
-    float4* ze = reinterpret_cast<float4*>(zero_extra);
-    const int64_t ze_n = zero_extra != nullptr ? zero_extra_bytes / 16 : 0;
     if (lse) {
         delta_sidecar_kernel<T, D, true><<<int(blocks), 256, 0, st>>>(
             static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
-            zero_rows, ze, ze_n, rows, scale_log2, layout);
+            zero_rows, rows, scale_log2, layout);
     } else {
         delta_sidecar_kernel<T, D, false><<<int(blocks), 256, 0, st>>>(
             static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
-            zero_rows, ze, ze_n, rows, scale_log2, layout);
+            zero_rows, rows, scale_log2, layout);
     }
 }
 
+// sidecar may be null (only delta is written); zero_rows, when non-null, is the fp32 dQ accumulator
+// that the same pass clears.
 void launch_delta(const ShaoboFa3Params* p, const void* dout, const void* out, const float* aux0,
-                  const float* aux1, float* delta, float* sidecar, float* zero_rows, bool lse,
-                  float* zero_extra = nullptr, int64_t zero_extra_bytes = 0) {
+                  const float* aux1, float* delta, float* sidecar, float* zero_rows, bool lse) {
     const TensorShape shape = shape_of(p);
     const int64_t rows = int64_t(shape.batch) * p->num_heads_q * shape.rows_q;
     const float scale_log2 = p->softmax_scale * kLog2E;
@@ -231,19 +236,19 @@ void launch_delta(const ShaoboFa3Params* p, const void* dout, const void* out, c
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const RowLayout layout = row_layout(p, p->num_heads_q, shape.rows_q, shape.bshd);
     if (p->head_dim_qk == 128) {
-        if (bf) launch_delta_t<__nv_bfloat16, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
-        else launch_delta_t<__half, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
+        if (bf) launch_delta_t<__nv_bfloat16, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, layout, st);
+        else launch_delta_t<__half, 128>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, layout, st);
     } else {
-        if (bf) launch_delta_t<__nv_bfloat16, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
-        else launch_delta_t<__half, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, zero_extra, zero_extra_bytes, rows, lse, scale_log2, layout, st);
+        if (bf) launch_delta_t<__nv_bfloat16, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, layout, st);
+        else launch_delta_t<__half, 64>(dout, out, aux0, aux1, delta, sidecar, zero_rows, rows, lse, scale_log2, layout, st);
     }
 }
 
 // ---------------------------------------------------------------- convert
-// dq = T(scale * dq_accum); with split tiles also dk = T(dk_accum), dv = T(dv_accum) (the scale of
-// dK was applied before its partial sums were added).
+// dq = T(scale * dq_accum); with split tiles also dk, dv = T(sum of the slabs of each key tile) (the
+// scale of dK was applied before the partial sums were written).
 void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
-                    const float* dkv_accum = nullptr, void* dk = nullptr, void* dv = nullptr) {
+                    const float* dkv_slabs = nullptr, void* dk = nullptr, void* dv = nullptr) {
     ConvertSegments seg{};
     seg.src[0] = accum;
     seg.dst[0] = dq;
@@ -254,16 +259,29 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
     seg.head_dim = p->head_dim_qk;
     seg.count = 1;
     int64_t total = seg.n_vec8[0];
-    if (dkv_accum != nullptr) {
+    const SplitPlan split = dkv_slabs != nullptr ? split_plan(p) : SplitPlan{};
+    if (split.chunk_steps > 0) {
         const int64_t n = int64_t(shape.batch) * p->num_heads_kv * shape.rows_k * p->head_dim_qk;
-        seg.src[1] = dkv_accum;
         seg.dst[1] = dk;
-        seg.src[2] = dkv_accum + n;
         seg.dst[2] = dv;
         seg.n_vec8[1] = seg.n_vec8[2] = n / 8;
         seg.scale[1] = seg.scale[2] = 1.0f;
         seg.layout[1] = seg.layout[2] = row_layout(p, p->num_heads_kv, shape.rows_k, shape.bshd);
         seg.count = 3;
+        seg.slabs = dkv_slabs;
+        seg.rows_k = shape.rows_k;
+        seg.chunks_per_head = split.chunks_per_head;
+        // the chunk list of a head, as the GEMM kernel numbers its CTAs: key tile 0 first
+        const Band band = band_of(p);
+        const int group = p->num_heads_q / p->num_heads_kv;
+        const int tiles = tiles_of(p->seqlen_k);
+        int next = 0;
+        for (int kt = 0; kt < tiles && kt < kMaxSplitTiles; ++kt) {
+            seg.chunk_begin[kt] = static_cast<unsigned short>(next);
+            const int steps = group * q_tiles_of_k_tile(kt, band);
+            next += (steps + split.chunk_steps - 1) / split.chunk_steps;
+        }
+        seg.chunk_begin[tiles] = static_cast<unsigned short>(next);
         total += 2 * (n / 8);
     }
     int64_t blocks = (total + 255) / 256;  // one 8-element vector per thread while the grid allows it
@@ -289,9 +307,8 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
 // ------------------------------------------------------- fused / dKV kernel
 template <typename T, int D, bool kCausal, bool kWithDq, typename TOut, bool kSoftcap = false>
 int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                   const CUtensorMap& mdo, const CUtensorMap& mdq, const CUtensorMap& mdk,
-                   const CUtensorMap& mdv, const FusedArgs& args, int blocks, cudaStream_t st,
-                   bool pdl) {
+                   const CUtensorMap& mdo, const CUtensorMap& mdq, const FusedArgs& args, int blocks,
+                   cudaStream_t st, bool pdl) {
     auto kernel = fused_bwd_kernel<T, D, kCausal, kWithDq, TOut, kSoftcap>;
     static DeviceOnce configured;  // per instantiation and device
     if (!configured.done()) {
@@ -313,7 +330,7 @@ int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
     attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, mdo, mdq, mdk, mdv, args) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, mdo, mdq, args) != cudaSuccess) {
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
     return SHAOBO_FA3_STATUS_SUCCESS;
@@ -322,35 +339,41 @@ int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 template <typename T, bool kWithDq, typename TOut>
 int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorMap& mk,
                    const CUtensorMap& mv, const CUtensorMap& mdo, const CUtensorMap& mdq,
-                   const CUtensorMap& mdk, const CUtensorMap& mdv, const FusedArgs& args, int blocks,
-                   bool pdl) {
+                   const FusedArgs& args, int blocks, bool pdl) {
     cudaStream_t st = stream_of(p);
     const bool banded = needs_general_form(p);
     if (p->softcap > 0.0f) {  // softcapped scores: general form only
         return p->head_dim_qk == 128
-                   ? launch_fused_t<T, 128, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
-                   : launch_fused_t<T, 64, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
+                   ? launch_fused_t<T, 128, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl)
+                   : launch_fused_t<T, 64, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl);
     }
     if (p->head_dim_qk == 128) {
-        return banded ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
-                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
+        return banded ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl)
+                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl);
     }
-    return banded ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
-                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
+    return banded ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl)
+                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl);
 }
+
+// Row statistics of a launch: the packed sidecar, or (v2 entry) the caller's log-sum-exp plus the
+// delta array, which the GEMM kernel then reads directly.
+struct RowStats {
+    const float* sidecar = nullptr;
+    const float* lse = nullptr;
+    const float* delta = nullptr;
+};
 
 // with_dq: fused five-GEMM kernel writing dK/dV in the input dtype and adding
 // dQ into dq_accum (already zero).  !with_dq: four-GEMM dK/dV kernel with fp32
 // outputs (split path).
-// dkv_accum non-null (fused path only): key tiles are split as split_plan(p) says and their
-// dK/dV partial sums are reduce-added into dkv_accum ([dK | dV], fp32, already zero) instead of
-// being written to dk / dv.
+// dkv_slabs non-null (fused path only): key tiles are split as split_plan(p) says and every CTA
+// writes its partial dK/dV to its own pair of fp32 slabs instead of dk / dv.
 // Everything the launch of the five-GEMM / dK-dV kernel needs, built on the host ahead of time: the
 // v2 entry prepares it before it launches the delta kernel, so that the GPU does not sit idle
-// between the two launches while the host encodes seven tensor maps.
+// between the two launches while the host encodes the tensor maps.
 struct FusedLaunch {
     int status = SHAOBO_FA3_STATUS_SUCCESS;
-    CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
+    CUtensorMap mq, mk, mv, mdo, mdq;
     FusedArgs args;
     int blocks = 0;
     bool with_dq = false;
@@ -358,12 +381,12 @@ struct FusedLaunch {
 };
 
 FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
-                          const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
-                          bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr) {
+                          const void* v, const RowStats& stats, float* dq_accum, void* dk, void* dv,
+                          bool with_dq, bool dkv_f32 = false, float* dkv_slabs = nullptr) {
     FusedLaunch L;
     L.with_dq = with_dq;
     L.dkv_f32 = dkv_f32;
-    CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq, &mdk = L.mdk, &mdv = L.mdv;
+    CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq;
     FusedArgs& args = L.args;
     auto fail = [&](int status) {
         L.status = status;
@@ -374,7 +397,6 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
     const int d = p->head_dim_qk;
     const TensorShape shape = shape_of(p);
     const bool bshd = shape.bshd;
-    const int64_t kv_heads_total = int64_t(shape.batch) * p->num_heads_kv;
     if (!make_map_16(&mq, type, q, shape.batch, p->num_heads_q, shape.rows_q, d, bshd) ||
         !make_map_16(&mk, type, k, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd) ||
         !make_map_16(&mv, type, v, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd) ||
@@ -388,17 +410,7 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
     } else {
         mdq = mq;  // unused by the kernel
     }
-    const SplitPlan split = (with_dq && dkv_accum != nullptr) ? split_plan(p) : SplitPlan{};
-    if (split.chunk_steps > 0) {
-        const int64_t kv_elems = kv_heads_total * shape.rows_k * d;
-        if (!make_map_accum(&mdk, dkv_accum, kv_heads_total, shape.rows_k, d) ||
-            !make_map_accum(&mdv, dkv_accum + kv_elems, kv_heads_total, shape.rows_k, d)) {
-            return fail(SHAOBO_FA3_STATUS_HIP_ERROR);
-        }
-    } else {
-        mdk = mq;  // unused by the kernel
-        mdv = mq;
-    }
+    const SplitPlan split = (with_dq && dkv_slabs != nullptr) ? split_plan(p) : SplitPlan{};
     const int n_tiles = tiles_of(plan_seqlen_k(p));
     const Band band = band_of(p);
     const TileWork work = TileWork::of(band);
@@ -408,9 +420,12 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
     const long long dq_bytes_per_head =
         with_dq ? (long long)group * plan_seqlen_q(p) * p->head_dim_qk * 4 : 0;
     const CtaOrderPlan plan = cached_plan(work, bh, group, sm_count(), dq_bytes_per_head);
-    args.sidecar = sidecar;
+    args.sidecar = stats.sidecar;
+    args.lse = stats.lse;
+    args.delta = stats.delta;
     args.dk = dk;
     args.dv = dv;
+    args.dkv_slabs = dkv_slabs;
     // fp32 dK/dV of the split path are always [B,Hkv,Sk,D]; 16-bit outputs follow the layout of K/V
     args.kv_strides = strides_of(bshd && !dkv_f32, p->num_heads_kv, shape.rows_k, d);
     args.batch = p->batch;
@@ -440,25 +455,27 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
 int run_fused(const ShaoboFa3Params* p, const FusedLaunch& L, bool pdl) {
     if (L.status != SHAOBO_FA3_STATUS_SUCCESS) return L.status;
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
-    const CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq, &mdk = L.mdk, &mdv = L.mdv;
+    const CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq;
     const FusedArgs& args = L.args;
     const int blocks = L.blocks;
     if (L.with_dq) {
-        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
-                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
+        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl)
+                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl);
     }
     if (L.dkv_f32) {
-        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
-                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
+        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl)
+                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl);
     }
-    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
-              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
+    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl)
+              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl);
 }
 
 int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
                  const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
-                 bool with_dq, bool dkv_f32 = false, float* dkv_accum = nullptr, bool pdl = false) {
-    return run_fused(p, prepare_fused(p, dout, q, k, v, sidecar, dq_accum, dk, dv, with_dq, dkv_f32, dkv_accum), pdl);
+                 bool with_dq, bool dkv_f32 = false, float* dkv_slabs = nullptr, bool pdl = false) {
+    RowStats stats;
+    stats.sidecar = sidecar;
+    return run_fused(p, prepare_fused(p, dout, q, k, v, stats, dq_accum, dk, dv, with_dq, dkv_f32, dkv_slabs), pdl);
 }
 
 // -------------------------------------------------------------- dQ kernel
@@ -495,9 +512,11 @@ int launch_dq_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorM
                      : launch_dq_t<T, 64, false, TOut>(mq, mk, mv, mdo, args, blocks, st);
 }
 
-// Three-GEMM dQ kernel (split path).  out_f32 selects fp32 or input-dtype dq.
+// Three-GEMM dQ kernel (split path).  out_f32 selects fp32 or input-dtype dq.  The row statistics
+// are the packed sidecar, or (sidecar null) aux0 / aux1 / delta as three arrays.
 int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
-              const void* v, const float* sidecar, void* dq, bool out_f32) {
+              const void* v, const float* sidecar, void* dq, bool out_f32,
+              const float* aux0 = nullptr, const float* aux1 = nullptr, const float* delta = nullptr) {
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
     const CUtensorMapDataType type = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const int d = p->head_dim_qk;
@@ -512,6 +531,9 @@ int launch_dq(const ShaoboFa3Params* p, const void* dout, const void* q, const v
     }
     DqArgs args;
     args.sidecar = sidecar;
+    args.aux0 = aux0;
+    args.aux1 = aux1;
+    args.delta = delta;
     args.dq = dq;
     // fp32 dQ of the split path is always [B,Hq,Sq,D]; 16-bit dQ follows the layout of Q
     args.q_strides = strides_of(bshd && !out_f32, p->num_heads_q, shape.rows_q, d);
@@ -638,14 +660,21 @@ extern "C" int shaobo_fa3_b200_device_error(int clear) {
 // the current device and makes every following v2 call record them around its
 // three launches; enable == 0 stops recording and destroys them.
 extern "C" int shaobo_fa3_b200_stage_timing(int enable) {
-    if (enable != 0 && !g_stage_timer.enabled) {
+    std::lock_guard<std::mutex> lock(g_stage_timer.mu);
+    if (enable != 0 && !g_stage_timer.enabled.load()) {
         for (auto& e : g_stage_timer.ev) {
-            if (cudaEventCreate(&e) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
+            if (cudaEventCreate(&e) != cudaSuccess) {
+                for (auto& made : g_stage_timer.ev) {
+                    if (made != nullptr) cudaEventDestroy(made);
+                    made = nullptr;
+                }
+                return SHAOBO_FA3_STATUS_HIP_ERROR;
+            }
         }
-        g_stage_timer.enabled = true;
         g_stage_timer.valid = false;
-    } else if (enable == 0 && g_stage_timer.enabled) {
-        g_stage_timer.enabled = false;
+        g_stage_timer.enabled.store(true);
+    } else if (enable == 0 && g_stage_timer.enabled.load()) {
+        g_stage_timer.enabled.store(false);
         for (auto& e : g_stage_timer.ev) {
             cudaEventDestroy(e);
             e = nullptr;
@@ -658,7 +687,8 @@ extern "C" int shaobo_fa3_b200_stage_timing(int enable) {
 // fused path {delta, five-GEMM kernel, dQ convert}; deterministic path
 // {delta, dK/dV kernel, dQ kernel}.
 extern "C" int shaobo_fa3_b200_last_stage_ms(float* ms3) {
-    if (!g_stage_timer.enabled || !g_stage_timer.valid || ms3 == nullptr) {
+    std::lock_guard<std::mutex> lock(g_stage_timer.mu);
+    if (!g_stage_timer.enabled.load() || !g_stage_timer.valid || ms3 == nullptr) {
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     if (cudaEventSynchronize(g_stage_timer.ev[3]) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
@@ -670,23 +700,18 @@ extern "C" int shaobo_fa3_b200_last_stage_ms(float* ms3) {
     return SHAOBO_FA3_STATUS_SUCCESS;
 }
 
-#ifdef FA3B200_DEBUG_DUMP
-extern "C" int shaobo_fa3_b200_debug_cycles(long long* host_out, int clear) {
+#ifdef FA3B200_TRACE
+// Instrumented builds only: copy out (and clear) the per-CTA cycle stamps and the row-wise kernels'
+// first-start / last-end times.
+extern "C" int shaobo_fa3_b200_trace_read(long long* stamps, long long* rowwise) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    if (cudaMemcpyFromSymbol(host_out, g_debug_cycles, sizeof(long long) * 64) != cudaSuccess) return -1;
-    if (clear) {
-        long long zero[64] = {0};
-        cudaMemcpyToSymbol(g_debug_cycles, zero, sizeof(zero));
-    }
+    if (cudaMemcpyFromSymbol(stamps, g_trace, sizeof(long long) * kTraceCtas * 4 * kTraceEvents) != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(rowwise, g_trace_rowwise, sizeof(long long) * 4) != cudaSuccess) return -1;
+    static long long zeros[kTraceCtas * 4 * kTraceEvents];
+    cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
+    const long long init[4] = {0x7fffffffffffffffLL, 0, 0x7fffffffffffffffLL, 0};
+    cudaMemcpyToSymbol(g_trace_rowwise, init, sizeof(init));
     return 0;
-}
-extern "C" int shaobo_fa3_b200_debug_stamps(long long* host_out) {
-    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    return cudaMemcpyFromSymbol(host_out, g_debug_stamps, sizeof(long long) * 3 * 4 * 16) == cudaSuccess ? 0 : -1;
-}
-extern "C" int shaobo_fa3_b200_debug_dump(float* host_out) {
-    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    return cudaMemcpyFromSymbol(host_out, g_debug_dump, sizeof(float) * 3 * 128 * 128) == cudaSuccess ? 0 : -1;
 }
 #endif
 
@@ -728,16 +753,16 @@ extern "C" int shaobo_fa3_bwd_fused5(const void* dout, const void* q, const void
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     float* accum = static_cast<float*>(params->workspace);
-    float* dkv_accum = dkv_bytes != 0
+    float* dkv_slabs = dkv_bytes != 0
                            ? reinterpret_cast<float*>(static_cast<uint8_t*>(params->workspace) + dq_bytes)
                            : nullptr;
-    if (cudaMemsetAsync(accum, 0, need, stream_of(params)) != cudaSuccess) {
+    if (cudaMemsetAsync(accum, 0, dq_bytes, stream_of(params)) != cudaSuccess) {  // (the slabs are written, not added into)
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
     int status = launch_fused(params, dout, q, k, v, static_cast<const float*>(packed_sidecar),
-                              accum, dk, dv, true, false, dkv_accum);
+                              accum, dk, dv, true, false, dkv_slabs);
     if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
-    launch_convert(params, accum, dq, dkv_accum, dk, dv);
+    launch_convert(params, accum, dq, dkv_slabs, dk, dv);
     return finish(params, params->sync_after_launch != 0);
 }
 
@@ -772,22 +797,29 @@ extern "C" int shaobo_fa3_bwd_dq(const void* dout, const void* q, const void* k,
                                  const void* out, const void* aux0, const void* aux1, void* dq,
                                  void* dk, void* dv, const ShaoboFa3Params* params) {
     begin();
-    (void)out; (void)dk; (void)dv; (void)aux0; (void)aux1;
+    (void)out; (void)dk; (void)dv;
     if (params == nullptr) return SHAOBO_FA3_STATUS_INVALID_VALUE;
     if (params->dq_path == SHAOBO_FA3_DQ_PATH_REFERENCE) return SHAOBO_FA3_STATUS_NOT_IMPLEMENTED;
     if (params->dq_path != SHAOBO_FA3_DQ_PATH_CANONICAL || !stage_params_ok(params)) {
         return SHAOBO_FA3_STATUS_UNSUPPORTED;
     }
-    // The row statistics travel in the packed sidecar, like the dK/dV half;
-    // delta alone (reserved_ptr[0]) is not enough without the row maximum and
-    // sum, which the reference passes as aux0/aux1.  Both conventions are
-    // accepted: a sidecar in reserved_ptr[3] wins.
-    const void* sidecar = params->reserved_ptr[SHAOBO_FA3_RESERVED_PTR_SIDECAR];
+    // Two calling conventions.  The reference's (src/dq_kernel.cpp:1515-1549): row maximum and row
+    // sum in softmax_aux0 / softmax_aux1 (or the log-sum-exp and NULL when softmax_aux_mode is LSE)
+    // and delta in reserved_ptr[0]; when these are all given they are used, as in the reference.
+    // Otherwise the packed sidecar of the delta stage in reserved_ptr[3], like the dK/dV half.
+    const float* sidecar = static_cast<const float*>(params->reserved_ptr[SHAOBO_FA3_RESERVED_PTR_SIDECAR]);
+    const float* delta = static_cast<const float*>(params->reserved_ptr[SHAOBO_FA3_RESERVED_PTR_DELTA]);
+    const bool lse = params->softmax_aux_mode == SHAOBO_FA3_SOFTMAX_AUX_LSE;
+    const bool arrays_complete = aux0 != nullptr && (lse || aux1 != nullptr) && delta != nullptr;
     if (dout == nullptr || q == nullptr || k == nullptr || v == nullptr || dq == nullptr ||
-        sidecar == nullptr) {
+        (sidecar == nullptr && !arrays_complete)) {
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
-    const int status = launch_dq(params, dout, q, k, v, static_cast<const float*>(sidecar), dq, true);
+    const int status =
+        arrays_complete
+            ? launch_dq(params, dout, q, k, v, nullptr, dq, true, static_cast<const float*>(aux0),
+                        lse ? nullptr : static_cast<const float*>(aux1), delta)
+            : launch_dq(params, dout, q, k, v, sidecar, dq, true);
     if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
     return finish(params, params->sync_after_launch != 0);
 }
@@ -820,21 +852,26 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
 
     int status = SHAOBO_FA3_STATUS_SUCCESS;
     if (launch.deterministic == 0) {
-        // delta + sidecar, and the dQ accumulator is cleared in the same pass
+        // delta, and the dQ accumulator is cleared in the same pass.  The GEMM kernel reads the
+        // caller's log-sum-exp and delta directly, so only its dS phase and its dQ adds depend on
+        // the delta kernel; no sidecar is written on this path.
         cudaStream_t st = stream_of(&launch);
-        float* dkv_accum = ws.dkv_accum_bytes != 0
+        float* dkv_slabs = ws.dkv_accum_bytes != 0
                                ? reinterpret_cast<float*>(base + ws.dq_accum_bytes)
                                : nullptr;
+        RowStats stats;
+        stats.lse = static_cast<const float*>(softmax_lse);
+        stats.delta = delta;
         // host work of the second launch first, then the three launches back to back
-        const FusedLaunch fused = prepare_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true, false, dkv_accum);
+        const FusedLaunch fused = prepare_fused(&launch, dout, q, k, v, stats, accum, dk, dv, true, false, dkv_slabs);
         if (fused.status != SHAOBO_FA3_STATUS_SUCCESS) return fused.status;
         stage_mark(0, st);
         launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
-                     sidecar, accum, true, dkv_accum, int64_t(ws.dkv_accum_bytes));
+                     nullptr, accum, true);
         stage_mark(1, st);
         status = run_fused(&launch, fused, true);
         stage_mark(2, st);
-        if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq, dkv_accum, dk, dv);
+        if (status == SHAOBO_FA3_STATUS_SUCCESS) launch_convert(&launch, accum, dq, dkv_slabs, dk, dv);
         stage_mark(3, st);
     } else {
         // Atomic-free split path (bitwise reproducible): dK/dV by the four-GEMM
@@ -954,7 +991,8 @@ namespace {
 constexpr int kHostLanes = 3;
 
 struct HostLanes {
-    std::mutex mu;
+    std::mutex mu;             // guards creation
+    std::mutex enqueue[128];   // one call at a time enqueues on a device's lanes (see the entry point)
     bool ready[128] = {};
     cudaStream_t stream[128][kHostLanes] = {};
     cudaEvent_t fork[128] = {};
@@ -962,12 +1000,22 @@ struct HostLanes {
     bool get(int dev) {
         std::lock_guard<std::mutex> lock(mu);
         if (ready[dev]) return true;
-        if (cudaEventCreateWithFlags(&fork[dev], cudaEventDisableTiming) != cudaSuccess) return false;
-        for (int i = 0; i < kHostLanes; ++i) {
-            if (cudaStreamCreateWithFlags(&stream[dev][i], cudaStreamNonBlocking) != cudaSuccess ||
-                cudaEventCreateWithFlags(&join[dev][i], cudaEventDisableTiming) != cudaSuccess) {
-                return false;
+        bool ok = cudaEventCreateWithFlags(&fork[dev], cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; ok && i < kHostLanes; ++i) {
+            ok = cudaStreamCreateWithFlags(&stream[dev][i], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&join[dev][i], cudaEventDisableTiming) == cudaSuccess;
+        }
+        if (!ok) {  // give back what was made: the next call starts from nothing
+            if (fork[dev] != nullptr) cudaEventDestroy(fork[dev]);
+            fork[dev] = nullptr;
+            for (int i = 0; i < kHostLanes; ++i) {
+                if (stream[dev][i] != nullptr) cudaStreamDestroy(stream[dev][i]);
+                if (join[dev][i] != nullptr) cudaEventDestroy(join[dev][i]);
+                stream[dev][i] = nullptr;
+                join[dev][i] = nullptr;
             }
+            (void)cudaGetLastError();
+            return false;
         }
         ready[dev] = true;
         return true;
@@ -1107,6 +1155,12 @@ extern "C" int shaobo_fa3_b200_bwd_v2_host(const void* dout, const void* q, cons
     uint8_t* d_lse = d_dv + hs.kv_bytes;
     uint8_t* d_ws = d_lse + hs.lse_bytes;
 
+    // The fork and join events and the three lane streams are shared by every call on this device.
+    // A stream wait refers to the event's latest record at the moment the wait is enqueued, so one
+    // call's record -> wait pairs must not interleave with another call's: the whole enqueue (not the
+    // GPU work) runs under a per-device lock.  Calls from several host threads then queue up on the
+    // same lanes in lock order; each needs its own staging buffer.
+    std::lock_guard<std::mutex> enqueue_lock(g_host_lanes.enqueue[dev]);
     cudaStream_t caller = stream_of(params);
     if (cudaEventRecord(g_host_lanes.fork[dev], caller) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
     const int group = params->num_heads_q / params->num_heads_kv;
@@ -1115,54 +1169,64 @@ extern "C" int shaobo_fa3_b200_bwd_v2_host(const void* dout, const void* q, cons
     const size_t lse_head = size_t(params->seqlen_q) * sizeof(float);
     const int n = host_shard_count(params);
     bool used[kHostLanes] = {};
-    int piece_index = 0;
-    for (int r = 0; r < n; ++r) {
-        HostPiece pcs[3];
-        const int cnt = host_pieces(params, r, n, pcs);
-        for (int i = 0; i < cnt; ++i, ++piece_index) {
-            const int lane = piece_index % kHostLanes;
-            cudaStream_t st = g_host_lanes.stream[dev][lane];
-            if (!used[lane]) {
-                if (cudaStreamWaitEvent(st, g_host_lanes.fork[dev], 0) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
-                used[lane] = true;
-            }
-            const HostPiece& pc = pcs[i];
-            const size_t qh = size_t(pc.batch_begin) * params->num_heads_q + size_t(pc.kv_head_begin) * group;
-            const size_t kh = size_t(pc.batch_begin) * params->num_heads_kv + pc.kv_head_begin;
-            const size_t q_n = size_t(pc.batch_count) * pc.kv_head_count * group;  // query heads in the piece
-            const size_t k_n = size_t(pc.batch_count) * pc.kv_head_count;
-            auto h2d = [&](uint8_t* d, const void* h, size_t off, size_t bytes) {
-                return cudaMemcpyAsync(d + off, static_cast<const uint8_t*>(h) + off, bytes, cudaMemcpyHostToDevice, st) == cudaSuccess;
-            };
-            auto d2h = [&](void* h, const uint8_t* d, size_t off, size_t bytes) {
-                return cudaMemcpyAsync(static_cast<uint8_t*>(h) + off, d + off, bytes, cudaMemcpyDeviceToHost, st) == cudaSuccess;
-            };
-            if (!h2d(d_q, q, qh * q_head, q_n * q_head) || !h2d(d_k, k, kh * kv_head, k_n * kv_head) ||
-                !h2d(d_v, v, kh * kv_head, k_n * kv_head) || !h2d(d_do, dout, qh * q_head, q_n * q_head) ||
-                !h2d(d_out, out, qh * q_head, q_n * q_head) || !h2d(d_lse, softmax_lse, qh * lse_head, q_n * lse_head)) {
-                return SHAOBO_FA3_STATUS_HIP_ERROR;
-            }
-            ShaoboFa3Params s = piece_params(params, pc);
-            s.workspace = d_ws + size_t(lane) * hs.lane_ws;
-            s.workspace_bytes = hs.lane_ws;
-            s.reserved_ptr[SHAOBO_FA3_RESERVED_PTR_STREAM] = st;
-            const int status = shaobo_fa3_bwd_v2(d_do + qh * q_head, d_q + qh * q_head, d_k + kh * kv_head,
-                                                 d_v + kh * kv_head, d_out + qh * q_head, d_lse + qh * lse_head,
-                                                 d_dq + qh * q_head, d_dk + kh * kv_head, d_dv + kh * kv_head,
-                                                 nullptr, &s);
-            if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
-            if (!d2h(dq, d_dq, qh * q_head, q_n * q_head) || !d2h(dk, d_dk, kh * kv_head, k_n * kv_head) ||
-                !d2h(dv, d_dv, kh * kv_head, k_n * kv_head)) {
-                return SHAOBO_FA3_STATUS_HIP_ERROR;
+    auto enqueue_all = [&]() -> int {
+        int piece_index = 0;
+        for (int r = 0; r < n; ++r) {
+            HostPiece pcs[3];
+            const int cnt = host_pieces(params, r, n, pcs);
+            for (int i = 0; i < cnt; ++i, ++piece_index) {
+                const int lane = piece_index % kHostLanes;
+                cudaStream_t st = g_host_lanes.stream[dev][lane];
+                if (!used[lane]) {
+                    if (cudaStreamWaitEvent(st, g_host_lanes.fork[dev], 0) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
+                    used[lane] = true;
+                }
+                const HostPiece& pc = pcs[i];
+                const size_t qh = size_t(pc.batch_begin) * params->num_heads_q + size_t(pc.kv_head_begin) * group;
+                const size_t kh = size_t(pc.batch_begin) * params->num_heads_kv + pc.kv_head_begin;
+                const size_t q_n = size_t(pc.batch_count) * pc.kv_head_count * group;  // query heads in the piece
+                const size_t k_n = size_t(pc.batch_count) * pc.kv_head_count;
+                auto h2d = [&](uint8_t* d, const void* h, size_t off, size_t bytes) {
+                    return cudaMemcpyAsync(d + off, static_cast<const uint8_t*>(h) + off, bytes, cudaMemcpyHostToDevice, st) == cudaSuccess;
+                };
+                auto d2h = [&](void* h, const uint8_t* d, size_t off, size_t bytes) {
+                    return cudaMemcpyAsync(static_cast<uint8_t*>(h) + off, d + off, bytes, cudaMemcpyDeviceToHost, st) == cudaSuccess;
+                };
+                if (!h2d(d_q, q, qh * q_head, q_n * q_head) || !h2d(d_k, k, kh * kv_head, k_n * kv_head) ||
+                    !h2d(d_v, v, kh * kv_head, k_n * kv_head) || !h2d(d_do, dout, qh * q_head, q_n * q_head) ||
+                    !h2d(d_out, out, qh * q_head, q_n * q_head) || !h2d(d_lse, softmax_lse, qh * lse_head, q_n * lse_head)) {
+                    return SHAOBO_FA3_STATUS_HIP_ERROR;
+                }
+                ShaoboFa3Params s = piece_params(params, pc);
+                s.workspace = d_ws + size_t(lane) * hs.lane_ws;
+                s.workspace_bytes = hs.lane_ws;
+                s.reserved_ptr[SHAOBO_FA3_RESERVED_PTR_STREAM] = st;
+                const int status = shaobo_fa3_bwd_v2(d_do + qh * q_head, d_q + qh * q_head, d_k + kh * kv_head,
+                                                     d_v + kh * kv_head, d_out + qh * q_head, d_lse + qh * lse_head,
+                                                     d_dq + qh * q_head, d_dk + kh * kv_head, d_dv + kh * kv_head,
+                                                     nullptr, &s);
+                if (status != SHAOBO_FA3_STATUS_SUCCESS) return status;
+                if (!d2h(dq, d_dq, qh * q_head, q_n * q_head) || !d2h(dk, d_dk, kh * kv_head, k_n * kv_head) ||
+                    !d2h(dv, d_dv, kh * kv_head, k_n * kv_head)) {
+                    return SHAOBO_FA3_STATUS_HIP_ERROR;
+                }
             }
         }
-    }
+        return SHAOBO_FA3_STATUS_SUCCESS;
+    };
+    int status = enqueue_all();
+    // Whatever happened above, the caller's stream waits for everything that did get enqueued on the
+    // lanes: after an error return no copy into the caller's host buffers is left running unordered.
     for (int lane = 0; lane < kHostLanes; ++lane) {
         if (!used[lane]) continue;
         if (cudaEventRecord(g_host_lanes.join[dev][lane], g_host_lanes.stream[dev][lane]) != cudaSuccess ||
             cudaStreamWaitEvent(caller, g_host_lanes.join[dev][lane], 0) != cudaSuccess) {
-            return SHAOBO_FA3_STATUS_HIP_ERROR;
+            if (status == SHAOBO_FA3_STATUS_SUCCESS) status = SHAOBO_FA3_STATUS_HIP_ERROR;
         }
+    }
+    if (status != SHAOBO_FA3_STATUS_SUCCESS) {
+        (void)cudaGetLastError();
+        return status;
     }
     return finish(params, params->sync_after_launch != 0);
 }

@@ -50,8 +50,8 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
 // row is owned by D/8 adjacent lanes that each fetch one 16-byte vector of dO
 // and of O, so a warp reads 512 contiguous bytes per tensor per instruction.
 // When zero_rows is non-null the same lanes also clear the row of the fp32 dQ
-// accumulator (row pitch D floats), which saves a separate memset pass; a
-// second, unrelated range (zero_extra) can be cleared by the same launch.
+// accumulator (row pitch D floats), which saves a separate memset pass.  The
+// sidecar is optional (null: only delta is written).
 //
 // Rows are numbered in [batch, head, row] order (the order of aux0, delta and
 // the sidecar); RowLayout says where row r of dO and O lives, so that both the
@@ -81,8 +81,7 @@ __global__ void __launch_bounds__(256)
 delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
                      const float* __restrict__ aux0, const float* __restrict__ aux1,
                      float* __restrict__ delta, float* __restrict__ sidecar,
-                     float* __restrict__ zero_rows, float4* __restrict__ zero_extra,
-                     int64_t zero_extra_vec4, int64_t rows, float scale_log2, RowLayout layout) {
+                     float* __restrict__ zero_rows, int64_t rows, float scale_log2, RowLayout layout) {
     constexpr int kLanesPerRow = D / 8;
     constexpr int kRowsPerWarp = 32 / kLanesPerRow;
     const int lane = threadIdx.x & 31;
@@ -92,12 +91,9 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
     const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
     // let the GEMM kernel behind this one start its set-up (it waits before it reads our outputs)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    // optional second region to clear (the fp32 dK/dV accumulators of split tiles)
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_extra_vec4;
-         i += int64_t(gridDim.x) * blockDim.x) {
-        zero_extra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
+#ifdef FA3B200_TRACE
+    if (threadIdx.x == 0) atomicMin(reinterpret_cast<unsigned long long*>(&g_trace_rowwise[0]), (unsigned long long)trace_globaltimer());
+#endif
 
     // the loop bound is the same for every lane of a warp (the shuffles below need all 32 lanes);
     // lanes whose row lies past the end compute on zeros and write nothing
@@ -131,8 +127,8 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
                 z[col + i * kLanesPerRow] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        if (valid && col == 0) {
-            delta[row] = acc;
+        if (valid && col == 0) delta[row] = acc;
+        if (valid && col == 0 && sidecar != nullptr) {
             float m, r;
             if (kLseInput) {
                 m = aux0[row] * kLog2E;
@@ -152,25 +148,38 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
             s[2] = acc;
         }
     }
+#ifdef FA3B200_TRACE
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned long long*>(&g_trace_rowwise[1]), (unsigned long long)trace_globaltimer());
+#endif
 }
 
-// Up to three (fp32 accumulator -> storage dtype) conversions in one launch:
-// dQ (scaled) always; dK and dV as well when tiles were split.
+// Up to three (fp32 -> storage dtype) conversions in one launch: dQ (scaled) from its accumulator
+// always; dK and dV as well when key tiles were split.  A split tile's dK / dV is the sum of the
+// per-CTA slabs its chunks wrote ([128 rows][D] fp32 each, dK slab then dV slab per CTA), added here
+// in chunk order, so these two outputs do not depend on the order in which the CTAs ran.
+constexpr int kMaxSplitTiles = 148;  // tiles are only split while tiles x heads < 148
 struct ConvertSegments {
-    const float* src[3];   // fp32 [batch, head, row, D] contiguous
+    const float* src[3];   // [0]: fp32 dQ accumulator [batch, head, row, D] contiguous; [1],[2] unused
     void* dst[3];
     int64_t n_vec8[3];
     float scale[3];
     RowLayout layout[3];   // where the rows of dst live
     int count;
     int head_dim;
+    const float* slabs;    // count == 3: slab base; CTA x of the GEMM kernel owns slabs 2x (dK) and 2x+1 (dV)
+    int rows_k;            // key rows per (batch, KV head)
+    int chunks_per_head;   // CTAs per (batch, KV head)
+    unsigned short chunk_begin[kMaxSplitTiles + 1];  // first chunk of key tile kt inside its head
 };
 
 // dst[i] = T(scale * accum[i]).  8 elements per thread: 32 B in, 16 B out.
 // Algorithmic HBM bytes per element: 4 read + 2 written.
 template <typename T>
 __global__ void __launch_bounds__(256)
-dq_convert_kernel(const ConvertSegments seg) {
+dq_convert_kernel(const __grid_constant__ ConvertSegments seg) {
+#ifdef FA3B200_TRACE
+    if (threadIdx.x == 0) atomicMin(reinterpret_cast<unsigned long long*>(&g_trace_rowwise[2]), (unsigned long long)trace_globaltimer());
+#endif
     // launched programmatically behind the GEMM kernel: wait until all of it has completed
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // The segments form one index space, so that with enough blocks every thread makes a single
@@ -184,16 +193,43 @@ dq_convert_kernel(const ConvertSegments seg) {
         // (selects instead of indexing: the parameter arrays stay in constant memory)
         const int sgi = g < n0 ? 0 : (g < n01 ? 1 : 2);
         const int64_t i = g - (sgi == 0 ? 0 : (sgi == 1 ? n0 : n01));
-        const float* __restrict__ accum = sgi == 0 ? seg.src[0] : (sgi == 1 ? seg.src[1] : seg.src[2]);
         T* __restrict__ dst = static_cast<T*>(sgi == 0 ? seg.dst[0] : (sgi == 1 ? seg.dst[1] : seg.dst[2]));
         const float scale = sgi == 0 ? seg.scale[0] : (sgi == 1 ? seg.scale[1] : seg.scale[2]);
-        const uint4 lo = ld_stream_16B(accum + i * 8);
-        const uint4 hi = ld_stream_16B(accum + i * 8 + 4);
+        float v[8];
+        if (sgi == 0) {
+            const uint4 lo = ld_stream_16B(seg.src[0] + i * 8);
+            const uint4 hi = ld_stream_16B(seg.src[0] + i * 8 + 4);
+            v[0] = __uint_as_float(lo.x); v[1] = __uint_as_float(lo.y);
+            v[2] = __uint_as_float(lo.z); v[3] = __uint_as_float(lo.w);
+            v[4] = __uint_as_float(hi.x); v[5] = __uint_as_float(hi.y);
+            v[6] = __uint_as_float(hi.z); v[7] = __uint_as_float(hi.w);
+        } else {
+            // element (head, row, col) of dK / dV: add the slabs of the chunks of key tile row / 128
+            const int64_t row_all = i / vec_per_row;
+            const int col = int(i - row_all * vec_per_row) * 8;
+            const int64_t bh = row_all / seg.rows_k;
+            const int row = int(row_all - bh * seg.rows_k);
+            const int kt = row >> 7;
+            const int c0 = seg.chunk_begin[kt], c1 = seg.chunk_begin[kt + 1];
+            const int64_t slab_elems = int64_t(kTileRows) * seg.head_dim;
+            const float* src = seg.slabs + ((bh * seg.chunks_per_head + c0) * 2 + (sgi - 1)) * slab_elems +
+                               int64_t(row & 127) * seg.head_dim + col;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+            for (int c = c0; c < c1; ++c, src += 2 * slab_elems) {
+                const uint4 lo = ld_stream_16B(src);
+                const uint4 hi = ld_stream_16B(src + 4);
+                v[0] += __uint_as_float(lo.x); v[1] += __uint_as_float(lo.y);
+                v[2] += __uint_as_float(lo.z); v[3] += __uint_as_float(lo.w);
+                v[4] += __uint_as_float(hi.x); v[5] += __uint_as_float(hi.y);
+                v[6] += __uint_as_float(hi.z); v[7] += __uint_as_float(hi.w);
+            }
+        }
         uint4 o;
-        o.x = pack2<T>(__uint_as_float(lo.x) * scale, __uint_as_float(lo.y) * scale);
-        o.y = pack2<T>(__uint_as_float(lo.z) * scale, __uint_as_float(lo.w) * scale);
-        o.z = pack2<T>(__uint_as_float(hi.x) * scale, __uint_as_float(hi.y) * scale);
-        o.w = pack2<T>(__uint_as_float(hi.z) * scale, __uint_as_float(hi.w) * scale);
+        o.x = pack2<T>(v[0] * scale, v[1] * scale);
+        o.y = pack2<T>(v[2] * scale, v[3] * scale);
+        o.z = pack2<T>(v[4] * scale, v[5] * scale);
+        o.w = pack2<T>(v[6] * scale, v[7] * scale);
         // (the layout of a call is the same for all its segments up to heads and rows)
         const bool contiguous = seg.layout[0].contiguous != 0;
         if (contiguous) {
@@ -205,6 +241,9 @@ dq_convert_kernel(const ConvertSegments seg) {
             *reinterpret_cast<uint4*>(dst + row_offset(layout, row, seg.head_dim) + col) = o;
         }
     }
+#ifdef FA3B200_TRACE
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned long long*>(&g_trace_rowwise[3]), (unsigned long long)trace_globaltimer());
+#endif
 }
 
 }  // namespace fa3b200

@@ -17,6 +17,19 @@ class Fa3Error(RuntimeError):
         self.code = code
 
 
+class Fa3DeviceError(RuntimeError):
+    """A kernel gave up a bounded wait (1) or found its shared memory misaligned (2): its outputs are
+    not valid."""
+
+
+def _raise_on_device_error(lib, entry: str):
+    """After a synchronous call: read and clear the device-side error flag (the C entry points return
+    SUCCESS once the work is enqueued; a kernel that ran into trouble can only say so through the flag)."""
+    flag = lib.shaobo_fa3_b200_device_error(1)
+    if flag != 0:
+        raise Fa3DeviceError(f"{entry}: device error flag {flag}")
+
+
 def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
@@ -59,6 +72,33 @@ def _require_cuda(*tensors):
             raise RuntimeError("contiguous tensors are required ([B,H,S,D] or [B,S,H,D])")
 
 
+def _check_problem(q, k, v, layout, out=None, dout=None, softmax_lse=None):
+    """Shapes, dtypes and devices of one fixed-length problem: the C ABI takes raw pointers, so a
+    tensor of the wrong size would be read or written out of bounds."""
+    if q.dim() != 4 or k.dim() != 4:
+        raise ValueError("q and k must be 4-D ([B,H,S,D] or [B,S,H,D])")
+    if q.dtype not in _DTYPES:
+        raise TypeError(f"unsupported dtype {q.dtype}: fp16 or bf16")
+    if v.shape != k.shape:
+        raise ValueError(f"v {tuple(v.shape)} must have the shape of k {tuple(k.shape)}")
+    hq, hkv = (q.shape[2], k.shape[2]) if layout == "bshd" else (q.shape[1], k.shape[1])
+    sq = q.shape[1] if layout == "bshd" else q.shape[2]
+    if q.shape[0] != k.shape[0] or q.shape[3] != k.shape[3] or hkv == 0 or hq % hkv != 0:
+        raise ValueError(f"q {tuple(q.shape)} and k {tuple(k.shape)} do not describe one problem")
+    for name, t in (("k", k), ("v", v), ("out", out), ("dout", dout)):
+        if t is None:
+            continue
+        if t.dtype != q.dtype or t.device != q.device:
+            raise TypeError(f"{name} must have the dtype and device of q")
+        if name in ("out", "dout") and t.shape != q.shape:
+            raise ValueError(f"{name} {tuple(t.shape)} must have the shape of q {tuple(q.shape)}")
+    if softmax_lse is not None:
+        if softmax_lse.dtype != torch.float32 or softmax_lse.device != q.device:
+            raise TypeError("softmax_lse must be fp32 on the device of q")
+        if tuple(softmax_lse.shape) != (q.shape[0], hq, sq):
+            raise ValueError(f"softmax_lse {tuple(softmax_lse.shape)} must be [B,Hq,Sq] = {(q.shape[0], hq, sq)}")
+
+
 def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, deterministic=False,
             workspace=None, return_delta=False, sync=False, layout: str = "bhsd", window=(-1, -1),
             seqused_q=None, seqused_k=None, outputs=None, softcap: float = 0.0):
@@ -73,6 +113,7 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
     allocating.  Calls shaobo_fa3_bwd_v2.
     """
     _require_cuda(dout, q, k, v, out, softmax_lse)
+    _check_problem(q, k, v, layout, out, dout, softmax_lse)
     lib = capi.load()
     p = make_params(q, k, causal, softmax_scale, layout=layout, seqused_q=seqused_q, seqused_k=seqused_k,
                     softcap=float(softcap), deterministic=int(deterministic),
@@ -89,6 +130,9 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
     else:
         dq, dk, dv = outputs
         _require_cuda(dq, dk, dv)
+        for t, like in ((dq, q), (dk, k), (dv, v)):
+            if t.shape != like.shape or t.dtype != like.dtype or t.device != like.device:
+                raise ValueError("outputs must match q, k, v in shape, dtype and device")
     delta = (torch.empty((p.batch, p.num_heads_q, p.seqlen_q), dtype=torch.float32, device=q.device)
              if return_delta else None)
     with torch.cuda.device(q.device):
@@ -97,6 +141,8 @@ def fa3_bwd(dout, q, k, v, out, softmax_lse, causal: bool, softmax_scale=None, d
                                      _ptr(dq), _ptr(dk), _ptr(dv), _ptr(delta), ctypes.byref(p))
     if code != capi.STATUS_SUCCESS:
         raise Fa3Error("shaobo_fa3_bwd_v2", code)
+    if sync:
+        _raise_on_device_error(lib, "shaobo_fa3_bwd_v2")
     return (dq, dk, dv, delta) if return_delta else (dq, dk, dv)
 
 
@@ -105,6 +151,7 @@ def fa3_fwd(q, k, v, causal: bool, softmax_scale=None, layout: str = "bhsd", win
     """out, softmax_lse = forward of softmax(q k^T * scale) v (shaobo_fa3_b200_fwd).  Shapes, layouts,
     masks as in fa3_bwd; softmax_lse is fp32 [B,Hq,Sq] natural log."""
     _require_cuda(q, k, v)
+    _check_problem(q, k, v, layout)
     lib = capi.load()
     p = make_params(q, k, causal, softmax_scale, layout=layout, seqused_q=seqused_q, seqused_k=seqused_k,
                     softcap=float(softcap), sync_after_launch=int(sync),
@@ -180,6 +227,8 @@ def fa3_bwd_varlen(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, 
                                      _ptr(dq), _ptr(dk), _ptr(dv), _ptr(delta), ctypes.byref(p))
     if code != capi.STATUS_SUCCESS:
         raise Fa3Error("shaobo_fa3_bwd_v2", code)
+    if sync:
+        _raise_on_device_error(lib, "shaobo_fa3_bwd_v2")
     return (dq, dk, dv, delta) if return_delta else (dq, dk, dv)
 
 

@@ -23,16 +23,18 @@ def attention_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch
                   softmax_lse: torch.Tensor, causal: bool, softmax_scale: float,
                   deterministic: bool, window_left: int = -1, window_right: int = -1, softcap: float = 0.0,
                   layout: str = "bhsd") -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    dq, dk, dv = ops.fa3_bwd(dout.contiguous(), q, k, v, out, softmax_lse, causal, softmax_scale,
-                             deterministic=deterministic, window=(window_left, window_right), softcap=softcap,
-                             layout=layout)
+    # (the kernels read dense tensors: strided views are copied, as in the forward op)
+    dq, dk, dv = ops.fa3_bwd(dout.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), out.contiguous(),
+                             softmax_lse.contiguous(), causal, softmax_scale, deterministic=deterministic,
+                             window=(window_left, window_right), softcap=softcap, layout=layout)
     return dq, dk, dv
 
 
 @attention_bwd.register_fake
 def _(dout, q, k, v, out, softmax_lse, causal, softmax_scale, deterministic, window_left=-1, window_right=-1,
       softcap=0.0, layout="bhsd"):
-    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    # dense outputs whatever the strides of the inputs, like the real op
+    return q.new_empty(q.shape), k.new_empty(k.shape), v.new_empty(v.shape)
 
 
 @torch.library.custom_op("fa3b200::attention_fwd", mutates_args=(), device_types="cuda")
@@ -47,13 +49,16 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: boo
 @attention_fwd.register_fake
 def _(q, k, v, causal, softmax_scale, window_left=-1, window_right=-1, softcap=0.0, layout="bhsd"):
     b, h, s = (q.shape[0], q.shape[2], q.shape[1]) if layout == "bshd" else q.shape[:3]
-    return torch.empty_like(q), q.new_empty((b, h, s), dtype=torch.float32)
+    return q.new_empty(q.shape), q.new_empty((b, h, s), dtype=torch.float32)
 
 
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, softmax_scale, deterministic, window, softcap, layout):
         scale = softmax_scale if softmax_scale is not None else ops.default_scale(q.shape[-1])
+        # strided inputs (a transposed view, say) are made dense once, here, and the dense copies are what
+        # the backward gets; autograd maps the dense gradients back onto the views
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         out, lse = torch.ops.fa3b200.attention_fwd(q, k, v, causal, scale, window[0], window[1], softcap, layout)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.causal, ctx.scale, ctx.deterministic = causal, scale, deterministic

@@ -7,12 +7,16 @@
  * every field offset of ShaoboFa3Params (296 bytes on LP64) and every function
  * signature is the same as there; what differs is the capability set that
  * shaobo_fa3_bwd_get_capabilities reports and shaobo_fa3_bwd_v2_validate
- * accepts (BF16 and head_dim 64 are supported here, the reference rejects
- * both: reference src/shaobo_fa3_bwd_api.cpp:109-118).
+ * accepts (BF16, head_dim 64, the [B,S,H,D] layout, sequence lengths that are
+ * not multiples of 128 or differ between queries and keys, sliding windows,
+ * packed sequences and softcap are supported here; the reference rejects all
+ * of them: reference src/shaobo_fa3_bwd_api.cpp:53-68,109-118).
  *
  * Ownership: the library never allocates device memory in the entry points
  * declared here.  All tensors and the workspace are device pointers owned by
- * the caller.  Layout is BHSD contiguous (row stride = head_dim).
+ * the caller.  Tensors are contiguous in the layout params->layout names:
+ * [B,H,S,D] (SHAOBO_FA3_LAYOUT_BHSD, the reference's only layout) or
+ * [B,S,H,D]; packed sequences are [total, H, D].
  *
  * Stream: launches go to the legacy default stream of the current device,
  * like the reference (which has no stream argument).  As a compatible

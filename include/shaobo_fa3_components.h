@@ -58,10 +58,11 @@ int shaobo_fa3_bwd_fused5(const void* dout,
 /* Split path, dK/dV half (four GEMMs, no atomics, bitwise reproducible).
  * dkv_path selects SHAOBO_FA3_DKV_PATH_CANONICAL (tensor-core kernel; the
  * sidecar is passed in reserved_ptr[SHAOBO_FA3_RESERVED_PTR_SIDECAR]; dk and
- * dv are fp32 [B,Hkv,S,D]; no workspace) or SHAOBO_FA3_DKV_PATH_REFERENCE
- * (naive fp32 device kernels that recompute the softmax from q and k and need
- * the workspace the size function reports).  out, softmax_aux0/1 and dq are
- * ignored, as in the reference.
+ * dv are fp32 [B,Hkv,S,D]; no workspace).  SHAOBO_FA3_DKV_PATH_REFERENCE (the
+ * reference's naive fp32 debug kernels, src/dkv_kernel.cpp:1086-1266) is not
+ * built: NOT_IMPLEMENTED, and the size function reports the workspace that
+ * path would need.  out, softmax_aux0/1 and dq are ignored, as in the
+ * reference.
  * Replaces reference src/dkv_kernel.cpp:1288-1421. */
 size_t shaobo_fa3_bwd_dkv_workspace_bytes(const ShaoboFa3Params* params);
 
@@ -78,12 +79,22 @@ int shaobo_fa3_bwd_dkv(const void* dout,
                        const ShaoboFa3Params* params);
 
 /* Split path, dQ half (three GEMMs, no atomics, no workspace, bitwise
- * reproducible).  dq_path selects SHAOBO_FA3_DQ_PATH_CANONICAL (tensor-core
- * kernel; softmax_aux0/1 are the row maximum and row sum, or the LSE and NULL
- * when softmax_aux_mode is LSE; delta is passed in
- * reserved_ptr[SHAOBO_FA3_RESERVED_PTR_DELTA]; dq is fp32 [B,Hq,S,D]) or
- * SHAOBO_FA3_DQ_PATH_REFERENCE (naive fp32 device kernels).  out, dk and dv
- * are ignored.  Replaces reference src/dq_kernel.cpp:1486-1630. */
+ * reproducible); dq is fp32 [B,Hq,S,D]; out, dk and dv are ignored.
+ * dq_path must be SHAOBO_FA3_DQ_PATH_CANONICAL (the tensor-core kernel).
+ * The row statistics are taken, in this order of preference, from
+ *   (a) the reference's convention (src/dq_kernel.cpp:1515-1549):
+ *       softmax_aux0 / softmax_aux1 = row maximum of the unscaled scores and
+ *       row sum, [B,Hq,S] fp32 each (or the log-sum-exp and NULL when
+ *       softmax_aux_mode is SHAOBO_FA3_SOFTMAX_AUX_LSE), with delta [B,Hq,S]
+ *       in reserved_ptr[SHAOBO_FA3_RESERVED_PTR_DELTA]; used when all of
+ *       them are non-NULL;
+ *   (b) the packed sidecar of shaobo_fa3_bwd_dot_do_o in
+ *       reserved_ptr[SHAOBO_FA3_RESERVED_PTR_SIDECAR], as for the dK/dV half.
+ * INVALID_VALUE when neither form is complete.
+ * SHAOBO_FA3_DQ_PATH_REFERENCE (the reference's naive fp32 debug kernels,
+ * src/dq_kernel.cpp:955-1130) is not built: NOT_IMPLEMENTED, and its
+ * workspace size function reports what that path would need.
+ * Replaces reference src/dq_kernel.cpp:1486-1630. */
 size_t shaobo_fa3_bwd_dq_workspace_bytes(const ShaoboFa3Params* params);
 
 int shaobo_fa3_bwd_dq(const void* dout,

@@ -80,13 +80,15 @@ int main() {
         SHAOBO_FA3_BWD_FEATURE_BHSD | SHAOBO_FA3_BWD_FEATURE_FULL_ATTENTION;
     expect("caps.api_version", caps.api_version, SHAOBO_FA3_API_VERSION);
     expect("caps.required bits", (caps.feature_mask & required) == required, 1);
-    const ShaoboFa3BwdFeatureMask absent =
-        SHAOBO_FA3_BWD_FEATURE_FIXED_LENGTH & 0;  /* every feature of the reference's mask is offered */
     expect("caps.softcap", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_SOFTCAP) != 0, 1);
     expect("caps.varlen", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_VARLEN) != 0, 1);
     expect("caps.bshd", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_BSHD) != 0, 1);
     expect("caps.local window", (caps.feature_mask & SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW) != 0, 1);
-    expect("caps.absent bits", (caps.feature_mask & absent) == 0, 1);
+    // every feature bit the header defines is offered: nothing is set beyond them
+    const ShaoboFa3BwdFeatureMask defined_bits =
+        required | SHAOBO_FA3_BWD_FEATURE_SOFTCAP | SHAOBO_FA3_BWD_FEATURE_VARLEN |
+        SHAOBO_FA3_BWD_FEATURE_BSHD | SHAOBO_FA3_BWD_FEATURE_LOCAL_WINDOW;
+    expect("caps.no undefined bits", (caps.feature_mask & ~defined_bits) == 0, 1);
     expect("caps.min_head_dim", caps.min_head_dim, 64);
     expect("caps.max_head_dim", caps.max_head_dim, 128);
     expect("caps.head_dim_alignment", caps.head_dim_alignment, 64);
@@ -111,14 +113,14 @@ int main() {
     p = good(); p.max_seqlen_q = 1024; p.total_k = 1024;
     expect("redundant fixed-length fields", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
 
-    // unsupported configurations
-    // (sliding windows are accepted here; the reference turns them away)
+    // accepted here although the reference turns them away (src/shaobo_fa3_bwd_api.cpp:53-68,109-118)
     p = good(); p.window_left = 128;
     expect("local window", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
     p = good(); p.causal = 0; p.window_right = 0;
     expect("right window without causal", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
     p = good(); p.softcap = 1.0f;
     expect("softcap", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_SUCCESS);
+    // unsupported configurations
     p = good(); p.dropout_p = 0.1f;
     expect("dropout", shaobo_fa3_bwd_v2_validate(&p), SHAOBO_FA3_STATUS_UNSUPPORTED);
     p = good(); p.dtype = SHAOBO_FA3_DTYPE_FP8;

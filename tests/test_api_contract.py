@@ -51,12 +51,14 @@ def test_workspace_formula():
     p = _params()
     rows = 1 * 4 * 1024
     accum = rows * 128 * 4
-    # 8 key tiles x 2 KV heads = 16 units < 148 SMs: tiles are split, so fp32 dK/dV accumulators are added
-    dkv_accum = 2 * (1 * 2 * 1024 * 128 * 4)
+    # 8 key tiles x 2 KV heads = 16 units < 148 SMs: tiles are split.  Two query heads per KV head give
+    # 2 * (8 + 7 + ... + 1) = 72 steps per KV head; 144 one-step CTAs still fit one wave of 148 SMs, and
+    # every CTA owns one dK and one dV partial-sum slab of [128][128] fp32
+    dkv_accum = 144 * 2 * (128 * 128 * 4)
     expected = accum + dkv_accum + ((rows * 4 + 255) // 256) * 256 + rows * 12
     assert lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p)) == expected
     assert lib.shaobo_fa3_bwd_fused5_workspace_bytes(ctypes.byref(p)) == accum + dkv_accum
-    # the deterministic path never splits and needs no dK/dV accumulators
+    # the deterministic path never splits and needs no partial-sum slabs
     pd = _params(deterministic=1)
     assert lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(pd)) == expected - dkv_accum
     # linear in S (the reference's per-K-tile partials were quadratic)

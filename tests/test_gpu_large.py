@@ -5,8 +5,10 @@ Inputs are generated on the GPU (seeded) and the forward's O / LSE come from an
 fp32 torch softmax; the oracle recomputes everything for the sampled slices
 from the downloaded inputs, so its own O and LSE are also cross-checked.
 
-The gate is oracle.golden.check_gradient: rel-L2 <= 5e-3, max-abs <= 2e-2, with
-one storage spacing allowed where a bf16 output cannot be closer."""
+The gate is oracle.golden.check_gradient: rel-L2 <= 5e-3, max-abs <= 2e-2, or half a
+storage spacing + 5e-3 where a bf16 output cannot be closer; every check prints how many elements
+were off by more than the plain 2e-2 and the largest such error.  delta is gated at 1e-3 relative
+against the oracle's delta of the O the kernel was given."""
 import ctypes
 
 import numpy as np
@@ -26,6 +28,8 @@ def _call(q, k, v, do, out, lse, causal, deterministic=False):
 
 def _gate(actual, expected, dtype, label):
     m = golden.check_gradient(actual, expected, dtype)
+    print(f"{label}: rel_l2 {m['rel_l2']:.2e} max_abs {m['max_abs']:.2e} over 2e-2: {m['over_plain']} of "
+          f"{np.size(expected)} (worst {m['worst_over_plain']:.2e}), worst excess over tolerance {m['worst_excess']:.2e}")
     assert m["pass"], (label, m)
     return m
 
@@ -46,8 +50,11 @@ def _check_slices(q, k, v, do, out, lse, res, causal, dtype, kv_slices):
             dv_ref += r.dv
             # the torch forward used on the GPU agrees with the oracle's forward
             assert np.abs(helpers.host(lse[bi, h]) - r.lse).max() < 2e-4
-            assert golden.delta_pass(golden.compare(helpers.host(delta[bi, h]), r.delta)) or \
-                np.abs(helpers.host(delta[bi, h]) - r.delta).max() < 2e-2
+            # delta = rowsum(dO o O) of the O the kernel was given (the oracle's own O differs from it by
+            # storage rounding of a slightly different fp32 value)
+            delta_ref = np.sum(helpers.host(do[bi, h]) * helpers.host(out[bi, h]), axis=1, dtype=np.float32)
+            md = golden.compare(helpers.host(delta[bi, h]), delta_ref)
+            assert golden.delta_pass(md), (f"delta[{bi},{h}]", md)
             _gate(helpers.host(dq[bi, h]), r.dq, dtype, f"dq[{bi},{h}]")
         _gate(helpers.host(dk[bi, kvh]), dk_ref, dtype, f"dk[{bi},{kvh}]")
         _gate(helpers.host(dv[bi, kvh]), dv_ref, dtype, f"dv[{bi},{kvh}]")
@@ -82,7 +89,7 @@ def test_config4_gqa_b2_hq32_hkv8_s8192_causal_bf16():
     out, lse = synthetic.forward_reference(q, k, v, True)
     res = _call(q, k, v, do, out, lse, True)
     assert capi.load().shaobo_fa3_b200_device_error(1) == 0
-    _check_slices(q, k, v, do, out, lse, res, True, "bf16", [(1, 7)])
+    _check_slices(q, k, v, do, out, lse, res, True, "bf16", [(0, 0), (1, 7)])
     _properties(q, k, v, do, out, lse, res, True)
 
 

@@ -122,3 +122,75 @@ def test_autograd_with_window_softcap_and_bshd():
     for name, grad in (("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
         m = golden.check_gradient(prob.from_layout(helpers.host(grad)), prob.ref[name], "fp16")
         assert m["pass"], (name, m)
+
+
+def test_autograd_with_transposed_views():
+    """q, k, v given as strided views ([B,S,H,D] storage seen as [B,H,S,D]): forward and loss.backward()
+    work, and the gradients land on the leaf tensors."""
+    from flash_attention3_b200 import torch_binding
+    prob = helpers.Problem(1, 4, 2, 256, 64, "fp16", True, seed=307)
+    x = prob.device_inputs()
+    leaves = {n: x[n].transpose(1, 2).contiguous().requires_grad_(True) for n in ("q", "k", "v")}   # [B,S,H,D]
+    views = {n: t.transpose(1, 2) for n, t in leaves.items()}                                      # [B,H,S,D], strided
+    assert not views["q"].is_contiguous()
+    out = torch_binding.attention(views["q"], views["k"], views["v"], causal=True, softmax_scale=prob.scale)
+    loss = (out.float() * x["dout"].float()).sum()
+    loss.backward()
+    torch.cuda.synchronize()
+    for name, key in (("dq", "q"), ("dk", "k"), ("dv", "v")):
+        grad = leaves[key].grad.transpose(1, 2)
+        m = golden.check_gradient(helpers.host(grad), prob.ref[name], "fp16")
+        assert m["pass"], (name, m)
+
+
+def test_wrong_shapes_are_refused_before_the_call():
+    from flash_attention3_b200 import ops
+    prob = helpers.Problem(1, 2, 2, 128, 64, "fp16", True, seed=308)
+    x = prob.device_inputs()
+    with pytest.raises(ValueError):
+        ops.fa3_bwd(x["dout"], x["q"], x["k"], x["v"], x["out"], x["lse"][:, :, :64].contiguous(), True)
+    with pytest.raises(ValueError):
+        ops.fa3_bwd(x["dout"], x["q"], x["k"], x["v"][:, :, :64].contiguous(), x["out"], x["lse"], True)
+    with pytest.raises(TypeError):
+        ops.fa3_bwd(x["dout"], x["q"], x["k"], x["v"], x["out"].float(), x["lse"], True)
+
+
+def test_two_host_threads_with_separate_staging():
+    """Two host threads drive the host-tensor entry point on one GPU at the same time, each with its own
+    staging buffer and stream: both get the right answer."""
+    import threading
+    from flash_attention3_b200 import ops
+    td = helpers.TORCH_DTYPE["bf16"]
+    probs = [helpers.Problem(1, 8, 8, 1024, 128, "bf16", True, seed=311 + i) for i in range(2)]
+    pin = lambda a, dt=td: torch.from_numpy(np.ascontiguousarray(a)).to(dt).pin_memory()
+    jobs = []
+    for prob in probs:
+        q, k, v, do, out = (pin(a) for a in (prob.q, prob.k, prob.v, prob.do, prob.ref["out"]))
+        lse = pin(prob.ref["lse"], torch.float32)
+        outs = tuple(torch.full_like(t, float("nan")).pin_memory() for t in (q, k, v))
+        call = ops.HostBackwardC(1, 8, 8, 1024, 128, td, True, softmax_scale=prob.scale)
+        jobs.append((call, (do, q, k, v, out, lse) + outs, outs))
+    errors = []
+
+    def work(job):
+        call, args, _ = job
+        try:
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for _ in range(8):
+                    call(*args)
+            stream.synchronize()
+        except Exception as exc:
+            errors.append(exc)
+
+    threads = [threading.Thread(target=work, args=(job,)) for job in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    assert not errors, errors
+    for prob, (_, _, outs) in zip(probs, jobs):
+        for name, t in zip(("dq", "dk", "dv"), outs):
+            m = golden.check_gradient(t.float().numpy(), prob.ref[name], "bf16")
+            assert m["pass"], (name, m)
