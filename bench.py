@@ -17,7 +17,11 @@ Keys beyond the base contract:
                 timed on this host on the same workload
   e2e           the same call with host (pinned) inputs and outputs: H2D copies,
                 the call, D2H copies, all inside the timed region
-  also          TFLOP/s of the larger configurations (N=1 only, informative)
+  also          TFLOP/s of the larger configurations (N=1 only, informative), and at every N
+                "C5_strong": the large sharded configuration (B=16,H=32,S=8192,D=128 causal bf16)
+                split over the N ranks by batch with no collective -- strong scaling -- with a
+                parity flag (every rank checks one (batch, head) slice of its shard against the
+                CPU oracle outside the timed region)
 """
 from __future__ import annotations
 
@@ -143,9 +147,25 @@ def cpu_golden_rate(cfg, min_seconds, max_reps):
                       f"NumPy/BLAS on all host threads; the golden computes the full SxS matrix even when causal"}
 
 
+LAUNCHES_PER_CALL = 3  # delta, five-GEMM kernel, convert (or delta, dK/dV kernel, dQ kernel)
+
+
+def config_block(desc, strong, b, world, deterministic):
+    """The "config" object of the JSON line: identical for the GPU arm and the reference arm of one
+    command line (the L2 protocol is the GPU arm's; the CPU arm has no device cache to flush)."""
+    return {"workload": desc if strong else desc + " per GPU", "global_batch": b if strong else b * world,
+            "sharding": "batch (no collective)",
+            "path": "deterministic split path" if deterministic else "fused path",
+            "l2": f"GPU arm: flushed before every step ({L2_FLUSH_BYTES >> 20} MiB write + {L2_FLUSH_BYTES >> 20} MiB read, untimed)"}
+
+
 def run_reference_arm(args, cfg, rank, world):
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; this arm is the only work on the host, so it
+    # takes every host thread, as a single-process run does (NumPy is first imported below)
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = str(os.cpu_count())
     b, hq, hkv, s, d, dtype, causal, desc = cfg
     times = []
     base = None
@@ -157,13 +177,17 @@ def run_reference_arm(args, cfg, rank, world):
     ms = 1e3 * sum(times) / len(times)
     heads = min(b * hq, 4)
     value = bwd_flops(1, heads, s, d, causal) / (ms * 1e-3) / 1e12
-    base.update({"value": value, "sample": f"each step = {heads} (batch,head) slices of the workload through the "
-                                             "NumPy golden (oracle port of the reference's CPU path)"})
+    threads = os.environ.get("OMP_NUM_THREADS") or os.cpu_count()
+    base.update({"value": value, "cores": int(threads),
+                 "sample": f"each step = {heads} (batch,head) slices of the workload through the NumPy golden "
+                           f"(oracle port of the reference's CPU path), BLAS threads: {threads} "
+                           f"(OMP_NUM_THREADS={os.environ.get('OMP_NUM_THREADS', 'unset')})"})
+    config = config_block(desc, args.config == "C5", b, world, args.deterministic)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-        "config": {"workload": desc + " per GPU", "l2": "n/a (CPU)"},
+        "config": config,
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -305,6 +329,51 @@ def time_e2e(torch, wl, steps, warmup, flush, ops):
     return times, h2d, d2h
 
 
+def oracle_slice_parity(torch, wl, bi, h):
+    """One (batch entry, query head) slice of a workload against the CPU oracle.  The slice's O and
+    LSE are replaced by the oracle's own (rounded to storage), one more call is made, and dQ of the
+    head, dK / dV of its KV head (when the head has it to itself) and delta are gated as in the tests."""
+    import numpy as np
+    from oracle import golden
+    b, hq, hkv, s, d, dtype, causal, _ = wl.cfg
+    f = lambda t: t.detach().float().cpu().numpy()
+    group = hq // hkv
+    kv = h // group
+    r = golden.head_backward(f(wl.q[bi, h]), f(wl.k[bi, kv]), f(wl.v[bi, kv]), f(wl.do[bi, h]), causal,
+                             1.0 / float(np.sqrt(d)), dtype)
+    wl.out[bi, h] = torch.from_numpy(r.out).to(wl.out.dtype).cuda()
+    wl.lse[bi, h] = torch.from_numpy(r.lse).cuda()
+    wl.step()
+    torch.cuda.synchronize()
+    checks = {"dq": golden.check_gradient(f(wl.dq[bi, h]), r.dq, dtype)}
+    if group == 1:
+        checks["dk"] = golden.check_gradient(f(wl.dk[bi, kv]), r.dk, dtype)
+        checks["dv"] = golden.check_gradient(f(wl.dv[bi, kv]), r.dv, dtype)
+    ok = all(m["pass"] for m in checks.values()) and wl.lib.shaobo_fa3_b200_device_error(1) == 0
+    return ok, {k: round(m["rel_l2"], 6) for k, m in checks.items()}
+
+
+def c5_strong(torch, capi, ops, synthetic, flush, rank, world, dist, steps=10, warmup=3):
+    """The large sharded configuration split over the ranks by batch (strong scaling): time per step
+    as the max over ranks, aggregate TFLOP/s, and the parity flag of every rank's sampled slice."""
+    from flash_attention3_b200 import sharding
+    cfg = CONFIGS["C5"]
+    b, hq, hkv, s, d, dtype, causal, desc = cfg
+    mine = sharding.plan(b, hkv, world)[rank]
+    assert len(mine) == 1 and mine[0].kv_head_count == hkv, "C5 shards are whole batches"
+    wl = Workload((mine[0].batch_count,) + cfg[1:], 4321 + mine[0].batch_begin, torch, capi, ops, synthetic)
+    times = time_steps(torch, wl, steps, warmup, flush)
+    ms = sharding.max_over_ranks(sum(times), dist, "cuda") / steps
+    ok, rel = oracle_slice_parity(torch, wl, mine[0].batch_count - 1, (7 * rank + 3) % hq)
+    all_ok = sharding.max_over_ranks(0.0 if ok else 1.0, dist, "cuda") == 0.0
+    tflops = bwd_flops(b, hq, s, d, causal) / (ms * 1e-3) / 1e12
+    del wl
+    torch.cuda.empty_cache()
+    return {"workload": desc, "scaling": "strong", "n_gpus": world, "steps": steps, "ms_per_step": ms,
+            "tflops": tflops, "per_gpu_frac_of_measured_peak": tflops / world / measured_peaks()["tflops_burst"],
+            "parity_at_n": bool(all_ok), "rank0_slice_rel_l2": rel}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -386,10 +455,11 @@ def main():
     achieved = stage1_flops / (stage_ms[1] * 1e-3) / 1e12
     traffic = None
     tpath = ROOT / "profiles" / "dram_traffic.json"
-    if tpath.exists():
+    if tpath.exists():  # bytes per launch from a committed ncu capture of this workload, not from this run
         traffic = json.loads(tpath.read_text()).get(args.config, {}).get("fused_bwd_kernel")
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["tflops_burst"], "traffic": traffic,
+                "traffic_source": "profiles/dram_traffic.json (ncu capture of this workload, not this run)",
                 "kernel": ("fused_bwd_kernel without dQ (S, dP, dV, dK)" if args.deterministic
                            else "fused_bwd_kernel (S, dP, dV, dK, dQ)"),
                 "peak_source": peaks["source"] + " (burst bf16 GEMM)", "kernel_ms": stage_ms[1],
@@ -407,18 +477,21 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if strong else "weak",
         "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-        "config": {"workload": desc if strong else desc + " per GPU", "global_batch": b if strong else b * world,
-                   "sharding": "batch (no collective)",
-                   "path": "deterministic split path" if args.deterministic else "fused path",
-                   "l2": f"flushed before every step ({L2_FLUSH_BYTES >> 20} MiB write + {L2_FLUSH_BYTES >> 20} MiB read, untimed)",
-                   "frac_of_measured_peak": value / world / peaks["tflops_burst"],
-                   "frac_of_nominal_2250": value / world / 2250.0},
-        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": 3 * args.steps, "roofline": roofline,
+        "config": config_block(desc, strong, b, world, args.deterministic),
+        "fractions": {"per_gpu_of_measured_peak": value / world / peaks["tflops_burst"],
+                      "per_gpu_of_nominal_2250": value / world / 2250.0},
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": LAUNCHES_PER_CALL * args.steps, "roofline": roofline,
     }
+    also = {}
+    if not args.no_extra and not strong and not args.deterministic:
+        # the strong-scaling curve of the large sharded configuration, at this N (every rank takes part)
+        del wl
+        wl = None
+        torch.cuda.empty_cache()
+        also["C5_strong"] = c5_strong(torch, capi, ops, synthetic, flush, rank, world, dist)
     if rank == 0 and world == 1 and not args.no_extra:
         line["cpu_baseline"] = cpu_golden_rate(cfg, 10.0, 50)
-        also = {}
-        del wl
+        wl = None
         torch.cuda.empty_cache()
         for name in ("C3d128", "C3d64", "C4", "C5shard"):
             if name == args.config:
@@ -438,6 +511,7 @@ def main():
                                        "workload": "forward kernel, " + CONFIGS[name][7]}
             del w2
             torch.cuda.empty_cache()
+    if also:
         line["also"] = also
     if rank == 0:
         print(json.dumps(line))

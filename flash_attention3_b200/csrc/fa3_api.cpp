@@ -6,6 +6,8 @@
 // 122-156), widened to BF16 and head_dim 64.
 #include <cmath>
 #include <cstring>
+#include <queue>
+#include <vector>
 #include <limits>
 
 #include "fa3_host.h"
@@ -137,29 +139,56 @@ SplitPlan split_plan(const ShaoboFa3Params* p) {
         const long long steps = group * q_tiles_of_k_tile(kt, band);
         if (steps > longest) longest = steps;
     }
-    for (long long chunk = 1; chunk < longest; ++chunk) {
+    // Modelled makespan of chunk size `chunk`, in half steps: CTAs longest first onto 148 SMs as they
+    // free up; a CTA of n steps costs 7 + 2n (measured on B200: set-up, first loads, the first step's
+    // pipeline fill and the epilogue together cost about 3.5 steady-state steps).  CTA sizes are few (at most `chunk` different ones), so
+    // the list is walked by size class.
+    long long best_cost = -1;
+    for (long long chunk = 1; chunk <= longest; ++chunk) {
+        std::vector<long long> count(size_t(chunk) + 1, 0);  // CTAs of every size, all heads
         long long per_head = 0;
         for (int kt = 0; kt < tiles; ++kt) {
             const long long steps = group * q_tiles_of_k_tile(kt, band);
-            per_head += (steps + chunk - 1) / chunk;
+            if (steps == 0) continue;
+            const long long full = steps / chunk, rest = steps % chunk;
+            count[size_t(chunk)] += full * heads;
+            if (rest != 0) count[size_t(rest)] += heads;
+            per_head += full + (rest != 0 ? 1 : 0);
         }
-        if (per_head * heads <= kSplitSmCount) {
+        if (per_head * heads > kMaxSplitCtas) continue;
+        std::priority_queue<long long, std::vector<long long>, std::greater<long long>> free_at;
+        for (int i = 0; i < kSplitSmCount; ++i) free_at.push(0);
+        long long makespan = 0;
+        for (long long n = chunk; n >= 1; --n) {
+            for (long long i = 0; i < count[size_t(n)]; ++i) {
+                const long long end = free_at.top() + 7 + 2 * n;
+                free_at.pop();
+                free_at.push(end);
+                if (end > makespan) makespan = end;
+            }
+        }
+        if (best_cost < 0 || makespan < best_cost) {
+            best_cost = makespan;
             plan.chunk_steps = int(chunk);
             plan.chunks_per_head = int(per_head);
-            return plan;
+        } else if (makespan == best_cost) {
+            plan.chunk_steps = int(chunk);      // same makespan with fewer, longer CTAs: fewer partial sums
+            plan.chunks_per_head = int(per_head);
         }
     }
-    return plan;  // a chunk as long as the heaviest tile is no split at all
+    if (plan.chunk_steps >= longest) return SplitPlan{};  // a chunk as long as the heaviest tile is no split at all
+    return plan;
 }
 
 size_t dkv_accum_bytes(const ShaoboFa3Params* p) {
     const SplitPlan plan = split_plan(p);
     if (plan.chunk_steps == 0) return 0;
-    // one dK slab and one dV slab of [128 rows][D] fp32 per CTA
+    // one dK slab and one dV slab of [128 rows][D] per CTA: fp16 for fp16 inputs, fp32 for bf16 inputs
+    const size_t elem = p->dtype == SHAOBO_FA3_DTYPE_FP16 ? 2 : sizeof(float);
     size_t n = size_t(p->batch), out = 0;
     if (!mul_ok(n, size_t(p->num_heads_kv), &n) || !mul_ok(n, size_t(plan.chunks_per_head), &n) ||
         !mul_ok(n, size_t(kSequenceAlignment), &n) || !mul_ok(n, size_t(p->head_dim_qk), &n) ||
-        !mul_ok(n, 2 * sizeof(float), &n) || !round_up_256(n, &out)) {
+        !mul_ok(n, 2 * elem, &n) || !round_up_256(n, &out)) {
         return 0;
     }
     return out;

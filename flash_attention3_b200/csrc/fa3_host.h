@@ -66,9 +66,12 @@ size_t dq_accum_bytes(const ShaoboFa3Params* p);
 // Splitting of key tiles on small problems.  Shapes with fewer (batch x KV head x key tile) units
 // than a B200 has SMs would leave most of the chip idle, so the query steps of every key tile are
 // cut into chunks of `chunk_steps` steps, one CTA per chunk; every CTA writes its dK/dV partial sums
-// to its own fp32 slab and the convert kernel adds the slabs of a tile in chunk order.  The chunk size is the smallest one whose CTA count still fits one wave of 148
-// SMs.  The decision depends on the parameters only, so the workspace formula and the launch
-// always agree.  The deterministic path never splits.
+// to its own fp32 slab and the convert kernel adds the slabs of a tile in chunk order.  The chunk
+// size is the one with the smallest modelled makespan when the CTAs, longest first, are handed to
+// 148 SMs as they free up (a CTA costs a fixed part worth 3.5 steps plus its steps); that may be
+// more CTAs than SMs: the overflow are the shortest ones and run on the SMs that free up first.
+// The decision depends on the parameters only, so the workspace formula and the launch always
+// agree.  The deterministic path never splits.
 constexpr int kSplitSmCount = 148;
 struct SplitPlan {
     int chunk_steps = 0;      // 0 = no splitting
@@ -76,8 +79,8 @@ struct SplitPlan {
 };
 SplitPlan split_plan(const ShaoboFa3Params* p);
 
-// Bytes of the per-CTA partial-sum slabs of split tiles (one dK and one dV slab of [128][D] fp32
-// per CTA); 0 when tiles are not split.
+// Bytes of the per-CTA partial-sum slabs of split tiles (one dK and one dV slab of [128][D] per CTA,
+// fp16 for fp16 inputs and fp32 for bf16 inputs); 0 when tiles are not split.
 size_t dkv_accum_bytes(const ShaoboFa3Params* p);
 
 // Carving of the caller's workspace by shaobo_fa3_bwd_v2:

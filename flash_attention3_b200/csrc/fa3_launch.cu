@@ -6,12 +6,14 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <vector>
 
 #include "cta_order.h"
 #include "fa3_host.h"
@@ -48,13 +50,13 @@ EncodeTiledFn encode_tiled_fn() {
 // head, batch); boxes of [128 rows][64 columns] with the 128-byte swizzle.  Rows past the end of a
 // sequence are outside the tensor for the copy engine and read as zero.
 bool make_map_16(CUtensorMap* map, CUtensorMapDataType type, const void* base, int batch, int heads,
-                 int seqlen, int d, bool bshd) {
+                 int seqlen, int d, bool bshd, int box_rows = 128) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
     const TensorStrides st = strides_of(bshd, heads, seqlen, d);
     const cuuint64_t dims[4] = {cuuint64_t(d), cuuint64_t(seqlen), cuuint64_t(heads), cuuint64_t(batch)};
     const cuuint64_t strides[3] = {cuuint64_t(st.row) * 2, cuuint64_t(st.head) * 2, cuuint64_t(st.batch) * 2};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t box[4] = {64, cuuint32_t(box_rows), 1, 1};
     const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
     return fn(map, type, 4, const_cast<void*>(base), dims, strides, box, elem_strides,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -248,7 +250,7 @@ void launch_delta(const ShaoboFa3Params* p, const void* dout, const void* out, c
 // dq = T(scale * dq_accum); with split tiles also dk, dv = T(sum of the slabs of each key tile) (the
 // scale of dK was applied before the partial sums were written).
 void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
-                    const float* dkv_slabs = nullptr, void* dk = nullptr, void* dv = nullptr) {
+                    const void* dkv_slabs = nullptr, void* dk = nullptr, void* dv = nullptr) {
     ConvertSegments seg{};
     seg.src[0] = accum;
     seg.dst[0] = dq;
@@ -269,6 +271,7 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
         seg.layout[1] = seg.layout[2] = row_layout(p, p->num_heads_kv, shape.rows_k, shape.bshd);
         seg.count = 3;
         seg.slabs = dkv_slabs;
+        seg.slabs_f16 = p->dtype == SHAOBO_FA3_DTYPE_FP16 ? 1 : 0;
         seg.rows_k = shape.rows_k;
         seg.chunks_per_head = split.chunks_per_head;
         // the chunk list of a head, as the GEMM kernel numbers its CTAs: key tile 0 first
@@ -307,8 +310,8 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
 // ------------------------------------------------------- fused / dKV kernel
 template <typename T, int D, bool kCausal, bool kWithDq, typename TOut, bool kSoftcap = false>
 int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                   const CUtensorMap& mdo, const CUtensorMap& mdq, const FusedArgs& args, int blocks,
-                   cudaStream_t st, bool pdl) {
+                   const CUtensorMap& mdo, const CUtensorMap& mdq, const CUtensorMap& mdk,
+                   const CUtensorMap& mdv, const FusedArgs& args, int blocks, cudaStream_t st, bool pdl) {
     auto kernel = fused_bwd_kernel<T, D, kCausal, kWithDq, TOut, kSoftcap>;
     static DeviceOnce configured;  // per instantiation and device
     if (!configured.done()) {
@@ -330,7 +333,7 @@ int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
     attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, mdo, mdq, args) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, mdo, mdq, mdk, mdv, args) != cudaSuccess) {
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
     return SHAOBO_FA3_STATUS_SUCCESS;
@@ -339,20 +342,21 @@ int launch_fused_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 template <typename T, bool kWithDq, typename TOut>
 int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtensorMap& mk,
                    const CUtensorMap& mv, const CUtensorMap& mdo, const CUtensorMap& mdq,
-                   const FusedArgs& args, int blocks, bool pdl) {
+                   const CUtensorMap& mdk, const CUtensorMap& mdv, const FusedArgs& args, int blocks,
+                   bool pdl) {
     cudaStream_t st = stream_of(p);
     const bool banded = needs_general_form(p);
     if (p->softcap > 0.0f) {  // softcapped scores: general form only
         return p->head_dim_qk == 128
-                   ? launch_fused_t<T, 128, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl)
-                   : launch_fused_t<T, 64, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl);
+                   ? launch_fused_t<T, 128, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
+                   : launch_fused_t<T, 64, true, kWithDq, TOut, true>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
     }
     if (p->head_dim_qk == 128) {
-        return banded ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl)
-                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl);
+        return banded ? launch_fused_t<T, 128, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
+                         : launch_fused_t<T, 128, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
     }
-    return banded ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl)
-                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, args, blocks, st, pdl);
+    return banded ? launch_fused_t<T, 64, true, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl)
+                     : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
 }
 
 // Row statistics of a launch: the packed sidecar, or (v2 entry) the caller's log-sum-exp plus the
@@ -373,7 +377,7 @@ struct RowStats {
 // between the two launches while the host encodes the tensor maps.
 struct FusedLaunch {
     int status = SHAOBO_FA3_STATUS_SUCCESS;
-    CUtensorMap mq, mk, mv, mdo, mdq;
+    CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
     FusedArgs args;
     int blocks = 0;
     bool with_dq = false;
@@ -382,11 +386,11 @@ struct FusedLaunch {
 
 FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
                           const void* v, const RowStats& stats, float* dq_accum, void* dk, void* dv,
-                          bool with_dq, bool dkv_f32 = false, float* dkv_slabs = nullptr) {
+                          bool with_dq, bool dkv_f32 = false, void* dkv_slabs = nullptr) {
     FusedLaunch L;
     L.with_dq = with_dq;
     L.dkv_f32 = dkv_f32;
-    CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq;
+    CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq, &mdk = L.mdk, &mdv = L.mdv;
     FusedArgs& args = L.args;
     auto fail = [&](int status) {
         L.status = status;
@@ -411,6 +415,25 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
         mdq = mq;  // unused by the kernel
     }
     const SplitPlan split = (with_dq && dkv_slabs != nullptr) ? split_plan(p) : SplitPlan{};
+    // Where the epilogue stores dK / dV through the copy engine: the fp32 slabs of split tiles
+    // ([slab][128 rows][D], two slabs per CTA), or dk / dv themselves in boxes of 32 rows (16-bit
+    // outputs of fixed-length batches).  Other cases (packed sequences, fp32 outputs) store from
+    // registers and do not use these maps.
+    if (split.chunk_steps > 0) {
+        const int64_t slabs = int64_t(split.chunks_per_head) * p->batch * p->num_heads_kv * 2;
+        const bool ok = bf ? make_map_accum(&mdk, static_cast<const float*>(dkv_slabs), slabs, kTileRows, d)
+                           : make_map_16(&mdk, type, dkv_slabs, 1, int(slabs), kTileRows, d, false, 32);
+        if (!ok) return fail(SHAOBO_FA3_STATUS_HIP_ERROR);
+        mdv = mdk;
+    } else if (!dkv_f32 && !is_varlen(p)) {
+        if (!make_map_16(&mdk, type, dk, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd, 32) ||
+            !make_map_16(&mdv, type, dv, shape.batch, p->num_heads_kv, shape.rows_k, d, bshd, 32)) {
+            return fail(SHAOBO_FA3_STATUS_HIP_ERROR);
+        }
+    } else {
+        mdk = mq;
+        mdv = mq;
+    }
     const int n_tiles = tiles_of(plan_seqlen_k(p));
     const Band band = band_of(p);
     const TileWork work = TileWork::of(band);
@@ -446,6 +469,26 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
     args.head_group = plan.head_group;
     args.chunk_steps = split.chunk_steps;
     args.chunks_per_head = split.chunks_per_head;
+    if (split.chunk_steps > 0) {
+        // every chunk of every (batch, KV head), longest first (stable: equal lengths keep the order
+        // head, key tile, chunk), so that the CTAs beyond one wave are the shortest ones
+        struct Chunk { int steps; uint32_t entry; };
+        std::vector<Chunk> chunks;
+        for (int h = 0; h < bh; ++h) {
+            int place = 0;
+            for (int kt = 0; kt < n_tiles; ++kt) {
+                const int steps = group * q_tiles_of_k_tile(kt, band);
+                for (int c = 0, t0 = 0; t0 < steps; ++c, t0 += split.chunk_steps, ++place) {
+                    const int n = std::min(split.chunk_steps, steps - t0);
+                    const uint32_t slab = uint32_t(h * split.chunks_per_head + place);
+                    chunks.push_back(Chunk{n, uint32_t(kt) | (uint32_t(c) << 8) | (slab << 16)});
+                }
+            }
+        }
+        if (chunks.size() > size_t(kMaxSplitCtas) || n_tiles > 255) return fail(SHAOBO_FA3_STATUS_UNSUPPORTED);
+        std::stable_sort(chunks.begin(), chunks.end(), [](const Chunk& x, const Chunk& y) { return x.steps > y.steps; });
+        for (size_t i = 0; i < chunks.size(); ++i) args.cta_table[i] = chunks[i].entry;
+    }
     const int64_t blocks64 = split.chunk_steps > 0 ? int64_t(split.chunks_per_head) * bh : int64_t(n_tiles) * bh;
     if (blocks64 > 0x7fffffffLL) return fail(SHAOBO_FA3_STATUS_UNSUPPORTED);
     L.blocks = int(blocks64);
@@ -455,24 +498,24 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
 int run_fused(const ShaoboFa3Params* p, const FusedLaunch& L, bool pdl) {
     if (L.status != SHAOBO_FA3_STATUS_SUCCESS) return L.status;
     const bool bf = p->dtype == SHAOBO_FA3_DTYPE_BF16;
-    const CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq;
+    const CUtensorMap &mq = L.mq, &mk = L.mk, &mv = L.mv, &mdo = L.mdo, &mdq = L.mdq, &mdk = L.mdk, &mdv = L.mdv;
     const FusedArgs& args = L.args;
     const int blocks = L.blocks;
     if (L.with_dq) {
-        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl)
-                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl);
+        return bf ? launch_fused_d<__nv_bfloat16, true, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
+                  : launch_fused_d<__half, true, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
     }
     if (L.dkv_f32) {
-        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl)
-                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl);
+        return bf ? launch_fused_d<__nv_bfloat16, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
+                  : launch_fused_d<__half, false, float>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
     }
-    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl)
-              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, args, blocks, pdl);
+    return bf ? launch_fused_d<__nv_bfloat16, false, __nv_bfloat16>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl)
+              : launch_fused_d<__half, false, __half>(p, mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, pdl);
 }
 
 int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
                  const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
-                 bool with_dq, bool dkv_f32 = false, float* dkv_slabs = nullptr, bool pdl = false) {
+                 bool with_dq, bool dkv_f32 = false, void* dkv_slabs = nullptr, bool pdl = false) {
     RowStats stats;
     stats.sidecar = sidecar;
     return run_fused(p, prepare_fused(p, dout, q, k, v, stats, dq_accum, dk, dv, with_dq, dkv_f32, dkv_slabs), pdl);
@@ -753,9 +796,7 @@ extern "C" int shaobo_fa3_bwd_fused5(const void* dout, const void* q, const void
         return SHAOBO_FA3_STATUS_INVALID_VALUE;
     }
     float* accum = static_cast<float*>(params->workspace);
-    float* dkv_slabs = dkv_bytes != 0
-                           ? reinterpret_cast<float*>(static_cast<uint8_t*>(params->workspace) + dq_bytes)
-                           : nullptr;
+    void* dkv_slabs = dkv_bytes != 0 ? static_cast<uint8_t*>(params->workspace) + dq_bytes : nullptr;
     if (cudaMemsetAsync(accum, 0, dq_bytes, stream_of(params)) != cudaSuccess) {  // (the slabs are written, not added into)
         return SHAOBO_FA3_STATUS_HIP_ERROR;
     }
@@ -856,18 +897,25 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
         // caller's log-sum-exp and delta directly, so only its dS phase and its dQ adds depend on
         // the delta kernel; no sidecar is written on this path.
         cudaStream_t st = stream_of(&launch);
-        float* dkv_slabs = ws.dkv_accum_bytes != 0
-                               ? reinterpret_cast<float*>(base + ws.dq_accum_bytes)
-                               : nullptr;
+        void* dkv_slabs = ws.dkv_accum_bytes != 0 ? base + ws.dq_accum_bytes : nullptr;
         RowStats stats;
+#ifdef FA3B200_V2_USE_SIDECAR   // ablation: statistics through the packed sidecar, as the component entry points do
+        stats.sidecar = sidecar;
+#else
         stats.lse = static_cast<const float*>(softmax_lse);
         stats.delta = delta;
+#endif
         // host work of the second launch first, then the three launches back to back
         const FusedLaunch fused = prepare_fused(&launch, dout, q, k, v, stats, accum, dk, dv, true, false, dkv_slabs);
         if (fused.status != SHAOBO_FA3_STATUS_SUCCESS) return fused.status;
         stage_mark(0, st);
+#ifdef FA3B200_V2_USE_SIDECAR
+        launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
+                     sidecar, accum, true);
+#else
         launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
                      nullptr, accum, true);
+#endif
         stage_mark(1, st);
         status = run_fused(&launch, fused, true);
         stage_mark(2, st);
@@ -924,7 +972,9 @@ extern "C" int shaobo_fa3_b200_fwd(const void* q, const void* k, const void* v, 
 // caller has nowhere to get from.  This entry point keeps that scratch in a
 // fixed array that is part of the library image: it exists on every GPU that
 // loads the library, from load until the process exits, whether or not the
-// entry point is ever called.
+// entry point is ever called.  It holds whatever the caller's workspace would:
+// the dQ accumulator, the partial dK/dV sums of split key tiles, delta and the
+// sidecar; a problem fits when shaobo_fa3_bwd_v2_workspace_bytes says so.
 __device__ __align__(256) static unsigned char g_static_scratch[SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES];
 
 namespace {
@@ -963,6 +1013,11 @@ extern "C" int shaobo_fa3_b200_bwd_v2_noalloc(const void* dout, const void* q, c
                                               const ShaoboFa3Params* params) {
     const int validation = validate_v2(params);
     if (validation != SHAOBO_FA3_STATUS_SUCCESS) return validation;
+    // same order of checks as shaobo_fa3_bwd_v2: tensor pointers before anything about scratch
+    if (dout == nullptr || q == nullptr || k == nullptr || v == nullptr || out == nullptr ||
+        softmax_lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) {
+        return SHAOBO_FA3_STATUS_INVALID_VALUE;
+    }
     const V2Workspace ws = v2_workspace(params);
     if (!ws.valid) return SHAOBO_FA3_STATUS_INVALID_VALUE;
     if (ws.total_bytes > size_t(SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES)) {

@@ -87,6 +87,26 @@ __device__ __forceinline__ long long trace_globaltimer() {
 #define TRACE_GT(role, ev) do {} while (0)
 #endif
 
+// Build-time choices measured against each other on the GPU.
+#ifndef FA3B200_DQ_FIRST
+#define FA3B200_DQ_FIRST 0   // 1: issue dQ(t) before dK(t)
+#endif
+#ifndef FA3B200_LD_COLS
+#define FA3B200_LD_COLS 32   // tensor-memory columns a softmax thread fetches per round trip (32 or 64), P phase
+#endif
+#ifndef FA3B200_LD_COLS_B
+#define FA3B200_LD_COLS_B FA3B200_LD_COLS   // the same for the dS phase
+#endif
+#ifndef FA3B200_STATS_INLINE
+#define FA3B200_STATS_INLINE 0   // 1: the first softmax warpgroup fetches the row statistics itself (ablation)
+#endif
+#ifndef FA3B200_PDL_EARLY_WAIT
+#define FA3B200_PDL_EARLY_WAIT 0   // 1: the softmax warpgroups wait for the kernel in front before their first step (ablation)
+#endif
+#ifndef FA3B200_EPILOGUE_DIRECT
+#define FA3B200_EPILOGUE_DIRECT 0   // 1: unsplit tiles store dK / dV from registers (ablation)
+#endif
+
 struct FusedArgs {
     // Row statistics come in one of two forms.  Packed sidecar [B,Hq,Sq,3] = {m, r, delta} (the
     // component entry points), or, when lse is non-null, the caller's log-sum-exp and the delta
@@ -96,8 +116,9 @@ struct FusedArgs {
     const float* delta;
     void* dk;              // [B,Hkv,Sk,D] or [B,Sk,Hkv,D], see kv_strides
     void* dv;
-    float* dkv_slabs;      // split tiles: CTA x writes its fp32 partial dK (scaled) to slab 2x and dV to
-                           // slab 2x+1, each [128 rows][D]; the convert kernel adds the slabs of a tile
+    void* dkv_slabs;       // split tiles: a CTA writes its partial dK (scaled) to slab 2x and dV to slab 2x+1,
+                           // each [128 rows][D], fp16 for fp16 inputs and fp32 for bf16 inputs; the convert
+                           // kernel adds the slabs of a tile
     TensorStrides kv_strides;  // element strides of dk / dv
     int batch;
     int heads_q;
@@ -122,6 +143,10 @@ struct FusedArgs {
     int chunk_steps;       // > 0: the steps of a key tile are cut into chunks of this many steps, one CTA
                            // per chunk, and the partial dK/dV of every chunk go to its own fp32 slab
     int chunks_per_head;   // number of chunks of one (batch, KV head) when chunk_steps > 0
+    // chunk_steps > 0: which chunk CTA x runs, longest chunks first.  Entry = key tile | chunk index
+    // inside the tile << 8 | slab << 16, where slab = (batch, KV head) * chunks_per_head + the chunk's
+    // place in the head's list (key tile 0 first): the CTA's partial dK goes to slab 2*slab, dV to 2*slab+1.
+    uint32_t cta_table[kMaxSplitCtas];
 };
 
 __host__ __device__ inline int remap_k_tile(int physical, int count, int mode, int width) {
@@ -173,6 +198,7 @@ struct FusedCfg {
     static constexpr int kRegsCompute = D == 128 ? FA3B200_REGS_COMPUTE_128 : FA3B200_REGS_COMPUTE_64;
     static constexpr int kRegsDrain = D == 128 ? FA3B200_REGS_DRAIN_128 : FA3B200_REGS_DRAIN_64;
     static_assert(kRegsControl + 2 * kRegsCompute + kRegsDrain <= 512, "register file over-committed");
+    static_assert(kRegsControl < 128, "the control warpgroup gives registers up: its count must drop below the launch value");
 
     static constexpr int kTmemCols = 512;
     static constexpr int kColDK = 0;
@@ -181,6 +207,9 @@ struct FusedCfg {
     static constexpr int kColDP = 2 * D + 128;
     static constexpr int kColDQ = D == 128 ? kColDP : kColDP + 128;
     static_assert(kColDQ + D <= kTmemCols, "tensor-memory ledger exceeds 512 columns");
+    // epilogue staging over the dead Q / dO / dS^T buffers: 8 warps x D/32 fp32 boxes (split tiles) or
+    // 8 warps x D/64 16-bit boxes, 4 KiB each
+    static_assert(8 * (D / 32) * kStageBoxBytes <= kOffStage - kOffQ, "epilogue staging does not fit");
 };
 
 enum Bar : int {
@@ -239,23 +268,6 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity,
     return __all_sync(0xffffffffu, ok);
 }
 
-// 16-bit pair product for dS: P (already rounded to the storage type for the dV GEMM) times
-// (dP - delta) rounded to the storage type, one packed multiply per two elements.
-template <typename T>
-__device__ __forceinline__ uint32_t mul_packed(uint32_t a, uint32_t b);
-template <>
-__device__ __forceinline__ uint32_t mul_packed<__half>(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-template <>
-__device__ __forceinline__ uint32_t mul_packed<__nv_bfloat16>(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-
 // kCausal: general form -- the visible band may be bounded (causal mask, sliding window) and the
 // sequence lengths need not be multiples of 128; tiles that need it are masked in registers and the
 // query tiles of a key tile are walked in ascending order from the first one that sees it.
@@ -271,7 +283,8 @@ template <typename T, int D, bool kCausal, bool kWithDq, typename TOut, bool kSo
 __global__ void __launch_bounds__(512, 1)
 fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                 const __grid_constant__ CUtensorMap tm_dqacc, const FusedArgs a) {
+                 const __grid_constant__ CUtensorMap tm_dqacc, const __grid_constant__ CUtensorMap tm_dk,
+                 const __grid_constant__ CUtensorMap tm_dv, const __grid_constant__ FusedArgs a) {
     using C = FusedCfg<D>;
     constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -292,7 +305,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int bh_count = a.batch * a.heads_kv;
     const bool split = a.chunk_steps > 0;
     const int group = a.heads_q / a.heads_kv;
-    int kt, bhi, t_begin_split = 0;
+    int kt, bhi, t_begin_split = 0, slab = 0;
     if (!split) {
         // groups of head_group heads; inside a group tile slot major, head minor (see cta_order.h)
         const int per_group = n_tiles * a.head_group;
@@ -303,18 +316,11 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         bhi = hg * a.head_group + (rem - tile_slot * heads_here);
         kt = remap_k_tile(tile_slot, n_tiles, a.order_mode, a.order_width);
     } else {
-        // chunk list of one head: key tile 0 first (most steps), each tile cut into ceil(steps/chunk) chunks
-        bhi = int(blockIdx.x) / a.chunks_per_head;
-        int rest = int(blockIdx.x) % a.chunks_per_head;
-        kt = 0;
-        while (true) {
-            const int steps = group * q_tiles_of_k_tile(kt, a.band);  // (never with packed sequences)
-            const int chunks = (steps + a.chunk_steps - 1) / a.chunk_steps;
-            if (rest < chunks) break;
-            rest -= chunks;
-            ++kt;
-        }
-        t_begin_split = rest * a.chunk_steps;
+        const uint32_t entry = a.cta_table[blockIdx.x];
+        kt = int(entry & 0xffu);
+        t_begin_split = int((entry >> 8) & 0xffu) * a.chunk_steps;
+        slab = int(entry >> 16);
+        bhi = slab / a.chunks_per_head;
     }
     const int b = bhi / a.heads_kv;
     const int kvh = bhi % a.heads_kv;
@@ -391,7 +397,20 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     };
 
+    // (Hoisting the barrier initialisation or the tensor-memory allocation above the index arithmetic
+    // was tried: the compiler then spills in the dQ drain role.)
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+        ptx::tmem_relinquish();
+    }
     if (threadIdx.x == 0) {
+        TRACE(0, 4);
+        // the four descriptor fetches go out together, ahead of the barrier set-up: a load whose
+        // descriptor is not there yet waits for it, and the loads are served in order
+        ptx::prefetch_tensormap(&tm_q);
+        ptx::prefetch_tensormap(&tm_k);
+        ptx::prefetch_tensormap(&tm_v);
+        ptx::prefetch_tensormap(&tm_do);
         if ((sbase & 1023u) != 0) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
         ptx::mbar_init(bar(kKvFull), 1);
         for (int s = 0; s < 2; ++s) {
@@ -399,8 +418,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::mbar_init(bar(kQEmpty + s), 1);
             ptx::mbar_init(bar(kDoFull + s), 1);
             ptx::mbar_init(bar(kDoEmpty + s), 1);
-            ptx::mbar_init(bar(kNegFull + s), 64);
-            ptx::mbar_init(bar(kDelFull + s), 64);
+            ptx::mbar_init(bar(kNegFull + s), FA3B200_STATS_INLINE ? 128 : 64);
+            ptx::mbar_init(bar(kDelFull + s), FA3B200_STATS_INLINE ? 128 : 64);
             ptx::mbar_init(bar(kStatsEmpty + s), 8);
         }
         ptx::mbar_init(bar(kSFull), 1);
@@ -416,32 +435,21 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         TRACE(0, 2);
         // The first loads go out before the rest of the CTA has finished its set-up: Q, K, V, dO are
         // inputs of the call (nothing here depends on the kernel in front), and this thread, which
-        // is the TMA producer, has just initialised the barriers they complete on.
+        // is the TMA producer, has initialised the barriers they complete on.
         if (!misaligned) {
-            ptx::prefetch_tensormap(&tm_q);
-            ptx::prefetch_tensormap(&tm_k);
-            ptx::prefetch_tensormap(&tm_v);
-            ptx::prefetch_tensormap(&tm_do);
             // tensor maps are [batch][head][row][D]; rows past the end of a sequence read as zero
             ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
 #pragma unroll
             for (int bx = 0; bx < C::kBoxes; ++bx) {
                 ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
                                  k_base + kt * C::kTile, kvh, b_coord);
-            }
-            load_q(0);
-#pragma unroll
-            for (int bx = 0; bx < C::kBoxes; ++bx) {
                 ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
                                  k_base + kt * C::kTile, kvh, b_coord);
             }
+            load_q(0);
             load_do(0);
             TRACE(0, 3);
         }
-    }
-    if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
-        ptx::tmem_relinquish();
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -550,28 +558,34 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     if (!(ok = warp_wait<false>(bar(kDsReady), t & 1, abort_flag))) break;
                     if (t < 6) TRACE(1, tb + 3);
                     ptx::tc_fence_after();
-                    if (kWithDq) {
-                        if (D == 64) {  // own dQ region: wait for the drain of step t-1
-                            if (!(ok = warp_wait<false>(bar(kDqEmpty), (t & 1) ^ 1, abort_flag))) break;
-                            ptx::tc_fence_after();
-                        }
-                        // dQ = dS K first: its drain frees the columns dP(t+1) needs (D = 128: dQ(t)
-                        // overwrites dP(t), which was consumed before kDsReady)
+                    auto issue_dq = [&]() {
+                        // dQ = dS K  (D = 128: overwrites dP(t), which was consumed before kDsReady)
                         ptx::mma_ss_lean<false>(tmem + C::kColDQ, loDS_mn, loK_mn, kHi, kIdDq);
 #pragma unroll
                         for (int kk = 1; kk < 8; ++kk)
                             ptx::mma_ss_lean<true>(tmem + C::kColDQ, loDS_mn + mn_step(kk), loK_mn + mn_step(kk), kHi, kIdDq);
                         ptx::tc_commit_elect(bar(kDqFull));
-                    }
-                    // dK += dS^T Q
-                    {
+                    };
+                    auto issue_dk = [&]() {
+                        // dK += dS^T Q; its completion frees the Q stage
                         const uint32_t loQ = ptx::desc_lo_mn_major(sQ(t), C::kBoxBytes);
                         ptx::mma_ss_lean_rt(tmem + C::kColDK, loDS_k, loQ, kHi, kIdDkv, t > 0 ? 1u : 0u);
 #pragma unroll
                         for (int kk = 1; kk < 8; ++kk)
                             ptx::mma_ss_lean<true>(tmem + C::kColDK, loDS_k + k_step(kk), loQ + mn_step(kk), kHi, kIdDkv);
+                        ptx::tc_commit_elect(bar(kQEmpty + t % C::kQStages));
+                    };
+                    if (kWithDq && D == 64) {  // own dQ region: wait for the drain of step t-1
+                        if (!(ok = warp_wait<false>(bar(kDqEmpty), (t & 1) ^ 1, abort_flag))) break;
+                        ptx::tc_fence_after();
                     }
-                    ptx::tc_commit_elect(bar(kQEmpty + t % C::kQStages));
+                    if (FA3B200_DQ_FIRST) {
+                        if (kWithDq) issue_dq();
+                        issue_dk();
+                    } else {
+                        issue_dk();
+                        if (kWithDq) issue_dq();
+                    }
                     ptx::tc_commit_elect(bar(kDsFree));
                     if (t < 6) TRACE(1, tb + 4);
                     if (more) {
@@ -590,7 +604,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (ok) ptx::tc_commit_elect(bar(kDkvFull));
                 TRACE(1, 62);
             }
-        } else if (!misaligned) {
+        } else if (!misaligned && !FA3B200_STATS_INLINE) {
             // ================================================= row statistics (warps 2 and 3)
             // Thread i fetches n and delta of rows i and i+64 of the coming query tile and writes them
             // to the buffer of that step.  n needs only the caller's log-sum-exp when it is given; delta
@@ -650,7 +664,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     } else if (wg == 1 || wg == 2) {
         // ============================================ softmax / dS warpgroups
-        ptx::setmaxnreg_inc<C::kRegsCompute>();
+        if constexpr (C::kRegsCompute < 128) ptx::setmaxnreg_dec<C::kRegsCompute>();
+        else ptx::setmaxnreg_inc<C::kRegsCompute>();
         if (!misaligned) {
             const int half = wg - 1;          // which 64 queries of the tile
             const int j = threadIdx.x & 127;  // key row inside the tile == TMEM lane
@@ -660,6 +675,30 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const float* stats = reinterpret_cast<const float*>(smem + C::kOffStats);
             uint32_t ppk[32];
             bool ok = true;
+            if (FA3B200_PDL_EARLY_WAIT) ptx::grid_dependency_wait();
+#if FA3B200_STATS_INLINE
+            float in_n = 0.f, in_d = 0.f;
+            auto inline_fetch = [&](int t) {
+                int hq, qt;
+                step_coords(t, hq, qt);
+                const int qi = qt * C::kTile + j;
+                const bool valid = !kCausal || qi < band.seqlen_q;
+                const int64_t row = int64_t(b_coord * a.heads_q + hq) * a.sidecar_rows + q_base + (valid ? qi : 0);
+                float n, d;
+                if (a.lse != nullptr) {
+                    const float l = a.lse[row];
+                    n = l == -INFINITY ? -INFINITY : -l * 1.44269504088896340736f;
+                    d = a.delta[row];
+                } else {
+                    n = __log2f(a.sidecar[row * 3 + 1]) - a.sidecar[row * 3 + 0];
+                    d = a.sidecar[row * 3 + 2];
+                }
+                in_n = valid ? n : -INFINITY;
+                in_d = valid ? d : 0.f;
+            };
+            ptx::grid_dependency_wait();
+            if (half == 0) inline_fetch(0);
+#endif
 #pragma unroll 1
             for (int t = 0; t < n_steps; ++t) {
                 int hq, qt;
@@ -668,6 +707,16 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 const int tb = 4 + 8 * t;  // trace slots of this step
                 const float* negp = stats + buf * 128 + half * 64;
                 const float* delp = stats + 256 + buf * 128 + half * 64;
+#if FA3B200_STATS_INLINE
+                if (half == 0) {
+                    float* wstats = reinterpret_cast<float*>(smem + C::kOffStats);
+                    wstats[buf * 128 + j] = in_n;
+                    wstats[256 + buf * 128 + j] = in_d;
+                    ptx::mbar_arrive(bar(kNegFull + buf));
+                    ptx::mbar_arrive(bar(kDelFull + buf));
+                    if (t + 1 < n_steps) inline_fetch(t + 1);
+                }
+#endif
                 if (!(ok = warp_wait(bar(kNegFull + buf), (t >> 1) & 1, abort_flag))) break;
                 if (warp == 4 && t < 7) TRACE(2, tb + 0);
                 if (!(ok = warp_wait(bar(kSFull), t & 1, abort_flag))) break;
@@ -687,7 +736,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 };
                 // the 64 scores of this thread's key row come in one tensor-memory round trip (two for
                 // the softcap variant, which needs the registers)
-                constexpr int kW = kSoftcap ? 32 : 64;
+                constexpr int kW = kSoftcap ? 32 : FA3B200_LD_COLS;
 #pragma unroll
                 for (int w = 0; w < 64 / kW; ++w) {
                     uint32_t r[kW];
@@ -738,15 +787,16 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 ptx::tc_fence_after();
                 const uint32_t ds_row = sbase + C::kOffDS + half * C::kBoxBytes + j * 128;
                 const float inv_post = kSoftcap ? 1.0f / a.softcap_post : 0.0f;
+                constexpr int kWB = kSoftcap ? 32 : FA3B200_LD_COLS_B;
 #pragma unroll
-                for (int w = 0; w < 64 / kW; ++w) {
-                    uint32_t rr[kW];
-                    if constexpr (kW == 64) ptx::tmem_ld64(dp_cols, rr);
+                for (int w = 0; w < 64 / kWB; ++w) {
+                    uint32_t rr[kWB];
+                    if constexpr (kWB == 64) ptx::tmem_ld64(dp_cols, rr);
                     else ptx::tmem_ld32(dp_cols + w * 32, rr);
                     ptx::tmem_ld_wait();
-                    const uint32_t* r = rr - w * kW;  // r[e] = dP of query column e of this half
+                    const uint32_t* r = rr - w * kWB;  // r[e] = dP of query column e of this half
 #pragma unroll
-                    for (int e = w * kW; e < (w + 1) * kW; e += 8) {
+                    for (int e = w * kWB; e < (w + 1) * kWB; e += 8) {
                         const float4 d0 = *reinterpret_cast<const float4*>(delp + e);
                         const float4 d1 = *reinterpret_cast<const float4*>(delp + e + 4);
                         uint4 o;
@@ -768,7 +818,6 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                             o.z = ptx::Pack2<T>::pack(capped(pc.x, r[e + 4], d1.x, n1.x), capped(pc.y, r[e + 5], d1.y, n1.y));
                             o.w = ptx::Pack2<T>::pack(capped(pd.x, r[e + 6], d1.z, n1.z), capped(pd.y, r[e + 7], d1.w, n1.w));
                         } else {
-#ifdef FA3B200_DS_FP32
                             const float2 pa = ptx::Pack2<T>::unpack(ppk[e / 2 + 0]);
                             const float2 pb = ptx::Pack2<T>::unpack(ppk[e / 2 + 1]);
                             const float2 pc = ptx::Pack2<T>::unpack(ppk[e / 2 + 2]);
@@ -781,18 +830,6 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                                       pc.y * (__uint_as_float(r[e + 5]) - d1.y));
                             o.w = ptx::Pack2<T>::pack(pd.x * (__uint_as_float(r[e + 6]) - d1.z),
                                                       pd.y * (__uint_as_float(r[e + 7]) - d1.w));
-#else
-                            // (dP - delta) in fp32, rounded to the storage type, then one packed multiply
-                            // with P (which is in the storage type already) per two elements
-                            o.x = mul_packed<T>(ppk[e / 2 + 0], ptx::Pack2<T>::pack(__uint_as_float(r[e + 0]) - d0.x,
-                                                                                    __uint_as_float(r[e + 1]) - d0.y));
-                            o.y = mul_packed<T>(ppk[e / 2 + 1], ptx::Pack2<T>::pack(__uint_as_float(r[e + 2]) - d0.z,
-                                                                                    __uint_as_float(r[e + 3]) - d0.w));
-                            o.z = mul_packed<T>(ppk[e / 2 + 2], ptx::Pack2<T>::pack(__uint_as_float(r[e + 4]) - d1.x,
-                                                                                    __uint_as_float(r[e + 5]) - d1.y));
-                            o.w = mul_packed<T>(ppk[e / 2 + 3], ptx::Pack2<T>::pack(__uint_as_float(r[e + 6]) - d1.z,
-                                                                                    __uint_as_float(r[e + 7]) - d1.w));
-#endif
                         }
                         const int chunk = e / 8;  // 16-byte chunk inside this half's box
                         const uint32_t addr = ds_row + ((chunk ^ (j & 7)) << 4);
@@ -813,60 +850,147 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (ok) ok = warp_wait(bar(kDkvFull), 0, abort_flag);
             if (warp == 4) TRACE(2, 60);
             if (ok) {
-                // (tensor-memory loads are warp-wide: every lane runs them, only the stores of key rows
-                // past the end of the sequence are skipped)
-                // (rows between the used length and the end of the slot hold exact zeros)
-                const bool key_valid = kt * C::kTile + j < slot_k;
+                // Every MMA has completed, so the Q / dO / dS^T buffers are dead.  Each warp stages its
+                // 32 key rows there in the layout of a swizzled TMA box and one lane stores them with
+                // the copy engine: whole 128-byte lines, rows past the end of the tensor clipped by the
+                // hardware.  (A thread storing its own row straight from registers writes 16 bytes per
+                // line and instruction: measured 6 us per CTA instead of under 1.)
                 ptx::tc_fence_after();
                 const float mul = half == 0 ? a.scale : 1.0f;
                 const uint32_t col0 = tl + (half == 0 ? C::kColDK : C::kColDV);
-                auto store_f32 = [&](float* dst) {
+                const int w4 = warp & 3;  // which 32 rows of the tile
+                // packed sequences: the rows behind this sequence's end belong to its neighbour, which the
+                // copy engine cannot know; fp32 outputs of the split path: plain rows.  Both keep per-thread stores.
+                const bool staged = split || (!FA3B200_EPILOGUE_DIRECT && sizeof(TOut) == 2 && a.cu_seqlens_q == nullptr);
+                if (staged && split && !kBf16) {
+                    // fp16 inputs: the partial sums go to this CTA's slabs (slab 2x: dK, 2x+1: dV) as fp16,
+                    // boxes of [32 rows][64 x 16 bit].  (fp16 keeps 11 significant bits, three more than a
+                    // bf16 result would; the bytes written, not the arithmetic, bound this epilogue.)
+                    const uint32_t scratch = sbase + C::kOffQ + (half * 4 + w4) * (C::kBoxes * C::kStageBoxBytes);
 #pragma unroll
                     for (int c = 0; c < D / 32; ++c) {
                         uint32_t r[32];
                         ptx::tmem_ld32(col0 + c * 32, r);
                         ptx::tmem_ld_wait();
-                        if (key_valid) {
-                            float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
+                        const uint32_t row_addr = scratch + (c >> 1) * C::kStageBoxBytes + lane * 128;
 #pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                d4[e] = make_float4(__uint_as_float(r[4 * e]) * mul, __uint_as_float(r[4 * e + 1]) * mul,
-                                                    __uint_as_float(r[4 * e + 2]) * mul, __uint_as_float(r[4 * e + 3]) * mul);
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t o0 = ptx::Pack2<__half>::pack(__uint_as_float(r[8 * e + 0]) * mul, __uint_as_float(r[8 * e + 1]) * mul);
+                            const uint32_t o1 = ptx::Pack2<__half>::pack(__uint_as_float(r[8 * e + 2]) * mul, __uint_as_float(r[8 * e + 3]) * mul);
+                            const uint32_t o2 = ptx::Pack2<__half>::pack(__uint_as_float(r[8 * e + 4]) * mul, __uint_as_float(r[8 * e + 5]) * mul);
+                            const uint32_t o3 = ptx::Pack2<__half>::pack(__uint_as_float(r[8 * e + 6]) * mul, __uint_as_float(r[8 * e + 7]) * mul);
+                            const int chunk = (c & 1) * 4 + e;
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(row_addr + ((chunk ^ (lane & 7)) << 4)), "r"(o0), "r"(o1), "r"(o2), "r"(o3)
+                                         : "memory");
                         }
-                        __syncwarp();  // reconverge before the next warp-wide load
                     }
-                };
-                auto store_b16 = [&](T* dst) {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int bx = 0; bx < C::kBoxes; ++bx)
+                            ptx::tma_store_4d(&tm_dk, scratch + bx * C::kStageBoxBytes, bx * 64, w4 * 32, slab * 2 + half, 0);
+                        ptx::bulk_commit_group();
+                        ptx::bulk_wait_group_read<0>();
+                    }
+                } else if (staged && split) {
+                    // bf16 inputs: fp32 partial sums -> this CTA's slabs, boxes of [32 rows][32 fp32]
+                    constexpr int kBoxesPerWarp = D / 32;
+                    const uint32_t scratch = sbase + C::kOffQ + (half * 4 + w4) * (kBoxesPerWarp * C::kStageBoxBytes);
+#pragma unroll
+                    for (int c = 0; c < kBoxesPerWarp; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(col0 + c * 32, r);
+                        ptx::tmem_ld_wait();
+                        const uint32_t row_addr = scratch + c * C::kStageBoxBytes + lane * 128;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(row_addr + ((e ^ (lane & 7)) << 4)),
+                                           "f"(__uint_as_float(r[4 * e]) * mul), "f"(__uint_as_float(r[4 * e + 1]) * mul),
+                                           "f"(__uint_as_float(r[4 * e + 2]) * mul), "f"(__uint_as_float(r[4 * e + 3]) * mul)
+                                         : "memory");
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int c = 0; c < kBoxesPerWarp; ++c)
+                            ptx::tma_store_3d(&tm_dk, scratch + c * C::kStageBoxBytes, c * 32, w4 * 32,
+                                              slab * 2 + half);
+                        ptx::bulk_commit_group();
+                        ptx::bulk_wait_group_read<0>();
+                    }
+                } else if (staged) {
+                    // 16-bit outputs -> dk / dv through their tensor maps, boxes of [32 rows][64 x 16 bit]
+                    const uint32_t scratch = sbase + C::kOffQ + (half * 4 + w4) * (C::kBoxes * C::kStageBoxBytes);
 #pragma unroll
                     for (int c = 0; c < D / 32; ++c) {
                         uint32_t r[32];
                         ptx::tmem_ld32(col0 + c * 32, r);
                         ptx::tmem_ld_wait();
-                        if (key_valid) {
-                            uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+                        // 32 columns = 64 bytes = chunks 4*(c&1) .. 4*(c&1)+3 of this row of box c/2
+                        const uint32_t row_addr = scratch + (c >> 1) * C::kStageBoxBytes + lane * 128;
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                uint4 o;
-                                o.x = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 0]) * mul, __uint_as_float(r[8 * e + 1]) * mul);
-                                o.y = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 2]) * mul, __uint_as_float(r[8 * e + 3]) * mul);
-                                o.z = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 4]) * mul, __uint_as_float(r[8 * e + 5]) * mul);
-                                o.w = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 6]) * mul, __uint_as_float(r[8 * e + 7]) * mul);
-                                d4[e] = o;
-                            }
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t o0 = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 0]) * mul, __uint_as_float(r[8 * e + 1]) * mul);
+                            const uint32_t o1 = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 2]) * mul, __uint_as_float(r[8 * e + 3]) * mul);
+                            const uint32_t o2 = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 4]) * mul, __uint_as_float(r[8 * e + 5]) * mul);
+                            const uint32_t o3 = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 6]) * mul, __uint_as_float(r[8 * e + 7]) * mul);
+                            const int chunk = (c & 1) * 4 + e;
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(row_addr + ((chunk ^ (lane & 7)) << 4)), "r"(o0), "r"(o1), "r"(o2), "r"(o3)
+                                         : "memory");
                         }
-                        __syncwarp();
                     }
-                };
-                if (split) {
-                    // split tile: this CTA's partial sums go to its own fp32 slab ([128 rows][D], dK then dV);
-                    // the convert kernel adds the slabs of a tile in a fixed order
-                    store_f32(a.dkv_slabs + (int64_t(blockIdx.x) * 2 + half) * (C::kTile * D) + j * D);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const void* map = half == 0 ? static_cast<const void*>(&tm_dk) : static_cast<const void*>(&tm_dv);
+#pragma unroll
+                        for (int bx = 0; bx < C::kBoxes; ++bx)
+                            ptx::tma_store_4d(map, scratch + bx * C::kStageBoxBytes, bx * 64,
+                                              kt * C::kTile + w4 * 32, kvh, b);
+                        ptx::bulk_commit_group();
+                        ptx::bulk_wait_group_read<0>();
+                    }
                 } else {
+                    // (tensor-memory loads are warp-wide: every lane runs them, only the stores of key rows
+                    // past the end of the sequence are skipped)
+                    // (rows between the used length and the end of the slot hold exact zeros)
+                    const bool key_valid = kt * C::kTile + j < slot_k;
                     const int64_t off = b_coord * a.kv_strides.batch + kvh * a.kv_strides.head +
                                         int64_t(k_base + kt * C::kTile + j) * a.kv_strides.row;
                     TOut* dst = reinterpret_cast<TOut*>(half == 0 ? a.dk : a.dv) + off;
-                    if (sizeof(TOut) == 4) store_f32(reinterpret_cast<float*>(dst));
-                    else store_b16(reinterpret_cast<T*>(dst));
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(col0 + c * 32, r);
+                        ptx::tmem_ld_wait();
+                        if (key_valid) {
+                            if (sizeof(TOut) == 4) {
+                                float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    d4[e] = make_float4(__uint_as_float(r[4 * e]) * mul, __uint_as_float(r[4 * e + 1]) * mul,
+                                                        __uint_as_float(r[4 * e + 2]) * mul, __uint_as_float(r[4 * e + 3]) * mul);
+                            } else {
+                                uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    uint4 o;
+                                    o.x = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 0]) * mul, __uint_as_float(r[8 * e + 1]) * mul);
+                                    o.y = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 2]) * mul, __uint_as_float(r[8 * e + 3]) * mul);
+                                    o.z = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 4]) * mul, __uint_as_float(r[8 * e + 5]) * mul);
+                                    o.w = ptx::Pack2<T>::pack(__uint_as_float(r[8 * e + 6]) * mul, __uint_as_float(r[8 * e + 7]) * mul);
+                                    d4[e] = o;
+                                }
+                            }
+                        }
+                        __syncwarp();  // reconverge before the next warp-wide load
+                    }
                 }
             }
             if (warp == 4) TRACE(2, 61);
@@ -886,7 +1010,8 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!kWithDq) {
             ptx::setmaxnreg_dec<C::kRegsControl>();
         } else {
-            ptx::setmaxnreg_inc<C::kRegsDrain>();
+            if constexpr (C::kRegsDrain < 128) ptx::setmaxnreg_dec<C::kRegsDrain>();
+            else ptx::setmaxnreg_inc<C::kRegsDrain>();
             if (!misaligned) {
                 const int qd = warp & 3;
                 const uint32_t tl = tmem + (uint32_t(qd * 32) << 16);

@@ -20,6 +20,9 @@ namespace fa3b200 {
 
 constexpr int kTileRows = 128;
 constexpr int kUnbounded = 1 << 29;  // larger than any supported sequence length
+// Most CTAs a small problem is cut into when its key tiles are split: the size of the CTA table that
+// travels in the GEMM kernel's parameters (the host planner keeps to it).
+constexpr int kMaxSplitCtas = 512;
 
 FA3B200_HD inline int tiles_of(int seqlen) { return (seqlen + kTileRows - 1) / kTileRows; }
 

@@ -156,7 +156,8 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
 // Up to three (fp32 -> storage dtype) conversions in one launch: dQ (scaled) from its accumulator
 // always; dK and dV as well when key tiles were split.  A split tile's dK / dV is the sum of the
 // per-CTA slabs its chunks wrote ([128 rows][D] fp32 each, dK slab then dV slab per CTA), added here
-// in chunk order, so these two outputs do not depend on the order in which the CTAs ran.
+// in chunk order, so these two outputs do not depend on the order in which the CTAs ran.  The slabs
+// hold fp16 when the inputs are fp16 and fp32 when they are bf16.
 constexpr int kMaxSplitTiles = 148;  // tiles are only split while tiles x heads < 148
 struct ConvertSegments {
     const float* src[3];   // [0]: fp32 dQ accumulator [batch, head, row, D] contiguous; [1],[2] unused
@@ -166,7 +167,8 @@ struct ConvertSegments {
     RowLayout layout[3];   // where the rows of dst live
     int count;
     int head_dim;
-    const float* slabs;    // count == 3: slab base; CTA x of the GEMM kernel owns slabs 2x (dK) and 2x+1 (dV)
+    const void* slabs;     // count == 3: slab base; chunk x of the GEMM kernel owns slabs 2x (dK) and 2x+1 (dV)
+    int slabs_f16;         // the slabs hold fp16 (fp16 inputs) instead of fp32
     int rows_k;            // key rows per (batch, KV head)
     int chunks_per_head;   // CTAs per (batch, KV head)
     unsigned short chunk_begin[kMaxSplitTiles + 1];  // first chunk of key tile kt inside its head
@@ -212,17 +214,29 @@ dq_convert_kernel(const __grid_constant__ ConvertSegments seg) {
             const int kt = row >> 7;
             const int c0 = seg.chunk_begin[kt], c1 = seg.chunk_begin[kt + 1];
             const int64_t slab_elems = int64_t(kTileRows) * seg.head_dim;
-            const float* src = seg.slabs + ((bh * seg.chunks_per_head + c0) * 2 + (sgi - 1)) * slab_elems +
-                               int64_t(row & 127) * seg.head_dim + col;
+            const int64_t first = ((bh * seg.chunks_per_head + c0) * 2 + (sgi - 1)) * slab_elems +
+                                  int64_t(row & 127) * seg.head_dim + col;
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[e] = 0.0f;
-            for (int c = c0; c < c1; ++c, src += 2 * slab_elems) {
-                const uint4 lo = ld_stream_16B(src);
-                const uint4 hi = ld_stream_16B(src + 4);
-                v[0] += __uint_as_float(lo.x); v[1] += __uint_as_float(lo.y);
-                v[2] += __uint_as_float(lo.z); v[3] += __uint_as_float(lo.w);
-                v[4] += __uint_as_float(hi.x); v[5] += __uint_as_float(hi.y);
-                v[6] += __uint_as_float(hi.z); v[7] += __uint_as_float(hi.w);
+            if (seg.slabs_f16) {
+                const __half* src = static_cast<const __half*>(seg.slabs) + first;
+                for (int c = c0; c < c1; ++c, src += 2 * slab_elems) {
+                    const uint4 x = ld_stream_16B(src);
+                    const float2 a0 = unpack2<__half>(x.x), a1 = unpack2<__half>(x.y);
+                    const float2 a2 = unpack2<__half>(x.z), a3 = unpack2<__half>(x.w);
+                    v[0] += a0.x; v[1] += a0.y; v[2] += a1.x; v[3] += a1.y;
+                    v[4] += a2.x; v[5] += a2.y; v[6] += a3.x; v[7] += a3.y;
+                }
+            } else {
+                const float* src = static_cast<const float*>(seg.slabs) + first;
+                for (int c = c0; c < c1; ++c, src += 2 * slab_elems) {
+                    const uint4 lo = ld_stream_16B(src);
+                    const uint4 hi = ld_stream_16B(src + 4);
+                    v[0] += __uint_as_float(lo.x); v[1] += __uint_as_float(lo.y);
+                    v[2] += __uint_as_float(lo.z); v[3] += __uint_as_float(lo.w);
+                    v[4] += __uint_as_float(hi.x); v[5] += __uint_as_float(hi.y);
+                    v[6] += __uint_as_float(hi.z); v[7] += __uint_as_float(hi.w);
+                }
             }
         }
         uint4 o;

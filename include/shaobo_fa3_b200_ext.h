@@ -46,17 +46,24 @@ int shaobo_fa3_b200_last_stage_ms(float* ms3);
  * by its launcher.  Such a caller can pass inputs and outputs but has no
  * workspace to offer, and shaobo_fa3_bwd_v2 needs one.
  *
- * What it does: the same computation as shaobo_fa3_bwd_v2, same arguments,
- * same results and status codes, except that params->workspace and
- * params->workspace_bytes are ignored: the scratch (fp32 dQ accumulator, delta,
- * packed sidecar) is a fixed array of SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES
- * inside the library.  The call performs no cudaMalloc, no cudaFree and no
- * other allocating runtime or library call.
+ * What it does: the same computation as shaobo_fa3_bwd_v2, same arguments and
+ * results, except that params->workspace and params->workspace_bytes are
+ * ignored: the scratch is a fixed array of
+ * SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES inside the library.  It holds what the
+ * workspace of shaobo_fa3_bwd_v2 holds: the fp32 dQ accumulator
+ * (4*B*Hq*Sq*D bytes), on small problems whose key tiles are split over
+ * several thread blocks the fp32 partial dK/dV sums of those blocks (256*D
+ * bytes per block, up to 148 blocks), delta and the packed sidecar (16 bytes
+ * per query row).  The call performs no cudaMalloc, no cudaFree and no other
+ * allocating runtime or library call.
  *
- * Limit: a problem whose shaobo_fa3_bwd_v2_workspace_bytes exceeds
- * SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES returns SHAOBO_FA3_STATUS_UNSUPPORTED
- * and launches nothing (B*Hq*S*D up to about 8 Mi elements fits, e.g.
- * B=1,H=4,S=2048,D=128 or B=2,H=8,S=2048,D=128).
+ * Limit: the problem must satisfy
+ *     shaobo_fa3_bwd_v2_workspace_bytes(params) <= SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES
+ * (ask that function; e.g. B=1,H=4,S=2048,D=128 needs 22 MiB and
+ * B=1,H=15,S=4096,D=128 31 MiB, B=2,H=16,S=2048,D=128 does not fit).  A larger
+ * problem returns SHAOBO_FA3_STATUS_UNSUPPORTED and launches nothing.  Status
+ * codes otherwise follow shaobo_fa3_bwd_v2 in the same order: parameter
+ * validation first, then NULL tensor pointers (INVALID_VALUE), then this limit.
  *
  * First call: the first call on each device looks up the device address of the
  * array (one runtime query, with that device current).  Make that first call

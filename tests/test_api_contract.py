@@ -53,11 +53,14 @@ def test_workspace_formula():
     accum = rows * 128 * 4
     # 8 key tiles x 2 KV heads = 16 units < 148 SMs: tiles are split.  Two query heads per KV head give
     # 2 * (8 + 7 + ... + 1) = 72 steps per KV head; 144 one-step CTAs still fit one wave of 148 SMs, and
-    # every CTA owns one dK and one dV partial-sum slab of [128][128] fp32
-    dkv_accum = 144 * 2 * (128 * 128 * 4)
+    # every CTA owns one dK and one dV partial-sum slab of [128][128], fp16 for fp16 inputs (the default
+    # dtype of a parameter block) and fp32 for bf16 inputs
+    dkv_accum = 144 * 2 * (128 * 128 * 2)
     expected = accum + dkv_accum + ((rows * 4 + 255) // 256) * 256 + rows * 12
     assert lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p)) == expected
     assert lib.shaobo_fa3_bwd_fused5_workspace_bytes(ctypes.byref(p)) == accum + dkv_accum
+    pb = _params(dtype=capi.DTYPE_BF16)
+    assert lib.shaobo_fa3_bwd_fused5_workspace_bytes(ctypes.byref(pb)) == accum + 2 * dkv_accum
     # the deterministic path never splits and needs no partial-sum slabs
     pd = _params(deterministic=1)
     assert lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(pd)) == expected - dkv_accum

@@ -88,9 +88,10 @@ def test_softmax_d_is_optional():
     code = lib.shaobo_fa3_bwd_v2(vp(x["dout"]), vp(x["q"]), vp(x["k"]), vp(x["v"]), vp(x["out"]), vp(x["lse"]),
                                  vp(dq), vp(dk), vp(dv), None, ctypes.byref(p))
     assert code == 0
-    # delta then lives in the workspace right after the dQ accumulator and the dK/dV accumulators
-    # (2 key tiles < 148 SMs, so tiles are split)
-    off = 256 * 128 * 4 + 2 * 256 * 128 * 4
+    # delta then lives in the workspace right after the dQ accumulator and the partial-sum slabs of
+    # the split key tiles (2 key tiles < 148 SMs, so tiles are split): the fused stage's own workspace
+    off = lib.shaobo_fa3_bwd_fused5_workspace_bytes(ctypes.byref(p))
+    assert off > 256 * 128 * 4 and off % 256 == 0
     delta = ws[off:off + 256 * 4].view(torch.float32).cpu().numpy()
     assert golden.delta_pass(golden.compare(delta, prob.ref["delta"][0, 0]))
     assert golden.check_gradient(helpers.host(dq), prob.ref["dq"], "fp16")["pass"]

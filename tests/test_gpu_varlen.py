@@ -134,3 +134,22 @@ def test_seqused_lengths(deterministic, layout):
         assert golden.check_gradient(dk[i:i + 1, :, :uk], ref["dk"], dtype)["pass"], (i, "dk")
         assert golden.check_gradient(dv[i:i + 1, :, :uk], ref["dv"], dtype)["pass"], (i, "dv")
         assert (dq[i, :, uq:] == 0).all() and (dk[i, :, uk:] == 0).all() and (dv[i, :, uk:] == 0).all(), (i, "tails")
+
+
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_every_batch_entry_unused(deterministic):
+    """seqused_q = 0 everywhere is valid input: no CTA of the GEMM kernel has any work, yet the call must
+    stay ordered behind the clearing of the accumulators, and all gradients are exact zeros."""
+    b, hq, hkv, s, d = 2, 4, 2, 256, 128
+    td = TORCH_DTYPE["bf16"]
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    q, do = (torch.randn(b, hq, s, d, device="cuda", generator=gen).to(td) for _ in range(2))
+    k, v = (torch.randn(b, hkv, s, d, device="cuda", generator=gen).to(td) for _ in range(2))
+    zero = torch.zeros(b, dtype=torch.int32, device="cuda")
+    out, lse = ops.fa3_fwd(q, k, v, True, seqused_q=zero, sync=True)
+    outputs = tuple(torch.full_like(t, float("nan")) for t in (q, k, v))
+    for _ in range(3):  # repeated: a convert kernel that ran ahead of the clearing would read stale sums
+        dq, dk, dv = ops.fa3_bwd(do, q, k, v, out, lse, True, deterministic=deterministic, seqused_q=zero,
+                                 outputs=outputs, sync=True)
+        for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):  # (sync=True has checked the device error flag)
+            assert (t == 0).all(), name

@@ -209,3 +209,56 @@ def test_oracle_softcap_gradients_match_finite_differences():
     assert np.abs(got["dq"][0, 0] - numeric(lambda X: forward(X, K, V), Q)).max() < 2e-3
     assert np.abs(got["dk"][0, 0] - numeric(lambda X: forward(Q, X, V), K)).max() < 2e-3
     assert np.abs(got["dv"][0, 0] - numeric(lambda X: forward(Q, K, X), V)).max() < 1e-5
+
+
+# The checks above share one thing with the oracle: the hand-derived formula dS = P o (dP - delta).
+# This one does not.  torch differentiates a float64 forward, softmax(cap(q k^T * scale) + mask) v,
+# by itself, and the oracle's gradients for the inputs the reference rejects (windows, seqlen_q !=
+# seqlen_k, softcap, GQA on top) must agree with that.  (The reference cannot pin these: it turns them
+# away, reference src/shaobo_fa3_bwd_api.cpp:53-68,109-118.)
+@pytest.mark.parametrize("sq,sk,causal,window,softcap,hq,hkv", [
+    (40, 40, True, (-1, -1), 0.0, 2, 1),      # the reference's own domain, as a baseline for the method
+    (24, 56, True, (-1, -1), 0.0, 2, 2),      # more keys than queries, bottom-right diagonal
+    (56, 24, True, (-1, -1), 0.0, 1, 1),      # more queries than keys: the first 32 queries see nothing
+    (48, 48, True, (7, -1), 0.0, 4, 2),       # causal sliding window
+    (33, 47, False, (5, 9), 0.0, 2, 1),       # two-sided window, ragged lengths
+    (40, 40, True, (-1, -1), 3.0, 2, 1),      # softcap
+    (31, 45, False, (6, 2), 1.5, 4, 2),       # everything at once
+])
+def test_oracle_gradients_match_autograd_of_a_float64_forward(sq, sk, causal, window, softcap, hq, hkv):
+    import torch
+    d, scale, b = 16, 0.29, 2
+    q, k, v, do = golden.seeded_inputs(123, b, hq, hkv, sq, d, "fp16", sk=sk)
+    got = golden.backward(q, k, v, do, causal, scale, "fp16", window, softcap)
+    tq, tk, tv = (torch.tensor(x, dtype=torch.float64, requires_grad=True) for x in (q, k, v))
+    tdo = torch.tensor(do, dtype=torch.float64)
+    group = hq // hkv
+    kk, vv = tk.repeat_interleave(group, dim=1), tv.repeat_interleave(group, dim=1)
+    z = torch.einsum("bhid,bhjd->bhij", tq, kk) * scale
+    if softcap > 0:
+        z = softcap * torch.tanh(z / softcap)
+    i = torch.arange(sq)[:, None]
+    j = torch.arange(sk)[None, :]
+    left, right = window
+    if causal:
+        right = 0
+    visible = torch.ones(sq, sk, dtype=torch.bool)
+    if right >= 0:
+        visible &= j <= i + (sk - sq) + right
+    if left >= 0:
+        visible &= j >= i + (sk - sq) - left
+    # rows that see no key: softmax over an all -inf row is NaN in torch; give them a finite row and
+    # zero it afterwards, so that they contribute nothing, which is what the oracle defines
+    any_visible = visible.any(dim=1, keepdim=True)
+    z = z.masked_fill(~(visible | ~any_visible), float("-inf"))
+    p = torch.softmax(z, dim=-1) * any_visible
+    out = torch.einsum("bhij,bhjd->bhid", p, vv)
+    (out * tdo).sum().backward()
+    # the oracle rounds O to fp16 before delta, as the reference does: that moves dS by up to
+    # 2^-11 * |dO . O| per row, which bounds the difference to the exact gradients
+    for name, grad in (("dq", tq.grad), ("dk", tk.grad), ("dv", tv.grad)):
+        ref = grad.numpy()
+        err = np.abs(got[name] - ref).max()
+        assert err < 3e-3 * max(1.0, np.abs(ref).max()), (name, err)
+        assert golden.compare(got[name], ref)["rel_l2"] < 1e-3, name
+    np.testing.assert_allclose(got["out"], out.detach().numpy(), atol=2e-3)
