@@ -300,10 +300,13 @@ void launch_convert(const ShaoboFa3Params* p, const float* accum, void* dq,
     attr[0].val.programmaticStreamSerializationAllowed = 1;  // the kernel waits for the GEMM kernel itself
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    const bool slabs = seg.count == 3;
     if (p->dtype == SHAOBO_FA3_DTYPE_BF16) {
-        cudaLaunchKernelEx(&cfg, dq_convert_kernel<__nv_bfloat16>, seg);
+        if (slabs) cudaLaunchKernelEx(&cfg, dq_convert_kernel<__nv_bfloat16, true>, seg);
+        else cudaLaunchKernelEx(&cfg, dq_convert_kernel<__nv_bfloat16, false>, seg);
     } else {
-        cudaLaunchKernelEx(&cfg, dq_convert_kernel<__half>, seg);
+        if (slabs) cudaLaunchKernelEx(&cfg, dq_convert_kernel<__half, true>, seg);
+        else cudaLaunchKernelEx(&cfg, dq_convert_kernel<__half, false>, seg);
     }
 }
 
@@ -359,14 +362,6 @@ int launch_fused_d(const ShaoboFa3Params* p, const CUtensorMap& mq, const CUtens
                      : launch_fused_t<T, 64, false, kWithDq, TOut>(mq, mk, mv, mdo, mdq, mdk, mdv, args, blocks, st, pdl);
 }
 
-// Row statistics of a launch: the packed sidecar, or (v2 entry) the caller's log-sum-exp plus the
-// delta array, which the GEMM kernel then reads directly.
-struct RowStats {
-    const float* sidecar = nullptr;
-    const float* lse = nullptr;
-    const float* delta = nullptr;
-};
-
 // with_dq: fused five-GEMM kernel writing dK/dV in the input dtype and adding
 // dQ into dq_accum (already zero).  !with_dq: four-GEMM dK/dV kernel with fp32
 // outputs (split path).
@@ -385,7 +380,7 @@ struct FusedLaunch {
 };
 
 FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
-                          const void* v, const RowStats& stats, float* dq_accum, void* dk, void* dv,
+                          const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
                           bool with_dq, bool dkv_f32 = false, void* dkv_slabs = nullptr) {
     FusedLaunch L;
     L.with_dq = with_dq;
@@ -443,9 +438,7 @@ FusedLaunch prepare_fused(const ShaoboFa3Params* p, const void* dout, const void
     const long long dq_bytes_per_head =
         with_dq ? (long long)group * plan_seqlen_q(p) * p->head_dim_qk * 4 : 0;
     const CtaOrderPlan plan = cached_plan(work, bh, group, sm_count(), dq_bytes_per_head);
-    args.sidecar = stats.sidecar;
-    args.lse = stats.lse;
-    args.delta = stats.delta;
+    args.sidecar = sidecar;
     args.dk = dk;
     args.dv = dv;
     args.dkv_slabs = dkv_slabs;
@@ -516,9 +509,7 @@ int run_fused(const ShaoboFa3Params* p, const FusedLaunch& L, bool pdl) {
 int launch_fused(const ShaoboFa3Params* p, const void* dout, const void* q, const void* k,
                  const void* v, const float* sidecar, float* dq_accum, void* dk, void* dv,
                  bool with_dq, bool dkv_f32 = false, void* dkv_slabs = nullptr, bool pdl = false) {
-    RowStats stats;
-    stats.sidecar = sidecar;
-    return run_fused(p, prepare_fused(p, dout, q, k, v, stats, dq_accum, dk, dv, with_dq, dkv_f32, dkv_slabs), pdl);
+    return run_fused(p, prepare_fused(p, dout, q, k, v, sidecar, dq_accum, dk, dv, with_dq, dkv_f32, dkv_slabs), pdl);
 }
 
 // -------------------------------------------------------------- dQ kernel
@@ -893,29 +884,15 @@ extern "C" int shaobo_fa3_bwd_v2(const void* dout, const void* q, const void* k,
 
     int status = SHAOBO_FA3_STATUS_SUCCESS;
     if (launch.deterministic == 0) {
-        // delta, and the dQ accumulator is cleared in the same pass.  The GEMM kernel reads the
-        // caller's log-sum-exp and delta directly, so only its dS phase and its dQ adds depend on
-        // the delta kernel; no sidecar is written on this path.
+        // delta + sidecar, and the dQ accumulator is cleared in the same pass
         cudaStream_t st = stream_of(&launch);
         void* dkv_slabs = ws.dkv_accum_bytes != 0 ? base + ws.dq_accum_bytes : nullptr;
-        RowStats stats;
-#ifdef FA3B200_V2_USE_SIDECAR   // ablation: statistics through the packed sidecar, as the component entry points do
-        stats.sidecar = sidecar;
-#else
-        stats.lse = static_cast<const float*>(softmax_lse);
-        stats.delta = delta;
-#endif
         // host work of the second launch first, then the three launches back to back
-        const FusedLaunch fused = prepare_fused(&launch, dout, q, k, v, stats, accum, dk, dv, true, false, dkv_slabs);
+        const FusedLaunch fused = prepare_fused(&launch, dout, q, k, v, sidecar, accum, dk, dv, true, false, dkv_slabs);
         if (fused.status != SHAOBO_FA3_STATUS_SUCCESS) return fused.status;
         stage_mark(0, st);
-#ifdef FA3B200_V2_USE_SIDECAR
         launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
                      sidecar, accum, true);
-#else
-        launch_delta(&launch, dout, out, static_cast<const float*>(softmax_lse), nullptr, delta,
-                     nullptr, accum, true);
-#endif
         stage_mark(1, st);
         status = run_fused(&launch, fused, true);
         stage_mark(2, st);

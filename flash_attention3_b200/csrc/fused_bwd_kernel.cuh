@@ -7,29 +7,23 @@
 //
 //     S^T  = K  Q^T        [key j on TMEM lanes, query i on columns]   SS MMA
 //     dP^T = V  dO^T                                                    SS MMA
-//     P^T  = exp2(S^T * scale*log2e + n_i)            (CUDA cores, -> TMEM b16)
+//     P^T  = exp2(S^T * scale*log2e - m_i) * r_i      (CUDA cores, -> TMEM b16)
 //     dV  += P^T dO        A = P^T from TMEM, B = dO (MN-major)         TS MMA
 //     dS^T = P^T o (dP^T - delta_i)                   (CUDA cores, -> smem b16)
-//     dQ   = dS K          A = dS^T read MN-major, B = K (MN-major)     SS MMA
 //     dK  += dS^T Q        A = dS^T (K-major), B = Q (MN-major)         SS MMA
+//     dQ   = dS K          A = dS^T read MN-major, B = K (MN-major)     SS MMA
 //     dQacc[tile] += dQ    TMEM -> regs -> smem -> TMA reduce-add (fp32)
 //
-// n_i = log2(r_i) - m_i is the row's softmax reference in log2 units (-lse*log2e when the caller
-// passes a log-sum-exp).  The softmax scale is applied once at the end (dK in the epilogue, dQ in
-// the convert kernel) instead of per element of dS.
+// The softmax scale is applied once at the end (dK in the epilogue, dQ in the
+// convert kernel) instead of per element of dS.
 //
-// Warp roles (512 threads, four warpgroups): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
-// owner, warps 2-3 = row statistics (they fetch n_i and delta_i of the coming query tile from
-// global memory into a two-buffer ring in shared memory, so the math warps never wait for global
-// memory); warps 4-7 and 8-11 = two softmax / dS warpgroups (thread j of each owns TMEM lane j =
-// key j; the first takes queries 0-63 of the tile, the second queries 64-127); warps 12-15 = dQ
-// drain warpgroup.  Registers are re-split with setmaxnreg.  All hand-offs go through mbarriers;
-// every wait is bounded and a time-out raises an error flag instead of hanging.
-//
-// Order on the tensor pipe in steady state (one MMA-issuing warp, MMAs execute in issue order):
-//     ... P(t) ready -> dV(t), S(t+1) | dS(t) ready -> dQ(t), dK(t) | dQ(t) drained -> dP(t+1) ...
-// dQ(t) goes before dK(t) because dP(t+1) has to wait for the drain of dQ(t) (they share tensor
-// memory at D=128): the drain then overlaps dK(t).
+// Warp roles (512 threads, four warpgroups): warp 0 = TMA producer, warp 1 = MMA
+// issuer and TMEM owner; warps 4-7 and 8-11 = two softmax / dS warpgroups (thread
+// j of each owns TMEM lane j = key j; the first takes queries 0-63 of the tile,
+// the second queries 64-127); warps 12-15 = dQ drain warpgroup.  Registers are
+// re-split with setmaxnreg (96 / 112 / 112 / 176 per thread at D=128).  All hand-offs go
+// through mbarriers; every wait is bounded and a time-out raises an error flag
+// instead of hanging.
 //
 // Tensor-memory ledger (512 columns x 128 lanes x 32 bit):
 //     D = 128:  dK [0,128)  dV [128,256)  S/P [256,384)  dP and dQ share [384,512)
@@ -45,7 +39,7 @@
 //     dO              1 stage (D=128) or 2 stages (D=64) x D*256
 //     dS^T            32 KiB               [128 keys][128 queries]
 //     dQ staging      32 KiB               4 warps x 2 boxes of [32 rows][32 fp32]
-//     row statistics  2 KiB                {n_i, delta_i} x 128 rows x 2 buffers
+//     row statistics  2 KiB                {-m + log2 r, delta} x 128 rows x 2 buffers
 //     mbarriers       256
 //     total           231,680 (D=128) / 166,144 (D=64)   of 232,448 available
 #pragma once
@@ -87,33 +81,13 @@ __device__ __forceinline__ long long trace_globaltimer() {
 #define TRACE_GT(role, ev) do {} while (0)
 #endif
 
-// Build-time choices measured against each other on the GPU.
-#ifndef FA3B200_DQ_FIRST
-#define FA3B200_DQ_FIRST 0   // 1: issue dQ(t) before dK(t)
-#endif
-#ifndef FA3B200_LD_COLS
-#define FA3B200_LD_COLS 32   // tensor-memory columns a softmax thread fetches per round trip (32 or 64), P phase
-#endif
-#ifndef FA3B200_LD_COLS_B
-#define FA3B200_LD_COLS_B FA3B200_LD_COLS   // the same for the dS phase
-#endif
-#ifndef FA3B200_STATS_INLINE
-#define FA3B200_STATS_INLINE 0   // 1: the first softmax warpgroup fetches the row statistics itself (ablation)
-#endif
-#ifndef FA3B200_PDL_EARLY_WAIT
-#define FA3B200_PDL_EARLY_WAIT 0   // 1: the softmax warpgroups wait for the kernel in front before their first step (ablation)
-#endif
-#ifndef FA3B200_EPILOGUE_DIRECT
-#define FA3B200_EPILOGUE_DIRECT 0   // 1: unsplit tiles store dK / dV from registers (ablation)
+// Build-time choice measured on the GPU.
+#ifndef FA3B200_EARLY_LOADS
+#define FA3B200_EARLY_LOADS 0   // 1: K, V and the first Q / dO tiles are requested before the CTA's set-up barrier
 #endif
 
 struct FusedArgs {
-    // Row statistics come in one of two forms.  Packed sidecar [B,Hq,Sq,3] = {m, r, delta} (the
-    // component entry points), or, when lse is non-null, the caller's log-sum-exp and the delta
-    // array [B,Hq,Sq] each (the v2 entry: only delta then depends on the kernel in front).
-    const float* sidecar;
-    const float* lse;
-    const float* delta;
+    const float* sidecar;  // [B,Hq,Sq,3] = {m, r, delta} per query row (packed sequences: [Hq, total_q, 3])
     void* dk;              // [B,Hkv,Sk,D] or [B,Sk,Hkv,D], see kv_strides
     void* dv;
     void* dkv_slabs;       // split tiles: a CTA writes its partial dK (scaled) to slab 2x and dV to slab 2x+1,
@@ -129,7 +103,7 @@ struct FusedArgs {
     const int* cu_seqlens_k;  // owns rows cu[b] .. cu[b+1]-1; the tensor maps then have batch = 1
     const int* seqused_q;     // non-null: only the first seqused[b] rows of batch entry b take part; the
     const int* seqused_k;     // gradient rows behind them, up to the end of the entry's slot, are zero
-    int sidecar_rows;      // rows per head of the statistics / accumulators (seqlen_q, or total_q when packed)
+    int sidecar_rows;      // rows per head of the sidecar / accumulators (seqlen_q, or total_q when packed)
     float scale;
     float scale_log2;
     // softcap variant: the scaled scores go through softcap * tanh(x / softcap) before the softmax;
@@ -186,19 +160,11 @@ struct FusedCfg {
     static_assert(kSmemBytes <= 232448, "shared-memory ledger exceeds 227 KiB");
     static_assert(kOffStage % 1024 == 0 && kOffDS % 1024 == 0, "swizzled regions need 1 KiB alignment");
 
-    // setmaxnreg split per warpgroup (producer+MMA+statistics / softmax x2 / drain); sums to <= 512
-#ifndef FA3B200_REGS_CONTROL
-#define FA3B200_REGS_CONTROL 112
-#define FA3B200_REGS_COMPUTE_128 128
-#define FA3B200_REGS_DRAIN_128 144
-#define FA3B200_REGS_COMPUTE_64 136
-#define FA3B200_REGS_DRAIN_64 128
-#endif
-    static constexpr int kRegsControl = FA3B200_REGS_CONTROL;
-    static constexpr int kRegsCompute = D == 128 ? FA3B200_REGS_COMPUTE_128 : FA3B200_REGS_COMPUTE_64;
-    static constexpr int kRegsDrain = D == 128 ? FA3B200_REGS_DRAIN_128 : FA3B200_REGS_DRAIN_64;
+    // setmaxnreg split per warpgroup (producer+MMA / softmax x2 / drain); sums to <= 512
+    static constexpr int kRegsControl = 96;
+    static constexpr int kRegsCompute = D == 128 ? 112 : 136;
+    static constexpr int kRegsDrain = D == 128 ? 176 : 136;
     static_assert(kRegsControl + 2 * kRegsCompute + kRegsDrain <= 512, "register file over-committed");
-    static_assert(kRegsControl < 128, "the control warpgroup gives registers up: its count must drop below the launch value");
 
     static constexpr int kTmemCols = 512;
     static constexpr int kColDK = 0;
@@ -207,8 +173,6 @@ struct FusedCfg {
     static constexpr int kColDP = 2 * D + 128;
     static constexpr int kColDQ = D == 128 ? kColDP : kColDP + 128;
     static_assert(kColDQ + D <= kTmemCols, "tensor-memory ledger exceeds 512 columns");
-    // epilogue staging over the dead Q / dO / dS^T buffers: 8 warps x D/32 fp32 boxes (split tiles) or
-    // 8 warps x D/64 16-bit boxes, 4 KiB each
     static_assert(8 * (D / 32) * kStageBoxBytes <= kOffStage - kOffQ, "epilogue staging does not fit");
 };
 
@@ -226,12 +190,9 @@ enum Bar : int {
     kDqFull = 14,
     kDqEmpty = 15,
     kDkvFull = 16,
-    kNegFull = 17,     // 2 buffers: n_i of the tile written
-    kDelFull = 19,     // 2 buffers: delta_i of the tile written
-    kStatsEmpty = 21,  // 2 buffers: both softmax phases of the tile have read them
-    kNumBars = 23,
+    kStatsFull = 17,  // 2 buffers
+    kNumBars = 19,
 };
-static_assert(8 * kNumBars + 8 <= 256, "barrier block overflows its 256 bytes");
 
 constexpr long long kWaitTimeoutCycles = 2000000000LL;  // about one second
 
@@ -277,7 +238,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity,
 // and dV outputs (T for the fused path, float for the split path).  kWithDq:
 // false turns the kernel into the four-GEMM dK/dV half of the split path.
 // kSoftcap: softcapped scores (general form only).  dS then carries the slope 1 - tanh^2 of the cap,
-// which the second softmax phase recovers from P itself (t = (log2 P - n_i) / softcap_post)
+// which the second softmax phase recovers from P itself (t = (log2 P - (log2 r - m)) / softcap_post)
 // instead of keeping it in registers between the phases.
 template <typename T, int D, bool kCausal, bool kWithDq, typename TOut, bool kSoftcap = false>
 __global__ void __launch_bounds__(512, 1)
@@ -295,11 +256,11 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     auto bar = [&](int i) -> uint32_t { return sbase + C::kOffBar + 8 * i; };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + 8 * kNumBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+
     if (threadIdx.x == 0) {
         TRACE(0, 0);
         TRACE_GT(0, 1);
     }
-
     // ---- which tile is ours ------------------------------------------------
     const int n_tiles = tiles_of(a.band.seqlen_k);      // key tiles (of the longest sequence)
     const int bh_count = a.batch * a.heads_kv;
@@ -358,6 +319,76 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // to dK / dV
     const bool owes_zeros = !split && n_steps == 0 && (sbase & 1023u) == 0;
 
+    if (threadIdx.x == 0) {
+        TRACE(0, 4);
+        if ((sbase & 1023u) != 0) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
+        ptx::mbar_init(bar(kKvFull), 1);
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(bar(kQFull + s), 1);
+            ptx::mbar_init(bar(kQEmpty + s), 1);
+            ptx::mbar_init(bar(kDoFull + s), 1);
+            ptx::mbar_init(bar(kDoEmpty + s), 1);
+            ptx::mbar_init(bar(kStatsFull + s), 128);
+        }
+        ptx::mbar_init(bar(kSFull), 1);
+        ptx::mbar_init(bar(kDpFull), 1);
+        ptx::mbar_init(bar(kPReady), 256);
+        ptx::mbar_init(bar(kDsReady), 256);
+        ptx::mbar_init(bar(kDsFree), 1);
+        ptx::mbar_init(bar(kDqFull), 1);
+        ptx::mbar_init(bar(kDqEmpty), 128);
+        ptx::mbar_init(bar(kDkvFull), 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        TRACE(0, 2);
+        if (FA3B200_EARLY_LOADS && !misaligned) {
+            // Q, K, V, dO are inputs of the call: nothing here depends on the kernel in front, and this
+            // thread (the TMA producer) has just initialised the barriers the loads complete on
+            ptx::prefetch_tensormap(&tm_k);
+            ptx::prefetch_tensormap(&tm_v);
+            ptx::prefetch_tensormap(&tm_q);
+            ptx::prefetch_tensormap(&tm_do);
+            ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
+#pragma unroll
+            for (int bx = 0; bx < C::kBoxes; ++bx) {
+                ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
+                                 k_base + kt * C::kTile, kvh, b_coord);
+                ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
+                                 k_base + kt * C::kTile, kvh, b_coord);
+            }
+            // first query tile of this CTA (what step_coords(0) gives)
+            const int g0 = t_begin / steps_per_head;
+            const int r0 = t_begin - g0 * steps_per_head;
+            int qt0 = q_begin + r0;
+            if (!kCausal) {
+                qt0 = r0 + ((n_q_tiles == 0) ? 0 : kt % n_q_tiles);
+                if (qt0 >= n_q_tiles) qt0 -= n_q_tiles;
+            }
+            const int hq0 = kvh * group + g0;
+            ptx::mbar_arrive_expect_tx(bar(kQFull + 0), C::kOperandBytes);
+#pragma unroll
+            for (int bx = 0; bx < C::kBoxes; ++bx)
+                ptx::tma_load_4d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kQFull + 0), bx * 64,
+                                 q_base + qt0 * C::kTile, hq0, b_coord);
+            ptx::mbar_arrive_expect_tx(bar(kDoFull + 0), C::kOperandBytes);
+#pragma unroll
+            for (int bx = 0; bx < C::kBoxes; ++bx)
+                ptx::tma_load_4d(sbase + C::kOffDO + bx * C::kBoxBytes, &tm_do, bar(kDoFull + 0), bx * 64,
+                                 q_base + qt0 * C::kTile, hq0, b_coord);
+            TRACE(0, 3);
+        }
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    // The kernel behind this one (dQ convert) may begin to launch; it waits for our completion itself.
+    ptx::launch_dependents();
+
     // Query tiles are visited in ascending order starting at the diagonal (causal) or at a
     // per-CTA rotation (non-causal), so that CTAs of one head that run together add into
     // different dQ tiles at any moment.
@@ -374,111 +405,56 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (qt >= n_q_tiles) qt -= n_q_tiles;
         }
     };
-    auto load_q = [&](int t) {
-        int hq, qt;
-        step_coords(t, hq, qt);
-        const int s = t % C::kQStages;
-        ptx::mbar_arrive_expect_tx(bar(kQFull + s), C::kOperandBytes);
-#pragma unroll
-        for (int bx = 0; bx < C::kBoxes; ++bx) {
-            ptx::tma_load_4d(sbase + C::kOffQ + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_q,
-                             bar(kQFull + s), bx * 64, q_base + qt * C::kTile, hq, b_coord);
-        }
-    };
-    auto load_do = [&](int t) {
-        int hq, qt;
-        step_coords(t, hq, qt);
-        const int sd = t % C::kDoStages;
-        ptx::mbar_arrive_expect_tx(bar(kDoFull + sd), C::kOperandBytes);
-#pragma unroll
-        for (int bx = 0; bx < C::kBoxes; ++bx) {
-            ptx::tma_load_4d(sbase + C::kOffDO + sd * C::kOperandBytes + bx * C::kBoxBytes, &tm_do,
-                             bar(kDoFull + sd), bx * 64, q_base + qt * C::kTile, hq, b_coord);
-        }
-    };
-
-    // (Hoisting the barrier initialisation or the tensor-memory allocation above the index arithmetic
-    // was tried: the compiler then spills in the dQ drain role.)
-    if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
-        ptx::tmem_relinquish();
-    }
-    if (threadIdx.x == 0) {
-        TRACE(0, 4);
-        // the four descriptor fetches go out together, ahead of the barrier set-up: a load whose
-        // descriptor is not there yet waits for it, and the loads are served in order
-        ptx::prefetch_tensormap(&tm_q);
-        ptx::prefetch_tensormap(&tm_k);
-        ptx::prefetch_tensormap(&tm_v);
-        ptx::prefetch_tensormap(&tm_do);
-        if ((sbase & 1023u) != 0) atomicCAS(&g_device_error, kDevOk, kDevSmemMisaligned);
-        ptx::mbar_init(bar(kKvFull), 1);
-        for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(bar(kQFull + s), 1);
-            ptx::mbar_init(bar(kQEmpty + s), 1);
-            ptx::mbar_init(bar(kDoFull + s), 1);
-            ptx::mbar_init(bar(kDoEmpty + s), 1);
-            ptx::mbar_init(bar(kNegFull + s), FA3B200_STATS_INLINE ? 128 : 64);
-            ptx::mbar_init(bar(kDelFull + s), FA3B200_STATS_INLINE ? 128 : 64);
-            ptx::mbar_init(bar(kStatsEmpty + s), 8);
-        }
-        ptx::mbar_init(bar(kSFull), 1);
-        ptx::mbar_init(bar(kDpFull), 1);
-        ptx::mbar_init(bar(kPReady), 256);
-        ptx::mbar_init(bar(kDsReady), 256);
-        ptx::mbar_init(bar(kDsFree), 1);
-        ptx::mbar_init(bar(kDqFull), 1);
-        ptx::mbar_init(bar(kDqEmpty), 128);
-        ptx::mbar_init(bar(kDkvFull), 1);
-        *abort_flag = 0;
-        ptx::fence_mbar_init();
-        TRACE(0, 2);
-        // The first loads go out before the rest of the CTA has finished its set-up: Q, K, V, dO are
-        // inputs of the call (nothing here depends on the kernel in front), and this thread, which
-        // is the TMA producer, has initialised the barriers they complete on.
-        if (!misaligned) {
-            // tensor maps are [batch][head][row][D]; rows past the end of a sequence read as zero
-            ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
-#pragma unroll
-            for (int bx = 0; bx < C::kBoxes; ++bx) {
-                ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
-                                 k_base + kt * C::kTile, kvh, b_coord);
-                ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
-                                 k_base + kt * C::kTile, kvh, b_coord);
-            }
-            load_q(0);
-            load_do(0);
-            TRACE(0, 3);
-        }
-    }
-    ptx::tc_fence_before();
-    __syncthreads();
-    ptx::tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-    // The kernel behind this one (dQ convert) may begin to launch; it waits for our completion itself.
-    ptx::launch_dependents();
 
     if (wg == 0) {
         ptx::setmaxnreg_dec<C::kRegsControl>();
         if (!misaligned && warp == 0) {
             // =================================================== TMA producer
             if (lane == 0) {
+                if (!FA3B200_EARLY_LOADS) {
+                    ptx::prefetch_tensormap(&tm_q);
+                    ptx::prefetch_tensormap(&tm_k);
+                    ptx::prefetch_tensormap(&tm_v);
+                    ptx::prefetch_tensormap(&tm_do);
+                    // tensor maps are [batch][head][row][D]; rows past the end of a sequence read as zero
+                    ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
+                        ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
+                                         k_base + kt * C::kTile, kvh, b_coord);
+                        ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
+                                         k_base + kt * C::kTile, kvh, b_coord);
+                    }
+                    TRACE(0, 3);
+                }
 #pragma unroll 1
-                for (int t = 1; t < n_steps; ++t) {
+                for (int t = FA3B200_EARLY_LOADS ? 1 : 0; t < n_steps; ++t) {
+                    int hq, qt;
+                    step_coords(t, hq, qt);
+                    const int q_row = q_base + qt * C::kTile;
                     const int s = t % C::kQStages;
                     if (!bounded_wait<true>(bar(kQEmpty + s), ((t / C::kQStages) & 1) ^ 1, abort_flag)) break;
-                    load_q(t);
-                    if (t < 8) TRACE(0, 4 + 2 * t);
+                    ptx::mbar_arrive_expect_tx(bar(kQFull + s), C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
+                        ptx::tma_load_4d(sbase + C::kOffQ + s * C::kOperandBytes + bx * C::kBoxBytes, &tm_q,
+                                         bar(kQFull + s), bx * 64, q_row, hq, b_coord);
+                    }
                     const int sd = t % C::kDoStages;
                     if (!bounded_wait<true>(bar(kDoEmpty + sd), ((t / C::kDoStages) & 1) ^ 1, abort_flag)) break;
-                    load_do(t);
-                    if (t < 8) TRACE(0, 5 + 2 * t);
+                    ptx::mbar_arrive_expect_tx(bar(kDoFull + sd), C::kOperandBytes);
+#pragma unroll
+                    for (int bx = 0; bx < C::kBoxes; ++bx) {
+                        ptx::tma_load_4d(sbase + C::kOffDO + sd * C::kOperandBytes + bx * C::kBoxBytes, &tm_do,
+                                         bar(kDoFull + sd), bx * 64, q_row, hq, b_coord);
+                    }
                 }
             }
         } else if (!misaligned && warp == 1) {
             // ===================================================== MMA issuer
             // The whole warp runs this role converged; MMAs and commits elect their lane inside the asm.
             {
+                TRACE(1, 0);
                 constexpr uint32_t kIdSdP = ptx::instr_desc_f16(kBf16, 128, 128, false, false);
                 constexpr uint32_t kIdDkv = ptx::instr_desc_f16(kBf16, 128, D, false, true);
                 constexpr uint32_t kIdDq = ptx::instr_desc_f16(kBf16, 128, D, true, true);
@@ -512,7 +488,6 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         ptx::mma_ss_lean<true>(tmem + C::kColDP, loV_k + k_step(kk), loDO + k_step(kk), kHi, kIdSdP);
                     ptx::tc_commit_elect(bar(kDpFull));
                 };
-                TRACE(1, 0);
                 bool ok = warp_wait<false>(bar(kKvFull), 0, abort_flag) &&
                           warp_wait<false>(bar(kQFull + 0), 0, abort_flag);
                 TRACE(1, 1);
@@ -521,7 +496,6 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     issue_s(0);
                     TRACE(1, 2);
                     ok = warp_wait<false>(bar(kDoFull + 0), 0, abort_flag);
-                    TRACE(1, 3);
                 }
                 if (ok) {
                     ptx::tc_fence_after();
@@ -531,11 +505,10 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll 1
                 for (int t = 0; ok && t < n_steps; ++t) {
                     const bool more = t + 1 < n_steps;
-                    const int tb = 8 + 8 * t;  // trace slots of this step
                     // dV += P^T dO.  P^T of queries 0-63 sits on columns [0,32) of the S
                     // region, of queries 64-127 on columns [64,96).
                     if (!(ok = warp_wait<false>(bar(kPReady), t & 1, abort_flag))) break;
-                    if (t < 6) TRACE(1, tb + 0);
+                    if (t < 6) TRACE(1, 8 + 8 * t + 0);
                     ptx::tc_fence_after();
                     {
                         const uint32_t loDO = ptx::desc_lo_mn_major(sDO(t), C::kBoxBytes);
@@ -546,7 +519,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                                    loDO + mn_step(kk), kHi, kIdDkv);
                     }
                     ptx::tc_commit_elect(bar(kDoEmpty + t % C::kDoStages));
-                    if (t < 6) TRACE(1, tb + 1);
+                    if (t < 6) TRACE(1, 8 + 8 * t + 1);
                     // S(t+1) may overwrite S/P(t): MMAs execute in issue order.
                     if (more) {
                         if (!(ok = warp_wait<false>(bar(kQFull + (t + 1) % C::kQStages),
@@ -554,117 +527,53 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         ptx::tc_fence_after();
                         issue_s(t + 1);
                     }
-                    if (t < 6) TRACE(1, tb + 2);
+                    if (t < 6) TRACE(1, 8 + 8 * t + 2);
+                    // dK += dS^T Q
                     if (!(ok = warp_wait<false>(bar(kDsReady), t & 1, abort_flag))) break;
-                    if (t < 6) TRACE(1, tb + 3);
+                    if (t < 6) TRACE(1, 8 + 8 * t + 3);
                     ptx::tc_fence_after();
-                    auto issue_dq = [&]() {
-                        // dQ = dS K  (D = 128: overwrites dP(t), which was consumed before kDsReady)
-                        ptx::mma_ss_lean<false>(tmem + C::kColDQ, loDS_mn, loK_mn, kHi, kIdDq);
-#pragma unroll
-                        for (int kk = 1; kk < 8; ++kk)
-                            ptx::mma_ss_lean<true>(tmem + C::kColDQ, loDS_mn + mn_step(kk), loK_mn + mn_step(kk), kHi, kIdDq);
-                        ptx::tc_commit_elect(bar(kDqFull));
-                    };
-                    auto issue_dk = [&]() {
-                        // dK += dS^T Q; its completion frees the Q stage
+                    {
                         const uint32_t loQ = ptx::desc_lo_mn_major(sQ(t), C::kBoxBytes);
                         ptx::mma_ss_lean_rt(tmem + C::kColDK, loDS_k, loQ, kHi, kIdDkv, t > 0 ? 1u : 0u);
 #pragma unroll
                         for (int kk = 1; kk < 8; ++kk)
                             ptx::mma_ss_lean<true>(tmem + C::kColDK, loDS_k + k_step(kk), loQ + mn_step(kk), kHi, kIdDkv);
-                        ptx::tc_commit_elect(bar(kQEmpty + t % C::kQStages));
-                    };
-                    if (kWithDq && D == 64) {  // own dQ region: wait for the drain of step t-1
-                        if (!(ok = warp_wait<false>(bar(kDqEmpty), (t & 1) ^ 1, abort_flag))) break;
-                        ptx::tc_fence_after();
                     }
-                    if (FA3B200_DQ_FIRST) {
-                        if (kWithDq) issue_dq();
-                        issue_dk();
-                    } else {
-                        issue_dk();
-                        if (kWithDq) issue_dq();
+                    ptx::tc_commit_elect(bar(kQEmpty + t % C::kQStages));
+                    if (kWithDq) {
+                        if (D == 64) {  // own dQ region: wait for the drain of step t-1
+                            if (!(ok = warp_wait<false>(bar(kDqEmpty), (t & 1) ^ 1, abort_flag))) break;
+                            ptx::tc_fence_after();
+                        }
+                        // dQ = dS K  (overwrites dP(t) when D = 128: dP(t) was consumed before kDsReady)
+                        ptx::mma_ss_lean<false>(tmem + C::kColDQ, loDS_mn, loK_mn, kHi, kIdDq);
+#pragma unroll
+                        for (int kk = 1; kk < 8; ++kk)
+                            ptx::mma_ss_lean<true>(tmem + C::kColDQ, loDS_mn + mn_step(kk), loK_mn + mn_step(kk), kHi, kIdDq);
+                        ptx::tc_commit_elect(bar(kDqFull));
                     }
                     ptx::tc_commit_elect(bar(kDsFree));
-                    if (t < 6) TRACE(1, tb + 4);
+                    if (t < 6) TRACE(1, 8 + 8 * t + 4);
                     if (more) {
                         if (!(ok = warp_wait<false>(bar(kDoFull + (t + 1) % C::kDoStages),
                                                 ((t + 1) / C::kDoStages) & 1, abort_flag))) break;
-                        if (t < 6) TRACE(1, tb + 5);
+                        if (t < 6) TRACE(1, 8 + 8 * t + 5);
                         if (kWithDq && D == 128) {  // dP(t+1) reuses the dQ(t) columns
                             if (!(ok = warp_wait<false>(bar(kDqEmpty), t & 1, abort_flag))) break;
                         }
-                        if (t < 6) TRACE(1, tb + 6);
+                        if (t < 6) TRACE(1, 8 + 8 * t + 6);
                         ptx::tc_fence_after();
                         issue_dp(t + 1);
-                        if (t < 6) TRACE(1, tb + 7);
+                        if (t < 6) TRACE(1, 8 + 8 * t + 7);
                     }
                 }
                 if (ok) ptx::tc_commit_elect(bar(kDkvFull));
                 TRACE(1, 62);
             }
-        } else if (!misaligned && !FA3B200_STATS_INLINE) {
-            // ================================================= row statistics (warps 2 and 3)
-            // Thread i fetches n and delta of rows i and i+64 of the coming query tile and writes them
-            // to the buffer of that step.  n needs only the caller's log-sum-exp when it is given; delta
-            // (and the sidecar) are written by the kernel in front, which may still be running
-            // (programmatic launch): the wait for it sits between the two.
-            const int i = int(threadIdx.x) - 64;
-            float* stats = reinterpret_cast<float*>(smem + C::kOffStats);
-            const bool direct = a.lse != nullptr;
-            float n_val[2], d_val[2];
-            // P = exp2(x - m) * r = exp2(x + (log2 r - m)); a row past the end of the sequence gets
-            // -inf, which makes its P (and with it dS) exactly zero, as does a row that saw no key
-            auto fetch = [&](int t, bool want_n, bool want_d) {
-                int hq, qt;
-                step_coords(t, hq, qt);
-                const int qi = qt * C::kTile + i;
-                const int64_t row = int64_t(b_coord * a.heads_q + hq) * a.sidecar_rows + q_base + qi;
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    const bool valid = !kCausal || qi + 64 * r < band.seqlen_q;
-                    float n = -INFINITY, d = 0.f;
-                    if (valid) {
-                        if (direct) {
-                            if (want_n) {
-                                const float l = a.lse[row + 64 * r];
-                                n = l == -INFINITY ? -INFINITY : -l * 1.44269504088896340736f;
-                            }
-                            if (want_d) d = a.delta[row + 64 * r];
-                        } else {
-                            const float* sc = a.sidecar + (row + 64 * r) * 3;
-                            if (want_n) n = __log2f(sc[1]) - sc[0];
-                            if (want_d) d = sc[2];
-                        }
-                    }
-                    if (want_n) n_val[r] = n;
-                    if (want_d) d_val[r] = d;
-                }
-            };
-            if (!direct) ptx::grid_dependency_wait();
-            fetch(0, true, false);
-#pragma unroll 1
-            for (int t = 0; t < n_steps; ++t) {
-                const int buf = t & 1;
-                if (t >= 2 && !bounded_wait<true>(bar(kStatsEmpty + buf), ((t >> 1) & 1) ^ 1, abort_flag)) break;
-                stats[buf * 128 + i] = n_val[0];
-                stats[buf * 128 + i + 64] = n_val[1];
-                ptx::mbar_arrive(bar(kNegFull + buf));
-                if (t == 0) {
-                    if (direct) ptx::grid_dependency_wait();
-                    fetch(0, false, true);
-                }
-                stats[256 + buf * 128 + i] = d_val[0];
-                stats[256 + buf * 128 + i + 64] = d_val[1];
-                ptx::mbar_arrive(bar(kDelFull + buf));
-                // one step ahead: the values are first touched at the next stores
-                if (t + 1 < n_steps) fetch(t + 1, true, true);
-            }
         }
     } else if (wg == 1 || wg == 2) {
         // ============================================ softmax / dS warpgroups
-        if constexpr (C::kRegsCompute < 128) ptx::setmaxnreg_dec<C::kRegsCompute>();
+        if (C::kRegsCompute < 128) ptx::setmaxnreg_dec<C::kRegsCompute>();
         else ptx::setmaxnreg_inc<C::kRegsCompute>();
         if (!misaligned) {
             const int half = wg - 1;          // which 64 queries of the tile
@@ -672,145 +581,138 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const uint32_t tl = tmem + (uint32_t((warp & 3) * 32) << 16);
             const uint32_t s_cols = tl + C::kColS + half * 64;
             const uint32_t dp_cols = tl + C::kColDP + half * 64;
-            const float* stats = reinterpret_cast<const float*>(smem + C::kOffStats);
+            float* stats = reinterpret_cast<float*>(smem + C::kOffStats);
             uint32_t ppk[32];
-            bool ok = true;
-            if (FA3B200_PDL_EARLY_WAIT) ptx::grid_dependency_wait();
-#if FA3B200_STATS_INLINE
-            float in_n = 0.f, in_d = 0.f;
-            auto inline_fetch = [&](int t) {
-                int hq, qt;
-                step_coords(t, hq, qt);
+            const float* side_base = a.sidecar;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+            bool s_valid = false;
+            // Statistics of query row qi of head hq, fetched one step ahead.  The loaded values are
+            // not touched here (their first use, one step later, is what waits for the loads); rows
+            // past the end of the sequence read row 0 instead and are replaced at that first use.
+            auto load_stats = [&](int hq, int qt) {
                 const int qi = qt * C::kTile + j;
-                const bool valid = !kCausal || qi < band.seqlen_q;
-                const int64_t row = int64_t(b_coord * a.heads_q + hq) * a.sidecar_rows + q_base + (valid ? qi : 0);
-                float n, d;
-                if (a.lse != nullptr) {
-                    const float l = a.lse[row];
-                    n = l == -INFINITY ? -INFINITY : -l * 1.44269504088896340736f;
-                    d = a.delta[row];
-                } else {
-                    n = __log2f(a.sidecar[row * 3 + 1]) - a.sidecar[row * 3 + 0];
-                    d = a.sidecar[row * 3 + 2];
-                }
-                in_n = valid ? n : -INFINITY;
-                in_d = valid ? d : 0.f;
+                s_valid = qi < band.seqlen_q;
+                const int64_t row = int64_t(b_coord * a.heads_q + hq) * a.sidecar_rows + q_base + (s_valid ? qi : 0);
+                s0 = side_base[row * 3 + 0];
+                s1 = side_base[row * 3 + 1];
+                s2 = side_base[row * 3 + 2];
             };
+            // the sidecar comes from the delta kernel, which may still be running (programmatic launch);
+            // Q, K, V, dO are inputs of the call, so the TMA and MMA warps did not have to wait
             ptx::grid_dependency_wait();
-            if (half == 0) inline_fetch(0);
-#endif
+            if (half == 0) {
+                int hq, qt;
+                step_coords(0, hq, qt);
+                load_stats(hq, qt);
+            }
+            bool ok = true;
 #pragma unroll 1
             for (int t = 0; t < n_steps; ++t) {
                 int hq, qt;
                 step_coords(t, hq, qt);
                 const int buf = t & 1;
-                const int tb = 4 + 8 * t;  // trace slots of this step
                 const float* negp = stats + buf * 128 + half * 64;
                 const float* delp = stats + 256 + buf * 128 + half * 64;
-#if FA3B200_STATS_INLINE
                 if (half == 0) {
-                    float* wstats = reinterpret_cast<float*>(smem + C::kOffStats);
-                    wstats[buf * 128 + j] = in_n;
-                    wstats[256 + buf * 128 + j] = in_d;
-                    ptx::mbar_arrive(bar(kNegFull + buf));
-                    ptx::mbar_arrive(bar(kDelFull + buf));
-                    if (t + 1 < n_steps) inline_fetch(t + 1);
+                    // row statistics of query row j of this tile, for both warpgroups
+                    // P = exp2(x - m) * r = exp2(x + (log2 r - m)); a row past the end of the sequence
+                    // gets -inf, which makes its P (and with it dS) exactly zero
+                    stats[buf * 128 + j] = (!kCausal || s_valid) ? __log2f(s1) - s0 : -INFINITY;
+                    stats[256 + buf * 128 + j] = (!kCausal || s_valid) ? s2 : 0.f;
+                    ptx::mbar_arrive(bar(kStatsFull + buf));
+                    if (t + 1 < n_steps) {
+                        int hq1, qt1;
+                        step_coords(t + 1, hq1, qt1);
+                        load_stats(hq1, qt1);
+                    }
                 }
-#endif
-                if (!(ok = warp_wait(bar(kNegFull + buf), (t >> 1) & 1, abort_flag))) break;
-                if (warp == 4 && t < 7) TRACE(2, tb + 0);
+                if (!(ok = warp_wait(bar(kStatsFull + buf), (t >> 1) & 1, abort_flag))) break;
+                if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 0);
                 if (!(ok = warp_wait(bar(kSFull), t & 1, abort_flag))) break;
-                if (warp == 4 && t < 7) TRACE(2, tb + 1);
+                if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 1);
                 ptx::tc_fence_after();
                 // A tile that crosses an edge of the band or holds keys past the end of the sequence is
                 // masked: element (key j, query i) survives iff mask_from <= i <= mask_to.
                 const bool diagonal = kCausal && tile_needs_mask(kt, qt, band);
                 int mask_from = 0, mask_to = 0;  // set only on masked tiles
-                // ---- P^T = exp2(S^T * scale_log2 + n_i), masked as above.
+                // ---- P^T = exp2(S^T * scale_log2 + neg_i), masked as above.
                 // (two copies of the chunk code, so that unmasked tiles carry no per-element test)
-                // score in log2 units, relative to the row's reference: s * scale*log2e + n, or the
-                // capped score + n
+                // score in log2 units, relative to the row's reference: s * scale*log2e + (log2 r - m), or the
+                // capped score + (log2 r - m)
                 auto log2_score = [&](uint32_t raw, float neg) {
                     return kSoftcap ? fmaf(a.softcap_post, ptx::tanh_approx(__uint_as_float(raw) * a.softcap_pre), neg)
                                     : fmaf(__uint_as_float(raw), a.scale_log2, neg);
                 };
-                // the 64 scores of this thread's key row come in one tensor-memory round trip (two for
-                // the softcap variant, which needs the registers)
-                constexpr int kW = kSoftcap ? 32 : FA3B200_LD_COLS;
+                auto softmax_chunk = [&](int c, const uint32_t* r, auto masked_tag) {
+                    constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-                for (int w = 0; w < 64 / kW; ++w) {
-                    uint32_t r[kW];
-                    if constexpr (kW == 64) ptx::tmem_ld64(s_cols, r);
-                    else ptx::tmem_ld32(s_cols + w * 32, r);
-                    ptx::tmem_ld_wait();
-                    auto softmax_chunk = [&](int c, auto masked_tag) {
-                        constexpr bool kMasked = decltype(masked_tag)::value;
-                        const int rc = kW == 64 ? c * 32 : 0;  // where chunk c starts in r
-#pragma unroll
-                        for (int e = 0; e < 32; e += 4) {
-                            const float4 n4 = *reinterpret_cast<const float4*>(negp + c * 32 + e);
-                            float p0 = ptx::ex2_approx(log2_score(r[rc + e + 0], n4.x));
-                            float p1 = ptx::ex2_approx(log2_score(r[rc + e + 1], n4.y));
-                            float p2 = ptx::ex2_approx(log2_score(r[rc + e + 2], n4.z));
-                            float p3 = ptx::ex2_approx(log2_score(r[rc + e + 3], n4.w));
-                            if (kMasked) {
-                                const int i = half * 64 + c * 32 + e;
-                                p0 = (i + 0 >= mask_from && i + 0 <= mask_to) ? p0 : 0.0f;
-                                p1 = (i + 1 >= mask_from && i + 1 <= mask_to) ? p1 : 0.0f;
-                                p2 = (i + 2 >= mask_from && i + 2 <= mask_to) ? p2 : 0.0f;
-                                p3 = (i + 3 >= mask_from && i + 3 <= mask_to) ? p3 : 0.0f;
-                            }
-                            ppk[c * 16 + e / 2 + 0] = ptx::Pack2<T>::pack(p0, p1);
-                            ppk[c * 16 + e / 2 + 1] = ptx::Pack2<T>::pack(p2, p3);
+                    for (int e = 0; e < 32; e += 4) {
+                        const float4 n4 = *reinterpret_cast<const float4*>(negp + c * 32 + e);
+                        float p0 = ptx::ex2_approx(log2_score(r[e + 0], n4.x));
+                        float p1 = ptx::ex2_approx(log2_score(r[e + 1], n4.y));
+                        float p2 = ptx::ex2_approx(log2_score(r[e + 2], n4.z));
+                        float p3 = ptx::ex2_approx(log2_score(r[e + 3], n4.w));
+                        if (kMasked) {
+                            const int i = half * 64 + c * 32 + e;
+                            p0 = (i + 0 >= mask_from && i + 0 <= mask_to) ? p0 : 0.0f;
+                            p1 = (i + 1 >= mask_from && i + 1 <= mask_to) ? p1 : 0.0f;
+                            p2 = (i + 2 >= mask_from && i + 2 <= mask_to) ? p2 : 0.0f;
+                            p3 = (i + 3 >= mask_from && i + 3 <= mask_to) ? p3 : 0.0f;
                         }
-                        // P chunk c -> columns [16c, 16c+16) of this half's S columns (already read)
-                        ptx::tmem_st16(s_cols + c * 16, &ppk[c * 16]);
-                    };
-                    if (w == 0 && diagonal) query_range_of_key(kt * C::kTile + j, qt * C::kTile, band, &mask_from, &mask_to);
+                        ppk[c * 16 + e / 2 + 0] = ptx::Pack2<T>::pack(p0, p1);
+                        ppk[c * 16 + e / 2 + 1] = ptx::Pack2<T>::pack(p2, p3);
+                    }
+                    // P chunk c -> columns [16c, 16c+16) of this half's S columns (already read)
+                    ptx::tmem_st16(s_cols + c * 16, &ppk[c * 16]);
+                };
+                if (diagonal) {
+                    query_range_of_key(kt * C::kTile + j, qt * C::kTile, band, &mask_from, &mask_to);
 #pragma unroll
-                    for (int c = w * (kW / 32); c < (w + 1) * (kW / 32); ++c) {
-                        if (diagonal) softmax_chunk(c, std::true_type{});
-                        else softmax_chunk(c, std::false_type{});
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(s_cols + c * 32, r);
+                        ptx::tmem_ld_wait();
+                        softmax_chunk(c, r, std::true_type{});
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(s_cols + c * 32, r);
+                        ptx::tmem_ld_wait();
+                        softmax_chunk(c, r, std::false_type{});
                     }
                 }
-                if (warp == 4 && t < 7) TRACE(2, tb + 2);
+                if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 2);
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(bar(kPReady));
-                if (warp == 4 && t < 7) TRACE(2, tb + 3);
+                if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 3);
                 // ---- dS^T = P^T * (dP^T - delta_i), stored [key][query] in the 128-byte swizzle
-                if (!(ok = warp_wait(bar(kDelFull + buf), (t >> 1) & 1, abort_flag))) break;
                 if (!(ok = warp_wait(bar(kDpFull), t & 1, abort_flag))) break;
-                if (warp == 4 && t < 7) TRACE(2, tb + 4);
+                if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 4);
                 if (!(ok = warp_wait(bar(kDsFree), (t & 1) ^ 1, abort_flag))) break;
-                if (warp == 4 && t < 7) TRACE(2, tb + 5);
+                if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 5);
                 ptx::tc_fence_after();
                 const uint32_t ds_row = sbase + C::kOffDS + half * C::kBoxBytes + j * 128;
                 const float inv_post = kSoftcap ? 1.0f / a.softcap_post : 0.0f;
-                constexpr int kWB = kSoftcap ? 32 : FA3B200_LD_COLS_B;
+                auto ds_chunk = [&](int c, const uint32_t* r) {
 #pragma unroll
-                for (int w = 0; w < 64 / kWB; ++w) {
-                    uint32_t rr[kWB];
-                    if constexpr (kWB == 64) ptx::tmem_ld64(dp_cols, rr);
-                    else ptx::tmem_ld32(dp_cols + w * 32, rr);
-                    ptx::tmem_ld_wait();
-                    const uint32_t* r = rr - w * kWB;  // r[e] = dP of query column e of this half
-#pragma unroll
-                    for (int e = w * kWB; e < (w + 1) * kWB; e += 8) {
-                        const float4 d0 = *reinterpret_cast<const float4*>(delp + e);
-                        const float4 d1 = *reinterpret_cast<const float4*>(delp + e + 4);
+                    for (int e = 0; e < 32; e += 8) {
+                        const float4 d0 = *reinterpret_cast<const float4*>(delp + c * 32 + e);
+                        const float4 d1 = *reinterpret_cast<const float4*>(delp + c * 32 + e + 4);
+                        const float2 pa = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 0]);
+                        const float2 pb = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 1]);
+                        const float2 pc = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 2]);
+                        const float2 pd = ptx::Pack2<T>::unpack(ppk[c * 16 + e / 2 + 3]);
                         uint4 o;
                         if (kSoftcap) {
                             // dS = P (dP - delta) (1 - t^2), t recovered from P and the row's reference
-                            const float2 pa = ptx::Pack2<T>::unpack(ppk[e / 2 + 0]);
-                            const float2 pb = ptx::Pack2<T>::unpack(ppk[e / 2 + 1]);
-                            const float2 pc = ptx::Pack2<T>::unpack(ppk[e / 2 + 2]);
-                            const float2 pd = ptx::Pack2<T>::unpack(ppk[e / 2 + 3]);
-                            const float4 n0 = *reinterpret_cast<const float4*>(negp + e);
-                            const float4 n1 = *reinterpret_cast<const float4*>(negp + e + 4);
+                            const float4 n0 = *reinterpret_cast<const float4*>(negp + c * 32 + e);
+                            const float4 n1 = *reinterpret_cast<const float4*>(negp + c * 32 + e + 4);
                             auto capped = [&](float p, uint32_t dp, float del, float neg) {
-                                const float tt = (__log2f(p) - neg) * inv_post;
-                                const float slope = fmaxf(1.0f - tt * tt, 0.0f);
+                                const float t = (__log2f(p) - neg) * inv_post;
+                                const float slope = fmaxf(1.0f - t * t, 0.0f);
                                 return p > 0.0f ? p * (__uint_as_float(dp) - del) * slope : 0.0f;
                             };
                             o.x = ptx::Pack2<T>::pack(capped(pa.x, r[e + 0], d0.x, n0.x), capped(pa.y, r[e + 1], d0.y, n0.y));
@@ -818,33 +720,33 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                             o.z = ptx::Pack2<T>::pack(capped(pc.x, r[e + 4], d1.x, n1.x), capped(pc.y, r[e + 5], d1.y, n1.y));
                             o.w = ptx::Pack2<T>::pack(capped(pd.x, r[e + 6], d1.z, n1.z), capped(pd.y, r[e + 7], d1.w, n1.w));
                         } else {
-                            const float2 pa = ptx::Pack2<T>::unpack(ppk[e / 2 + 0]);
-                            const float2 pb = ptx::Pack2<T>::unpack(ppk[e / 2 + 1]);
-                            const float2 pc = ptx::Pack2<T>::unpack(ppk[e / 2 + 2]);
-                            const float2 pd = ptx::Pack2<T>::unpack(ppk[e / 2 + 3]);
-                            o.x = ptx::Pack2<T>::pack(pa.x * (__uint_as_float(r[e + 0]) - d0.x),
-                                                      pa.y * (__uint_as_float(r[e + 1]) - d0.y));
-                            o.y = ptx::Pack2<T>::pack(pb.x * (__uint_as_float(r[e + 2]) - d0.z),
-                                                      pb.y * (__uint_as_float(r[e + 3]) - d0.w));
-                            o.z = ptx::Pack2<T>::pack(pc.x * (__uint_as_float(r[e + 4]) - d1.x),
-                                                      pc.y * (__uint_as_float(r[e + 5]) - d1.y));
-                            o.w = ptx::Pack2<T>::pack(pd.x * (__uint_as_float(r[e + 6]) - d1.z),
-                                                      pd.y * (__uint_as_float(r[e + 7]) - d1.w));
+                        o.x = ptx::Pack2<T>::pack(pa.x * (__uint_as_float(r[e + 0]) - d0.x),
+                                                  pa.y * (__uint_as_float(r[e + 1]) - d0.y));
+                        o.y = ptx::Pack2<T>::pack(pb.x * (__uint_as_float(r[e + 2]) - d0.z),
+                                                  pb.y * (__uint_as_float(r[e + 3]) - d0.w));
+                        o.z = ptx::Pack2<T>::pack(pc.x * (__uint_as_float(r[e + 4]) - d1.x),
+                                                  pc.y * (__uint_as_float(r[e + 5]) - d1.y));
+                        o.w = ptx::Pack2<T>::pack(pd.x * (__uint_as_float(r[e + 6]) - d1.z),
+                                                  pd.y * (__uint_as_float(r[e + 7]) - d1.w));
                         }
-                        const int chunk = e / 8;  // 16-byte chunk inside this half's box
+                        const int chunk = c * 4 + e / 8;  // 16-byte chunk inside this half's box
                         const uint32_t addr = ds_row + ((chunk ^ (j & 7)) << 4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.x),
                                      "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
                     }
+                };
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(dp_cols + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    ds_chunk(c, r);
                 }
-                if (warp == 4 && t < 7) TRACE(2, tb + 6);
+                if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 6);
                 ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(bar(kDsReady));
-                // both phases have read this step's statistics: the buffer may be refilled
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar(kStatsEmpty + buf));
-                if (warp == 4 && t < 7) TRACE(2, tb + 7);
+                if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 7);
             }
             // ---- epilogue: the first warpgroup writes dK (scaled), the second dV
             if (ok) ok = warp_wait(bar(kDkvFull), 0, abort_flag);
@@ -861,7 +763,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 const int w4 = warp & 3;  // which 32 rows of the tile
                 // packed sequences: the rows behind this sequence's end belong to its neighbour, which the
                 // copy engine cannot know; fp32 outputs of the split path: plain rows.  Both keep per-thread stores.
-                const bool staged = split || (!FA3B200_EPILOGUE_DIRECT && sizeof(TOut) == 2 && a.cu_seqlens_q == nullptr);
+                const bool staged = split || (sizeof(TOut) == 2 && a.cu_seqlens_q == nullptr);
                 if (staged && split && !kBf16) {
                     // fp16 inputs: the partial sums go to this CTA's slabs (slab 2x: dK, 2x+1: dV) as fp16,
                     // boxes of [32 rows][64 x 16 bit].  (fp16 keeps 11 significant bits, three more than a
@@ -1010,22 +912,22 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!kWithDq) {
             ptx::setmaxnreg_dec<C::kRegsControl>();
         } else {
-            if constexpr (C::kRegsDrain < 128) ptx::setmaxnreg_dec<C::kRegsDrain>();
-            else ptx::setmaxnreg_inc<C::kRegsDrain>();
+            ptx::setmaxnreg_inc<C::kRegsDrain>();
             if (!misaligned) {
                 const int qd = warp & 3;
                 const uint32_t tl = tmem + (uint32_t(qd * 32) << 16);
                 const uint32_t stage = sbase + C::kOffStage + qd * 2 * C::kStageBoxBytes;
                 bool pending = false;
+                // the accumulators are cleared by the delta kernel: do not add into them before it is done
+                ptx::grid_dependency_wait();
 #pragma unroll 1
                 for (int t = 0; t < n_steps; ++t) {
                     int hq, qt;
                     step_coords(t, hq, qt);
                     const int q_row = qt * C::kTile + qd * 32;  // row inside the head
                     const int q_head = b_coord * a.heads_q + hq;
-                    const int tb = 4 + 4 * t;
                     if (!warp_wait(bar(kDqFull), t & 1, abort_flag)) break;
-                    if (warp == 12 && t < 12) TRACE(3, tb + 0);
+                    if (warp == 12 && t < 12) TRACE(3, 4 + 4 * t + 0);
                     ptx::tc_fence_after();
                     // pull the whole dQ tile row into registers and hand the columns back at once
                     uint32_t r[D / 32][32];
@@ -1034,9 +936,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     ptx::tmem_ld_wait();
                     ptx::tc_fence_before();
                     ptx::mbar_arrive(bar(kDqEmpty));
-                    if (warp == 12 && t < 12) TRACE(3, tb + 1);
-                    // the accumulators are cleared by the kernel in front: nothing is added before it is done
-                    if (t == 0) ptx::grid_dependency_wait();
+                    if (warp == 12 && t < 12) TRACE(3, 4 + 4 * t + 1);
 #pragma unroll
                     for (int hf = 0; hf < D / 64; ++hf) {
                         if (pending) {
@@ -1065,7 +965,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         }
                         pending = true;
                     }
-                    if (warp == 12 && t < 12) TRACE(3, tb + 2);
+                    if (warp == 12 && t < 12) TRACE(3, 4 + 4 * t + 2);
                 }
                 if (lane == 0) ptx::bulk_wait_group<0>();
                 if (warp == 12) TRACE(3, 59);
@@ -1073,9 +973,7 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     }
 
-    // ---- teardown: everybody meets, then the allocating warp frees TMEM.  A CTA does not retire
-    // before the kernel in front has completed (a CTA without work would otherwise let this grid,
-    // and with it the kernel behind, run ahead of the clearing of the accumulators).
+    // ---- teardown: everybody meets, then the allocating warp frees TMEM
     if (threadIdx.x == 0) ptx::grid_dependency_wait();
     __syncwarp();
     ptx::tc_fence_before();

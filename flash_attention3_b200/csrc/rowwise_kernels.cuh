@@ -176,7 +176,8 @@ struct ConvertSegments {
 
 // dst[i] = T(scale * accum[i]).  8 elements per thread: 32 B in, 16 B out.
 // Algorithmic HBM bytes per element: 4 read + 2 written.
-template <typename T>
+// kSlabs = false: dQ alone (every problem whose key tiles are not split), a lean single-segment loop.
+template <typename T, bool kSlabs>
 __global__ void __launch_bounds__(256)
 dq_convert_kernel(const __grid_constant__ ConvertSegments seg) {
 #ifdef FA3B200_TRACE
@@ -187,13 +188,13 @@ dq_convert_kernel(const __grid_constant__ ConvertSegments seg) {
     // The segments form one index space, so that with enough blocks every thread makes a single
     // load -> store trip whatever the number of segments (small problems are latency-bound here).
     const int64_t n0 = seg.n_vec8[0];
-    const int64_t n01 = n0 + (seg.count > 1 ? seg.n_vec8[1] : 0);
-    const int64_t total = n01 + (seg.count > 2 ? seg.n_vec8[2] : 0);
+    const int64_t n01 = n0 + (kSlabs ? seg.n_vec8[1] : 0);
+    const int64_t total = n01 + (kSlabs ? seg.n_vec8[2] : 0);
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     const int vec_per_row = seg.head_dim / 8;
     for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += stride) {
         // (selects instead of indexing: the parameter arrays stay in constant memory)
-        const int sgi = g < n0 ? 0 : (g < n01 ? 1 : 2);
+        const int sgi = !kSlabs ? 0 : (g < n0 ? 0 : (g < n01 ? 1 : 2));
         const int64_t i = g - (sgi == 0 ? 0 : (sgi == 1 ? n0 : n01));
         T* __restrict__ dst = static_cast<T*>(sgi == 0 ? seg.dst[0] : (sgi == 1 ? seg.dst[1] : seg.dst[2]));
         const float scale = sgi == 0 ? seg.scale[0] : (sgi == 1 ? seg.scale[1] : seg.scale[2]);

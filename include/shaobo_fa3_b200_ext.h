@@ -52,14 +52,14 @@ int shaobo_fa3_b200_last_stage_ms(float* ms3);
  * SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES inside the library.  It holds what the
  * workspace of shaobo_fa3_bwd_v2 holds: the fp32 dQ accumulator
  * (4*B*Hq*Sq*D bytes), on small problems whose key tiles are split over
- * several thread blocks the fp32 partial dK/dV sums of those blocks (256*D
- * bytes per block, up to 148 blocks), delta and the packed sidecar (16 bytes
- * per query row).  The call performs no cudaMalloc, no cudaFree and no other
+ * several thread blocks the partial dK/dV sums of those blocks (512*D bytes
+ * per block for fp16 inputs, 1024*D for bf16 inputs, up to 148 blocks), delta
+ * and the packed sidecar (16 bytes per query row).  The call performs no cudaMalloc, no cudaFree and no other
  * allocating runtime or library call.
  *
  * Limit: the problem must satisfy
  *     shaobo_fa3_bwd_v2_workspace_bytes(params) <= SHAOBO_FA3_B200_STATIC_SCRATCH_BYTES
- * (ask that function; e.g. B=1,H=4,S=2048,D=128 needs 22 MiB and
+ * (ask that function; e.g. B=1,H=4,S=2048,D=128 fp16 needs 13 MiB and
  * B=1,H=15,S=4096,D=128 31 MiB, B=2,H=16,S=2048,D=128 does not fit).  A larger
  * problem returns SHAOBO_FA3_STATUS_UNSUPPORTED and launches nothing.  Status
  * codes otherwise follow shaobo_fa3_bwd_v2 in the same order: parameter

@@ -61,12 +61,12 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
 def test_split_tiles_deterministic_path_and_a_problem_just_under_the_limit():
     lib = capi.load()
     # (a) the benchmark's small shape: its key tiles are split over 136 thread blocks, whose partial
-    #     dK/dV sums live in the built-in array too (22 MiB of the 32)
+    #     dK/dV sums live in the built-in array too (13 MiB of the 32)
     prob = helpers.Problem(1, 4, 4, 2048, 128, "fp16", True, seed=903)
     x = prob.device_inputs()
     p = ops.make_params(x["q"], x["k"], True, prob.scale)
     need = lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p))
-    assert 16 << 20 < need <= capi.STATIC_SCRATCH_BYTES
+    assert 8 << 20 < need <= capi.STATIC_SCRATCH_BYTES
     for attempt in range(2):
         helpers.assert_parity(_call_noalloc(prob, x), prob, f"split tiles, attempt {attempt}")
     # (b) the atomic-free path through the same array: bitwise the ordinary entry point's result
