@@ -51,6 +51,7 @@ CONFIGS = {
     # profiler-sized case: ~0.2 GB on the device, working set above the 126 MB L2
     "P1": (1, 16, 16, 4096, 128, "bf16", False, "B=1,H=16,S=4096,D=128 non-causal bf16 (profiling case)"),
     "P2": (1, 16, 16, 4096, 128, "bf16", True, "B=1,H=16,S=4096,D=128 causal bf16 (profiling case)"),
+    "P3": (1, 16, 16, 4096, 64, "bf16", False, "B=1,H=16,S=4096,D=64 non-causal bf16 (profiling case)"),
 }
 METRIC = "fa3_bwd_tflops"
 UNIT = "TFLOP/s"

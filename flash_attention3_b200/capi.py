@@ -77,12 +77,9 @@ _lib = None
 def load(build_if_missing: bool = True) -> ctypes.CDLL:
     """Load the in-tree library.  There is no fallback: a missing or unloadable
     library raises."""
-    global _lib, LIB_PATH
+    global _lib
     if _lib is not None:
         return _lib
-    override = os.environ.get("FA3B200_LIB")  # development aid: A/B a differently built library
-    if override:
-        LIB_PATH = pathlib.Path(override).resolve()
     if not LIB_PATH.exists():
         if not build_if_missing:
             raise FileNotFoundError(f"{LIB_PATH} is not built")

@@ -45,11 +45,9 @@ enum CtaOrderMode : int {
     kOrderSerpentine = 2,
 };
 
-#ifndef FA3B200_DQ_L2_BUDGET_MB
-#define FA3B200_DQ_L2_BUDGET_MB 64
-#endif
-// dQ-accumulator bytes that the CTAs running at the same time may spread over (about half of L2)
-constexpr long long kDqL2BudgetBytes = (long long)(FA3B200_DQ_L2_BUDGET_MB) << 20;
+// dQ-accumulator bytes that the CTAs running at the same time may spread over (about half of L2;
+// 16 and 32 MB measured slower on the S=8192 shapes)
+constexpr long long kDqL2BudgetBytes = 64LL << 20;
 
 struct CtaOrderPlan {
     int mode = kOrderHeavyFirst;

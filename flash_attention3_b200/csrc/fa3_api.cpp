@@ -6,7 +6,10 @@
 // 122-156), widened to BF16 and head_dim 64.
 #include <cmath>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <queue>
+#include <tuple>
 #include <vector>
 #include <limits>
 
@@ -124,16 +127,41 @@ size_t dq_accum_bytes(const ShaoboFa3Params* p) {
     return out;
 }
 
+namespace {
+// The plan is a pure function of these; a call asks for it several times (workspace size, launch,
+// convert) and the search below simulates a schedule per candidate, so answers are remembered.
+using SplitKey = std::tuple<int, int, int, int, int, long long, long long>;
+std::mutex g_split_mu;
+std::map<SplitKey, SplitPlan> g_split_cache;
+}  // namespace
+
+static SplitPlan search_split_plan(const ShaoboFa3Params* p, int tiles, const Band& band, long long heads, long long group);
+
 SplitPlan split_plan(const ShaoboFa3Params* p) {
-    SplitPlan plan;
     // (per-sequence lengths of packed sequences, and used lengths, are not known on the host: no
     // splitting there)
-    if (!fused_shape_ok(p) || p->deterministic != 0 || is_varlen(p) || has_seqused(p)) return plan;
+    if (!fused_shape_ok(p) || p->deterministic != 0 || is_varlen(p) || has_seqused(p)) return SplitPlan{};
     const int tiles = tiles_of(p->seqlen_k);
     const Band band = band_of(p);
     const long long heads = (long long)p->batch * p->num_heads_kv;
-    if (tiles * heads >= kSplitSmCount) return plan;
+    if (tiles * heads >= kSplitSmCount) return SplitPlan{};
     const long long group = p->num_heads_q / p->num_heads_kv;
+    const SplitKey key{band.seqlen_q, band.seqlen_k, band.left, band.right, band.off, heads, group};
+    {
+        std::lock_guard<std::mutex> lock(g_split_mu);
+        auto it = g_split_cache.find(key);
+        if (it != g_split_cache.end()) return it->second;
+    }
+    const SplitPlan plan = search_split_plan(p, tiles, band, heads, group);
+    std::lock_guard<std::mutex> lock(g_split_mu);
+    if (g_split_cache.size() > 4096) g_split_cache.clear();
+    g_split_cache[key] = plan;
+    return plan;
+}
+
+static SplitPlan search_split_plan(const ShaoboFa3Params* p, int tiles, const Band& band, long long heads, long long group) {
+    (void)p;
+    SplitPlan plan;
     long long longest = 0;  // steps of the heaviest key tile
     for (int kt = 0; kt < tiles; ++kt) {
         const long long steps = group * q_tiles_of_k_tile(kt, band);

@@ -81,11 +81,6 @@ __device__ __forceinline__ long long trace_globaltimer() {
 #define TRACE_GT(role, ev) do {} while (0)
 #endif
 
-// Build-time choice measured on the GPU.
-#ifndef FA3B200_EARLY_LOADS
-#define FA3B200_EARLY_LOADS 0   // 1: K, V and the first Q / dO tiles are requested before the CTA's set-up barrier
-#endif
-
 struct FusedArgs {
     const float* sidecar;  // [B,Hq,Sq,3] = {m, r, delta} per query row (packed sequences: [Hq, total_q, 3])
     void* dk;              // [B,Hkv,Sk,D] or [B,Sk,Hkv,D], see kv_strides
@@ -341,42 +336,6 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         *abort_flag = 0;
         ptx::fence_mbar_init();
         TRACE(0, 2);
-        if (FA3B200_EARLY_LOADS && !misaligned) {
-            // Q, K, V, dO are inputs of the call: nothing here depends on the kernel in front, and this
-            // thread (the TMA producer) has just initialised the barriers the loads complete on
-            ptx::prefetch_tensormap(&tm_k);
-            ptx::prefetch_tensormap(&tm_v);
-            ptx::prefetch_tensormap(&tm_q);
-            ptx::prefetch_tensormap(&tm_do);
-            ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
-#pragma unroll
-            for (int bx = 0; bx < C::kBoxes; ++bx) {
-                ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
-                                 k_base + kt * C::kTile, kvh, b_coord);
-                ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
-                                 k_base + kt * C::kTile, kvh, b_coord);
-            }
-            // first query tile of this CTA (what step_coords(0) gives)
-            const int g0 = t_begin / steps_per_head;
-            const int r0 = t_begin - g0 * steps_per_head;
-            int qt0 = q_begin + r0;
-            if (!kCausal) {
-                qt0 = r0 + ((n_q_tiles == 0) ? 0 : kt % n_q_tiles);
-                if (qt0 >= n_q_tiles) qt0 -= n_q_tiles;
-            }
-            const int hq0 = kvh * group + g0;
-            ptx::mbar_arrive_expect_tx(bar(kQFull + 0), C::kOperandBytes);
-#pragma unroll
-            for (int bx = 0; bx < C::kBoxes; ++bx)
-                ptx::tma_load_4d(sbase + C::kOffQ + bx * C::kBoxBytes, &tm_q, bar(kQFull + 0), bx * 64,
-                                 q_base + qt0 * C::kTile, hq0, b_coord);
-            ptx::mbar_arrive_expect_tx(bar(kDoFull + 0), C::kOperandBytes);
-#pragma unroll
-            for (int bx = 0; bx < C::kBoxes; ++bx)
-                ptx::tma_load_4d(sbase + C::kOffDO + bx * C::kBoxBytes, &tm_do, bar(kDoFull + 0), bx * 64,
-                                 q_base + qt0 * C::kTile, hq0, b_coord);
-            TRACE(0, 3);
-        }
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
@@ -411,24 +370,22 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!misaligned && warp == 0) {
             // =================================================== TMA producer
             if (lane == 0) {
-                if (!FA3B200_EARLY_LOADS) {
-                    ptx::prefetch_tensormap(&tm_q);
-                    ptx::prefetch_tensormap(&tm_k);
-                    ptx::prefetch_tensormap(&tm_v);
-                    ptx::prefetch_tensormap(&tm_do);
-                    // tensor maps are [batch][head][row][D]; rows past the end of a sequence read as zero
-                    ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
+                ptx::prefetch_tensormap(&tm_q);
+                ptx::prefetch_tensormap(&tm_k);
+                ptx::prefetch_tensormap(&tm_v);
+                ptx::prefetch_tensormap(&tm_do);
+                // tensor maps are [batch][head][row][D]; rows past the end of a sequence read as zero
+                ptx::mbar_arrive_expect_tx(bar(kKvFull), 2 * C::kOperandBytes);
 #pragma unroll
-                    for (int bx = 0; bx < C::kBoxes; ++bx) {
-                        ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
-                                         k_base + kt * C::kTile, kvh, b_coord);
-                        ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
-                                         k_base + kt * C::kTile, kvh, b_coord);
-                    }
-                    TRACE(0, 3);
+                for (int bx = 0; bx < C::kBoxes; ++bx) {
+                    ptx::tma_load_4d(sbase + C::kOffK + bx * C::kBoxBytes, &tm_k, bar(kKvFull), bx * 64,
+                                     k_base + kt * C::kTile, kvh, b_coord);
+                    ptx::tma_load_4d(sbase + C::kOffV + bx * C::kBoxBytes, &tm_v, bar(kKvFull), bx * 64,
+                                     k_base + kt * C::kTile, kvh, b_coord);
                 }
+                TRACE(0, 3);
 #pragma unroll 1
-                for (int t = FA3B200_EARLY_LOADS ? 1 : 0; t < n_steps; ++t) {
+                for (int t = 0; t < n_steps; ++t) {
                     int hq, qt;
                     step_coords(t, hq, qt);
                     const int q_row = q_base + qt * C::kTile;
