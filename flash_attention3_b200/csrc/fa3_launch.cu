@@ -1027,24 +1027,32 @@ struct HostLanes {
     std::mutex enqueue[128];   // one call at a time enqueues on a device's lanes (see the entry point)
     bool ready[128] = {};
     cudaStream_t stream[128][kHostLanes] = {};
+    cudaStream_t aux[128][kHostLanes] = {};      // second stream of a lane: carries half of its copies-in
     cudaEvent_t fork[128] = {};
     cudaEvent_t join[128][kHostLanes] = {};
+    cudaEvent_t aux_done[128][kHostLanes] = {};
     bool get(int dev) {
         std::lock_guard<std::mutex> lock(mu);
         if (ready[dev]) return true;
         bool ok = cudaEventCreateWithFlags(&fork[dev], cudaEventDisableTiming) == cudaSuccess;
         for (int i = 0; ok && i < kHostLanes; ++i) {
             ok = cudaStreamCreateWithFlags(&stream[dev][i], cudaStreamNonBlocking) == cudaSuccess &&
-                 cudaEventCreateWithFlags(&join[dev][i], cudaEventDisableTiming) == cudaSuccess;
+                 cudaStreamCreateWithFlags(&aux[dev][i], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&join[dev][i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&aux_done[dev][i], cudaEventDisableTiming) == cudaSuccess;
         }
         if (!ok) {  // give back what was made: the next call starts from nothing
             if (fork[dev] != nullptr) cudaEventDestroy(fork[dev]);
             fork[dev] = nullptr;
             for (int i = 0; i < kHostLanes; ++i) {
                 if (stream[dev][i] != nullptr) cudaStreamDestroy(stream[dev][i]);
+                if (aux[dev][i] != nullptr) cudaStreamDestroy(aux[dev][i]);
                 if (join[dev][i] != nullptr) cudaEventDestroy(join[dev][i]);
+                if (aux_done[dev][i] != nullptr) cudaEventDestroy(aux_done[dev][i]);
                 stream[dev][i] = nullptr;
+                aux[dev][i] = nullptr;
                 join[dev][i] = nullptr;
+                aux_done[dev][i] = nullptr;
             }
             (void)cudaGetLastError();
             return false;
@@ -1060,14 +1068,9 @@ struct HostPiece {
     int batch_begin, batch_count, kv_head_begin, kv_head_count;
 };
 
-// First unit of shard r of n.  Shards are contiguous and as even as possible, except that with two
-// shards the second one is small (a quarter of the units): nothing overlaps the last shard's kernels
-// and copy-out, so the shorter it is the sooner the call ends (measured on 16.8 MB over PCIe: 365 us
-// with two equal shards).
-long long host_shard_begin(long long units, int r, int n) {
-    if (n == 2 && r == 1 && units >= 2) return units - std::max<long long>(1, units / 4);
-    return units * r / n;
-}
+// First unit of shard r of n: contiguous shards, as even as possible.  (A small last shard, to shorten
+// the tail nothing overlaps, measured slower: 395 against 368 us on 16.8 MB.)
+long long host_shard_begin(long long units, int r, int n) { return units * r / n; }
 
 // Pieces of shard r of n.
 int host_pieces(const ShaoboFa3Params* p, int r, int n, HostPiece* out) {
@@ -1218,8 +1221,12 @@ extern "C" int shaobo_fa3_b200_bwd_v2_host(const void* dout, const void* q, cons
             for (int i = 0; i < cnt; ++i, ++piece_index) {
                 const int lane = piece_index % kHostLanes;
                 cudaStream_t st = g_host_lanes.stream[dev][lane];
+                cudaStream_t ax = g_host_lanes.aux[dev][lane];
                 if (!used[lane]) {
-                    if (cudaStreamWaitEvent(st, g_host_lanes.fork[dev], 0) != cudaSuccess) return SHAOBO_FA3_STATUS_HIP_ERROR;
+                    if (cudaStreamWaitEvent(st, g_host_lanes.fork[dev], 0) != cudaSuccess ||
+                        cudaStreamWaitEvent(ax, g_host_lanes.fork[dev], 0) != cudaSuccess) {
+                        return SHAOBO_FA3_STATUS_HIP_ERROR;
+                    }
                     used[lane] = true;
                 }
                 const HostPiece& pc = pcs[i];
@@ -1227,15 +1234,21 @@ extern "C" int shaobo_fa3_b200_bwd_v2_host(const void* dout, const void* q, cons
                 const size_t kh = size_t(pc.batch_begin) * params->num_heads_kv + pc.kv_head_begin;
                 const size_t q_n = size_t(pc.batch_count) * pc.kv_head_count * group;  // query heads in the piece
                 const size_t k_n = size_t(pc.batch_count) * pc.kv_head_count;
+                // the copies-in of a piece alternate between the lane's two streams: one stream hands the
+                // copy engine its next copy only after the previous one has completed, two keep it fed
+                int h2d_count = 0;
                 auto h2d = [&](uint8_t* d, const void* h, size_t off, size_t bytes) {
-                    return cudaMemcpyAsync(d + off, static_cast<const uint8_t*>(h) + off, bytes, cudaMemcpyHostToDevice, st) == cudaSuccess;
+                    cudaStream_t s_copy = (h2d_count++ & 1) ? ax : st;
+                    return cudaMemcpyAsync(d + off, static_cast<const uint8_t*>(h) + off, bytes, cudaMemcpyHostToDevice, s_copy) == cudaSuccess;
                 };
                 auto d2h = [&](void* h, const uint8_t* d, size_t off, size_t bytes) {
                     return cudaMemcpyAsync(static_cast<uint8_t*>(h) + off, d + off, bytes, cudaMemcpyDeviceToHost, st) == cudaSuccess;
                 };
                 if (!h2d(d_q, q, qh * q_head, q_n * q_head) || !h2d(d_k, k, kh * kv_head, k_n * kv_head) ||
                     !h2d(d_v, v, kh * kv_head, k_n * kv_head) || !h2d(d_do, dout, qh * q_head, q_n * q_head) ||
-                    !h2d(d_out, out, qh * q_head, q_n * q_head) || !h2d(d_lse, softmax_lse, qh * lse_head, q_n * lse_head)) {
+                    !h2d(d_out, out, qh * q_head, q_n * q_head) || !h2d(d_lse, softmax_lse, qh * lse_head, q_n * lse_head) ||
+                    cudaEventRecord(g_host_lanes.aux_done[dev][lane], ax) != cudaSuccess ||
+                    cudaStreamWaitEvent(st, g_host_lanes.aux_done[dev][lane], 0) != cudaSuccess) {
                     return SHAOBO_FA3_STATUS_HIP_ERROR;
                 }
                 ShaoboFa3Params s = piece_params(params, pc);
@@ -1260,7 +1273,10 @@ extern "C" int shaobo_fa3_b200_bwd_v2_host(const void* dout, const void* q, cons
     // lanes: after an error return no copy into the caller's host buffers is left running unordered.
     for (int lane = 0; lane < kHostLanes; ++lane) {
         if (!used[lane]) continue;
-        if (cudaEventRecord(g_host_lanes.join[dev][lane], g_host_lanes.stream[dev][lane]) != cudaSuccess ||
+        // (the second stream of the lane is joined into the first once more: after an error it may not have been)
+        if (cudaEventRecord(g_host_lanes.aux_done[dev][lane], g_host_lanes.aux[dev][lane]) != cudaSuccess ||
+            cudaStreamWaitEvent(g_host_lanes.stream[dev][lane], g_host_lanes.aux_done[dev][lane], 0) != cudaSuccess ||
+            cudaEventRecord(g_host_lanes.join[dev][lane], g_host_lanes.stream[dev][lane]) != cudaSuccess ||
             cudaStreamWaitEvent(caller, g_host_lanes.join[dev][lane], 0) != cudaSuccess) {
             if (status == SHAOBO_FA3_STATUS_SUCCESS) status = SHAOBO_FA3_STATUS_HIP_ERROR;
         }
