@@ -17,6 +17,13 @@
 // The softmax scale is applied once at the end (dK in the epilogue, dQ in the
 // convert kernel) instead of per element of dS.
 //
+// Epilogue: when the last MMA has completed, every softmax warp stages its 32 key rows of dK
+// (scaled) or dV over the dead Q / dO / dS^T buffers in the layout of a swizzled TMA box and one
+// lane stores them with the copy engine.  On problems too small to fill the GPU the query steps
+// of a key tile are cut into chunks, one CTA each (a table in the kernel parameters says which,
+// longest chunks first); such a CTA stores its partial dK / dV to its own slab and the convert
+// kernel adds the slabs of a tile in chunk order.
+//
 // Warp roles (512 threads, four warpgroups): warp 0 = TMA producer, warp 1 = MMA
 // issuer and TMEM owner; warps 4-7 and 8-11 = two softmax / dS warpgroups (thread
 // j of each owns TMEM lane j = key j; the first takes queries 0-63 of the tile,
