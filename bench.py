@@ -502,6 +502,12 @@ def main():
             ms = statistics.median(t2)
             also[name] = {"ms_per_step": ms, "tflops": w2.flops / (ms * 1e-3) / 1e12,
                           "workload": CONFIGS[name][7]}
+            if name == "C4":
+                # the large shape through the host-tensor call: PCIe-bound, eight pipelined shards
+                te, h2d, d2h = time_e2e(torch, w2, 5, 3, flush, ops)
+                me = statistics.median(te)
+                also[name]["e2e"] = {"ms_per_step": me, "tflops": w2.flops / (me * 1e-3) / 1e12,
+                                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
             del w2
             torch.cuda.empty_cache()
         for name in ("C3d128", "C3d64", "C4"):
