@@ -157,7 +157,11 @@ struct FusedCfg {
     static constexpr int kOffDS = kOffDO + kDoStages * kOperandBytes;
     static constexpr int kOffStage = kOffDS + kDsBytes;
     static constexpr int kOffStats = kOffStage + kStageBytes;
-    static constexpr int kOffBar = kOffStats + 2048;
+    // Row statistics: kStatsBufs buffers of 128 x {log2 r - m} followed by as many of 128 x {delta}.  With three
+    // buffers (D=64, where the softmax warpgroups bound the step) a step's statistics are written one
+    // step ahead, so nobody waits for the writers; D=128 has no shared memory left for a third.
+    static constexpr int kStatsBufs = D == 64 ? 3 : 2;
+    static constexpr int kOffBar = kOffStats + kStatsBufs * 1024;
     static constexpr int kSmemBytes = kOffBar + 256;
     static_assert(kSmemBytes <= 232448, "shared-memory ledger exceeds 227 KiB");
     static_assert(kOffStage % 1024 == 0 && kOffDS % 1024 == 0, "swizzled regions need 1 KiB alignment");
@@ -188,7 +192,7 @@ enum Bar : int {
     kDpFull = 10,
     kPReady = 11,
     kDsReady = 12,
-    kDsFree = 13,
+    kUnused13 = 13,
     kDqFull = 14,
     kDqEmpty = 15,
     kDkvFull = 16,
@@ -330,13 +334,12 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::mbar_init(bar(kQEmpty + s), 1);
             ptx::mbar_init(bar(kDoFull + s), 1);
             ptx::mbar_init(bar(kDoEmpty + s), 1);
-            ptx::mbar_init(bar(kStatsFull + s), 128);
         }
+        for (int s = 0; s < 2; ++s) ptx::mbar_init(bar(kStatsFull + s), 128);  // (unused with three buffers)
         ptx::mbar_init(bar(kSFull), 1);
         ptx::mbar_init(bar(kDpFull), 1);
         ptx::mbar_init(bar(kPReady), 256);
         ptx::mbar_init(bar(kDsReady), 256);
-        ptx::mbar_init(bar(kDsFree), 1);
         ptx::mbar_init(bar(kDqFull), 1);
         ptx::mbar_init(bar(kDqEmpty), 128);
         ptx::mbar_init(bar(kDkvFull), 1);
@@ -516,7 +519,6 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                             ptx::mma_ss_lean<true>(tmem + C::kColDQ, loDS_mn + mn_step(kk), loK_mn + mn_step(kk), kHi, kIdDq);
                         ptx::tc_commit_elect(bar(kDqFull));
                     }
-                    ptx::tc_commit_elect(bar(kDsFree));
                     if (t < 6) TRACE(1, 8 + 8 * t + 4);
                     if (more) {
                         if (!(ok = warp_wait<false>(bar(kDoFull + (t + 1) % C::kDoStages),
@@ -564,33 +566,64 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // the sidecar comes from the delta kernel, which may still be running (programmatic launch);
             // Q, K, V, dO are inputs of the call, so the TMA and MMA warps did not have to wait
             ptx::grid_dependency_wait();
+            constexpr int kNB = C::kStatsBufs;
+            constexpr bool kStatsAhead = kNB == 3;
+            // row statistics of query row j of a tile, for both warpgroups:
+            // P = exp2(x - m) * r = exp2(x + (log2 r - m)); a row past the end of the sequence
+            // gets -inf, which makes its P (and with it dS) exactly zero
+            auto publish_stats = [&](int buf) {
+                stats[buf * 128 + j] = (!kCausal || s_valid) ? __log2f(s1) - s0 : -INFINITY;
+                stats[kNB * 128 + buf * 128 + j] = (!kCausal || s_valid) ? s2 : 0.f;
+                if (!kStatsAhead) ptx::mbar_arrive(bar(kStatsFull + buf));
+            };
             if (half == 0) {
                 int hq, qt;
                 step_coords(0, hq, qt);
                 load_stats(hq, qt);
+                if (kStatsAhead) {
+                    publish_stats(0);
+                    if (n_steps > 1) {
+                        step_coords(1, hq, qt);
+                        load_stats(hq, qt);
+                    }
+                }
             }
+            // (step 0's statistics are the exception: one meeting of the two warpgroups)
+            if (kStatsAhead) asm volatile("bar.sync 1, 256;" ::: "memory");
             bool ok = true;
 #pragma unroll 1
             for (int t = 0; t < n_steps; ++t) {
+                if (warp == 4 && t == 3) TRACE(2, 0);
                 int hq, qt;
                 step_coords(t, hq, qt);
-                const int buf = t & 1;
+                if (warp == 4 && t == 3) TRACE(2, 1);
+                const int buf = t % kNB;
                 const float* negp = stats + buf * 128 + half * 64;
-                const float* delp = stats + 256 + buf * 128 + half * 64;
+                const float* delp = stats + kNB * 128 + buf * 128 + half * 64;
                 if (half == 0) {
-                    // row statistics of query row j of this tile, for both warpgroups
-                    // P = exp2(x - m) * r = exp2(x + (log2 r - m)); a row past the end of the sequence
-                    // gets -inf, which makes its P (and with it dS) exactly zero
-                    stats[buf * 128 + j] = (!kCausal || s_valid) ? __log2f(s1) - s0 : -INFINITY;
-                    stats[256 + buf * 128 + j] = (!kCausal || s_valid) ? s2 : 0.f;
-                    ptx::mbar_arrive(bar(kStatsFull + buf));
-                    if (t + 1 < n_steps) {
-                        int hq1, qt1;
-                        step_coords(t + 1, hq1, qt1);
-                        load_stats(hq1, qt1);
+                    if (kStatsAhead) {
+                        // the registers hold step t+1: publish it now (its buffer was last read in step
+                        // t-2, which every warp has left: this warpgroup could not have written dS(t-1)
+                        // before dS(t-2) of both was consumed), then fetch step t+2
+                        if (t + 1 < n_steps) publish_stats((t + 1) % kNB);
+                        if (warp == 4 && t == 3) TRACE(2, 2);
+                    } else {
+                        publish_stats(buf);
+                        if (warp == 4 && t == 3) TRACE(2, 2);
+                        if (t + 1 < n_steps) {
+                            int hq1, qt1;
+                            step_coords(t + 1, hq1, qt1);
+                            load_stats(hq1, qt1);
+                        }
                     }
                 }
-                if (!(ok = warp_wait(bar(kStatsFull + buf), (t >> 1) & 1, abort_flag))) break;
+                if (warp == 4 && t == 3) TRACE(2, 3);
+                // Published one step ahead, the statistics of step t need no barrier of their own: their
+                // writers arrived at "P ready" of step t-1 after writing them, S(t) was issued after that
+                // barrier completed, and every reader waits for S(t) below.
+                if (!kStatsAhead) {
+                    if (!(ok = warp_wait(bar(kStatsFull + buf), (t / kNB) & 1, abort_flag))) break;
+                }
                 if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 0);
                 if (!(ok = warp_wait(bar(kSFull), t & 1, abort_flag))) break;
                 if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 1);
@@ -651,11 +684,18 @@ fused_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(bar(kPReady));
+                if (kStatsAhead && half == 0 && t + 2 < n_steps) {
+                    // (requested here, where the warp is about to wait for dP anyway)
+                    int hq2, qt2;
+                    step_coords(t + 2, hq2, qt2);
+                    load_stats(hq2, qt2);
+                }
                 if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 3);
                 // ---- dS^T = P^T * (dP^T - delta_i), stored [key][query] in the 128-byte swizzle
                 if (!(ok = warp_wait(bar(kDpFull), t & 1, abort_flag))) break;
                 if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 4);
-                if (!(ok = warp_wait(bar(kDsFree), (t & 1) ^ 1, abort_flag))) break;
+                // (the dS buffer is free: dP(t) was issued behind dK(t-1), dQ(t-1), the readers of dS(t-1),
+                // and the barrier just passed completes only when every MMA issued before it has)
                 if (warp == 4 && t < 7) TRACE(2, 4 + 8 * t + 5);
                 ptx::tc_fence_after();
                 const uint32_t ds_row = sbase + C::kOffDS + half * C::kBoxBytes + j * 128;

@@ -139,6 +139,12 @@ def main():
     stat("softmax: first dP seen", [rel(c, 2, 4 + 4) for c in ctas])
     stat("softmax: first dS written", [rel(c, 2, 4 + 6) for c in ctas])
     stat("drain: first dQ seen", [rel(c, 3, 4 + 0) for c in ctas])
+    print("-- top of step 3, softmax warp 4 (first warpgroup: row statistics bookkeeping)")
+    stat("dS(2) handed over -> loop top", [diff(c, 2, 0, 2, 4 + 8 * 2 + 7) for c in ctas])
+    stat("tile coordinates of the step", [diff(c, 2, 1, 2, 0) for c in ctas])
+    stat("statistics published", [diff(c, 2, 2, 2, 1) for c in ctas])
+    stat("next statistics requested", [diff(c, 2, 3, 2, 2) for c in ctas])
+    stat("statistics barrier passed", [diff(c, 2, 4 + 8 * 3 + 0, 2, 3) for c in ctas])
     print("-- per step (clk), softmax warp 4")
     for t in range(0, 6):
         tb = 4 + 8 * t
