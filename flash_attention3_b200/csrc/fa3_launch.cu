@@ -216,14 +216,25 @@ void launch_delta_t(const void* dout, const void* out, const float* aux0, const 
     int64_t blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
     const int64_t cap = int64_t(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
+    // programmatic launch: behind the convert kernel of a preceding call the blocks are placed while
+    // that one drains (the kernel itself waits for everything in front of it before it touches memory)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(blocks));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const T* dout_t = static_cast<const T*>(dout);
+    const T* out_t = static_cast<const T*>(out);
     if (lse) {
-        delta_sidecar_kernel<T, D, true><<<int(blocks), 256, 0, st>>>(
-            static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
-            zero_rows, rows, scale_log2, layout);
+        cudaLaunchKernelEx(&cfg, delta_sidecar_kernel<T, D, true>, dout_t, out_t, aux0, aux1, delta, sidecar,
+                           zero_rows, rows, scale_log2, layout);
     } else {
-        delta_sidecar_kernel<T, D, false><<<int(blocks), 256, 0, st>>>(
-            static_cast<const T*>(dout), static_cast<const T*>(out), aux0, aux1, delta, sidecar,
-            zero_rows, rows, scale_log2, layout);
+        cudaLaunchKernelEx(&cfg, delta_sidecar_kernel<T, D, false>, dout_t, out_t, aux0, aux1, delta, sidecar,
+                           zero_rows, rows, scale_log2, layout);
     }
 }
 

@@ -89,6 +89,10 @@ delta_sidecar_kernel(const T* __restrict__ dout, const T* __restrict__ out,
     const int col = lane % kLanesPerRow;
     const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    // Launched programmatically: when the kernel in front lets its dependents go early (the convert
+    // kernel of a preceding call does), the blocks are in place when it ends.  Nothing is read or
+    // written before all of it has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // let the GEMM kernel behind this one start its set-up (it waits before it reads our outputs)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #ifdef FA3B200_TRACE
@@ -185,6 +189,8 @@ dq_convert_kernel(const __grid_constant__ ConvertSegments seg) {
 #endif
     // launched programmatically behind the GEMM kernel: wait until all of it has completed
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // (a following call's first kernel may take its place now; it waits for this one itself)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // The segments form one index space, so that with enough blocks every thread makes a single
     // load -> store trip whatever the number of segments (small problems are latency-bound here).
     const int64_t n0 = seg.n_vec8[0];
