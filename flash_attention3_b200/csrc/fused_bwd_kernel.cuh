@@ -46,9 +46,9 @@
 //     dO              1 stage (D=128) or 2 stages (D=64) x D*256
 //     dS^T            32 KiB               [128 keys][128 queries]
 //     dQ staging      32 KiB               4 warps x 2 boxes of [32 rows][32 fp32]
-//     row statistics  2 KiB                {-m + log2 r, delta} x 128 rows x 2 buffers
+//     row statistics  2 KiB / 3 KiB        {-m + log2 r, delta} x 128 rows x 2 buffers (D=128) / 3 (D=64)
 //     mbarriers       256
-//     total           231,680 (D=128) / 166,144 (D=64)   of 232,448 available
+//     total           231,680 (D=128) / 167,168 (D=64)   of 232,448 available
 #pragma once
 
 #include <cuda.h>
@@ -192,12 +192,11 @@ enum Bar : int {
     kDpFull = 10,
     kPReady = 11,
     kDsReady = 12,
-    kUnused13 = 13,
-    kDqFull = 14,
-    kDqEmpty = 15,
-    kDkvFull = 16,
-    kStatsFull = 17,  // 2 buffers
-    kNumBars = 19,
+    kDqFull = 13,
+    kDqEmpty = 14,
+    kDkvFull = 15,
+    kStatsFull = 16,  // 2 buffers (not used where the statistics are published a step ahead)
+    kNumBars = 18,
 };
 
 constexpr long long kWaitTimeoutCycles = 2000000000LL;  // about one second
