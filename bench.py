@@ -56,6 +56,7 @@ CONFIGS = {
 METRIC = "fa3_bwd_tflops"
 UNIT = "TFLOP/s"
 L2_FLUSH_BYTES = 256 << 20  # larger than the 126 MB L2
+WARMUP_SECONDS = 0.3         # least wall-clock time of the warm-up of the back-to-back and end-to-end loops
 
 
 def bwd_flops(b, hq, s, d, causal):
@@ -309,8 +310,15 @@ def time_back_to_back(torch, sets, steps, warmup, barrier):
     """K calls back to back, call i on set i % len(sets); one pair of CUDA events around all of them,
     bracketed by a barrier and a device synchronisation on both sides.  Returns the milliseconds of the
     K calls together."""
-    for i in range(max(warmup, len(sets))):
+    # warm-up: at least W calls and every set once, and at least WARMUP_SECONDS of wall clock -- the calls are
+    # 30 us apart, which the host thread that enqueues them sustains only once its core has clocked up
+    t0 = time.perf_counter()
+    i = 0
+    while i < max(warmup, len(sets)) or time.perf_counter() - t0 < WARMUP_SECONDS:
         sets[i % len(sets)].step()
+        i += 1
+        if i % 256 == 0:
+            torch.cuda.synchronize()
     barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
@@ -352,8 +360,17 @@ def time_e2e(torch, wl, steps, warmup, flush, ops):
     def one():
         call(hdo_, hq_, hk_, hv_, hout_, hlse_, *host_out)
 
-    for _ in range(warmup):
+    # warm-up by wall clock as well as by count: the call is bound by copies over PCIe that the host
+    # thread must keep fed (18 copies, 6 launches and a dozen event operations per call), and a host core
+    # that has idled through the device-bound part of the run needs a while to clock up again (measured on
+    # fresh boxes: 0.6-0.9 ms per call in the first second of such calls, 0.37 ms after)
+    t0 = time.perf_counter()
+    n_warm = 0
+    while n_warm < warmup or time.perf_counter() - t0 < 2 * WARMUP_SECONDS:
         one()
+        n_warm += 1
+        if n_warm % 16 == 0:
+            torch.cuda.synchronize()
     torch.cuda.synchronize()
     times = []
     for _ in range(steps):
