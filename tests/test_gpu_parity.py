@@ -146,3 +146,39 @@ def test_cpu_tensors_are_refused():
     q = torch.zeros(1, 1, 128, 64, dtype=torch.float16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         ops.fa3_bwd(q, q, q, q, q, torch.zeros(1, 1, 128), True)
+
+
+def test_calls_queued_back_to_back_on_one_workspace():
+    """Three different problems enqueued without a synchronisation in between, all on one stream and
+    one workspace: the first kernel of a call is launched programmatically behind the last kernel of
+    the call in front and must not clear or overwrite the workspace while that one still reads it."""
+    lib = capi.load()
+    probs = [helpers.Problem(1, 4, 4, 1024, 128, "fp16", True, seed=611),      # split key tiles: slabs in the workspace
+             helpers.Problem(1, 4, 2, 512, 128, "bf16", False, seed=612),
+             helpers.Problem(2, 2, 2, 384, 64, "bf16", True, seed=613)]
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    calls, need_max = [], 0
+    for prob in probs:
+        x = prob.device_inputs()
+        p = ops.make_params(x["q"], x["k"], prob.causal, prob.scale)
+        need_max = max(need_max, lib.shaobo_fa3_bwd_v2_workspace_bytes(ctypes.byref(p)))
+        td = helpers.TORCH_DTYPE[prob.dtype]
+        out = dict(dq=helpers.poison(x["q"].shape, td), dk=helpers.poison(x["k"].shape, td),
+                   dv=helpers.poison(x["k"].shape, td), delta=helpers.poison(x["lse"].shape, torch.float32))
+        calls.append((prob, x, p, out))
+    ws = torch.full((need_max,), 0xFF, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    codes = []
+    for rep in range(2):                       # the second round finds the first one's leftovers
+        for prob, x, p, out in calls:
+            p.workspace, p.workspace_bytes = ws.data_ptr(), need_max
+            codes.append(lib.shaobo_fa3_bwd_v2(vp(x["dout"]), vp(x["q"]), vp(x["k"]), vp(x["v"]), vp(x["out"]),
+                                               vp(x["lse"]), vp(out["dq"]), vp(out["dk"]), vp(out["dv"]),
+                                               vp(out["delta"]), ctypes.byref(p)))
+    torch.cuda.synchronize()
+    assert all(c == capi.STATUS_SUCCESS for c in codes), codes
+    assert lib.shaobo_fa3_b200_device_error(1) == 0
+    for prob, x, p, out in calls:
+        got = dict(code=capi.STATUS_SUCCESS, device_error=0, dq=helpers.host(out["dq"]), dk=helpers.host(out["dk"]),
+                   dv=helpers.host(out["dv"]), delta=helpers.host(out["delta"]))
+        helpers.assert_parity(got, prob, "queued back to back")
